@@ -1,0 +1,489 @@
+"""Host-side orchestrator of the expert pipeline -- the Python face of what the reference
+bound as the ``core`` extension (MOLE/cpp/core.cpp:1347-1469).
+
+``create_UniMem``        the GPU slot pool for offloaded experts (MOLE/cpp/umemory.cpp:77-86)
+``MOLECore``             per-layer object: parameter cores, prefetch, and the forward /
+                         backward pipelines of ``_BatchFusedFWD`` (MOLE/cpp/core.cpp:991-1131,
+                         1133-1300) over "records" of at most ``ebatch_size`` experts.
+
+The pipeline keeps the reference's three phases per group of records -- exchange + parameter
+fetch, expert compute, return exchange -- on the communication / transfer / compute streams,
+but every phase is a call into ``libmole_b200.so`` on capacity-strided rows: no per-record
+tensor allocation, no permute/contiguous re-layout (core.cpp:233, 240) and no re-assembly
+copies (core.cpp:1097-1124); the grouped GEMM reads the (source rank, expert) chunks where
+the exchange put them and the return exchange writes straight into the output tensor.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from . import ops
+from ._lib import check, lib
+from .utils.Udist import MOLEDist
+from .utils.Ustream import ExpertStreamCtx
+
+
+# --------------------------------------------------------------------------- #
+# slot pool ("UniMem")
+# --------------------------------------------------------------------------- #
+class UniMem:
+    """``pool_size`` expert slots for each of W1 ``[F, M]``, b1 ``[F]``, W2 ``[F, M]``, b2 ``[M]``."""
+    _instance: Optional["UniMem"] = None
+
+    def __init__(self, device: int, pool_size: int, dtype: torch.dtype, sizes, dry: bool = False):
+        self.device = device
+        self.pool_size = pool_size
+        self.dtype = dtype
+        self.sizes = [list(s) for s in sizes]
+        self.handle = None
+        self.bases: List[Optional[torch.Tensor]] = [None] * 4
+        if pool_size == -1:
+            return
+        F, M = self.sizes[0]
+        handle = C.c_void_p()
+        ctx = None if dry else ExpertStreamCtx.get(torch.device("cuda", device)).handle
+        check(lib.mole_pool_create(ctx, pool_size, M, F, ops._DTYPES[dtype], C.byref(handle)))
+        self.handle = handle
+        self.dry = dry
+        self.bases = [self.base_ptr(i) for i in range(4)]
+
+    # -- thin wrappers -----------------------------------------------------------------
+    def base_ptr(self, p_id: int) -> int:
+        p = C.c_void_p()
+        check(lib.mole_pool_base(self.handle, p_id, C.byref(p)))
+        return p.value or 0
+
+    def view_pool_size(self) -> int:
+        n = C.c_int32()
+        check(lib.mole_pool_view_size(self.handle, C.byref(n)))
+        return n.value
+
+    def clear_virtual_mem(self) -> None:
+        check(lib.mole_pool_clear_virtual(self.handle))
+
+    def prefetch(self, moe_id: int, n: int) -> int:
+        first = C.c_int32()
+        check(lib.mole_pool_prefetch(self.handle, moe_id, n, C.byref(first)))
+        return first.value
+
+    def fetch_top_prefetched_batch(self, moe_id: int) -> int:
+        n = C.c_int32()
+        check(lib.mole_pool_pop_prefetched(self.handle, moe_id, C.byref(n)))
+        return n.value
+
+    def fetch(self, host_params, e0: int, n: int, slot0: int, skip: int,
+              absolute: bool = False) -> int:
+        arr = (C.c_void_p * 4)(*[t.data_ptr() if t is not None else None for t in host_params])
+        ticket = C.c_int32()
+        check(lib.mole_pool_fetch(self.handle, arr, e0, n, slot0, skip, int(absolute),
+                                  C.byref(ticket)))
+        return ticket.value
+
+    def wait_fetch(self, ticket: int, stream: torch.cuda.Stream) -> None:
+        check(lib.mole_pool_wait_fetch(self.handle, ticket, C.c_void_p(stream.cuda_stream)))
+
+    def mark_used(self, slot0: int, n: int, stream: torch.cuda.Stream) -> None:
+        check(lib.mole_pool_mark_used(self.handle, slot0, n, C.c_void_p(stream.cuda_stream)))
+
+    def abs_slot(self, view_slot: int) -> int:
+        a = C.c_int32()
+        check(lib.mole_pool_abs_slot(self.handle, view_slot, C.byref(a)))
+        return a.value
+
+    def log(self):
+        n = C.c_int32()
+        check(lib.mole_pool_log(self.handle, None, 0, C.byref(n)))
+        buf = (C.c_int32 * (4 * max(n.value, 1)))()
+        check(lib.mole_pool_log(self.handle, buf, n.value, C.byref(n)))
+        return [tuple(buf[4 * i:4 * i + 4]) for i in range(n.value)]
+
+
+def create_UniMem(device: int, pool_size: int, dtype, sizes, dry: bool = False) -> UniMem:
+    """One pool per process, shared by all layers (MOLE/cpp/umemory.cpp:77-86)."""
+    if isinstance(dtype, str):
+        dtype = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16}[dtype]
+    if UniMem._instance is None:
+        UniMem._instance = UniMem(device, pool_size, dtype, sizes, dry)
+    return UniMem._instance
+
+
+def _get_UniMem() -> UniMem:
+    return UniMem._instance
+
+
+# --------------------------------------------------------------------------- #
+# records
+# --------------------------------------------------------------------------- #
+@dataclass
+class Record:
+    """A batch of consecutive local experts processed by one FFN call
+    (``_BatchRecord``, MOLE/cpp/define.hpp:613-677)."""
+    use_cpu_param: bool
+    batch_base: int       # first expert inside its kind (GPU-resident or offloaded)
+    base_in_all: int      # first local expert index
+    batch_size: int
+    prefetched: int = 0   # leading experts already in their slots
+    view_base: int = 0    # first pool slot (view coordinates)
+    ticket: int = -1      # pool fetch ticket
+    slots: List[int] = field(default_factory=list)
+
+
+def build_records(s_experts: int, d_experts: int, ebatch_size: int, use_pool: bool,
+                  view_pool_size: int, prefetched: int):
+    """Records and launch groups exactly as MOLE/cpp/core.cpp:1009-1051 builds them: GPU-resident
+    experts in steps of ``ebatch_size``; offloaded experts in steps of
+    ``min(ebatch_size, visible pool)``, a new group whenever the pool wraps."""
+    records: List[Record] = []
+    groups: List[List[int]] = []
+    cur: List[int] = []
+    for i in range(0, s_experts, ebatch_size):
+        size = min(ebatch_size, s_experts - i)
+        cur.append(len(records))
+        records.append(Record(False, i, i, size))
+    d_batch = min(ebatch_size, view_pool_size if use_pool else 10000)
+    if d_experts > 0 and d_batch < 1:
+        raise RuntimeError("no pool slot is visible for the offloaded experts")
+    view_base = 0
+    for i in range(0, d_experts, max(d_batch, 1)):
+        size = min(d_batch, d_experts - i)
+        if use_pool and view_pool_size - view_base < size:
+            view_base = 0
+            groups.append(cur)
+            cur = []
+        cur.append(len(records))
+        cur_pref = min(size, prefetched - i) if prefetched > i else 0
+        records.append(Record(True, i, i + s_experts, size, cur_pref, view_base))
+        view_base += size
+    if cur:
+        groups.append(cur)
+    return records, groups
+
+
+# --------------------------------------------------------------------------- #
+# per-layer core
+# --------------------------------------------------------------------------- #
+class _Saved:
+    """Activations one forward keeps for its backward (``x0`` and ``extras[0]`` of the
+    reference's records, MOLE/cpp/define.hpp:638-639)."""
+    __slots__ = ("x0", "x1", "h", "counts", "Cs", "n_src")
+
+
+class MOLECore:
+    def __init__(self, use_pool, grad_use_pool, mome_use_pool, vari_use_pool, s_experts, d_experts,
+                 ebatch_size, world_size, act, adv_adam, acc_step, step, device, moe_id,
+                 total_experts, *, dtype=torch.float32, gelu_bwd="exact", ffn_backend=0):
+        self.use_pool = bool(use_pool)
+        self.grad_use_pool, self.mome_use_pool, self.vari_use_pool = grad_use_pool, mome_use_pool, vari_use_pool
+        self.s_experts, self.d_experts = s_experts, d_experts
+        self.ebatch_size = max(1, ebatch_size)
+        self.world_size = world_size
+        self.act_name = act
+        self.adv_adam = adv_adam
+        self.acc_step = acc_step
+        self.step = step
+        self.device = device
+        self.moe_id = moe_id
+        self.total_experts = total_experts
+        self.dtype = dtype
+        self.gelu_bwd = gelu_bwd
+        self.ffn_backend = ffn_backend
+        self.fwd_base = 0
+        self.bwd_base = 0
+        self.gpu_params = [None] * 4
+        self.gpu_grads = [None] * 4
+        self.cpu_params = [None] * 4
+        self.cpu_grads = [None] * 4
+        self._saved: Optional[_Saved] = None
+        self._records: List[Record] = []
+        self._grad_staging = None
+        if adv_adam:
+            raise NotImplementedError(
+                "adv_adam (optimizer step fused after backward) is outside the MoE-layer hot path")
+
+    # -- parameter cores (MOLE/cpp/uparameter.cpp:13-56) -----------------------------------
+    def set_GPUParamCore(self, p_id, all_tensors, grad_tensors, bias):
+        self.gpu_params[p_id], self.gpu_grads[p_id] = all_tensors, grad_tensors
+
+    def set_CPUParamCore(self, p_id, t, grad, mome, vari, bias, p_id2=None):
+        self.cpu_params[p_id], self.cpu_grads[p_id] = t, grad
+
+    def GPUParamCore_fetch_single(self, p_id, i):
+        return self.gpu_params[p_id][i]
+
+    def GPUParamCore_fetch_single_grad(self, p_id, i):
+        return self.gpu_grads[p_id][i]
+
+    def CPUParamCore_fetch_single(self, p_id, i):
+        return self.cpu_params[p_id][i]
+
+    def CPUParamCore_fetch_single_grad(self, p_id, i):
+        return self.cpu_grads[p_id][i]
+
+    def set_lazy_zero(self):
+        for g in self.cpu_grads:
+            if g is not None:
+                g.lazy_zero = True
+
+    def unset_lazy_zero(self):
+        for g in self.cpu_grads:
+            if g is not None:
+                g.lazy_zero = False
+
+    # -- prefetch (MOLE/cpp/core.cpp:25-75) ------------------------------------------------
+    def _prefetch(self, base_attr: str, batch_size: int) -> None:
+        if batch_size == 0 or self.d_experts == 0:
+            return
+        pool = _get_UniMem()
+        base = getattr(self, base_attr)
+        batch_size = min(batch_size, self.d_experts - base)
+        if batch_size <= 0:
+            return
+        first = pool.prefetch(self.moe_id, batch_size)
+        pool.fetch(self.cpu_params, base, batch_size, first, 0, absolute=True)
+        setattr(self, base_attr, base + batch_size)
+
+    def prefetch_fwd(self, batch_size: int) -> None:
+        self._prefetch("fwd_base", batch_size)
+
+    def prefetch_bwd(self, batch_size: int) -> None:
+        self._prefetch("bwd_base", batch_size)
+
+    def dummy_fetch(self, batch_size: int) -> None:
+        if batch_size == 0:
+            return
+        _get_UniMem().fetch(self.cpu_params, 0, batch_size, 0, 0)
+
+    # -- helpers ---------------------------------------------------------------------------
+    def _desc(self, M, F, n_src, Cs, rec: Record, n_slots, accumulate=False, n_grad_slots=0):
+        L = self.s_experts + self.d_experts
+        return ops.make_ffn_desc(self.dtype, self.act_name, self.gelu_bwd, M, F, L, n_src, Cs,
+                                 rec.base_in_all, rec.base_in_all + rec.batch_size, n_slots,
+                                 accumulate, self.ffn_backend, n_grad_slots)
+
+    def _weights(self, rec: Record):
+        """(w1, b1, w2, b2, slot map, n_slots) for a record."""
+        L = self.s_experts + self.d_experts
+        slots = [0] * L
+        if not rec.use_cpu_param:
+            for i in range(rec.batch_size):
+                slots[rec.base_in_all + i] = rec.batch_base + i
+            return (*self.gpu_params, slots, self.s_experts)
+        pool = _get_UniMem()
+        for i in range(rec.batch_size):
+            slots[rec.base_in_all + i] = rec.slots[i]
+        F, M = pool.sizes[0]
+        return (*pool.bases, slots, pool.pool_size)
+
+    def _fetch_para(self, rec: Record) -> None:
+        """Host-to-device fetch of a record's offloaded experts on the transfer stream
+        (``_BatchRecord::fetch_para``, MOLE/cpp/core.cpp:110-143)."""
+        if not rec.use_cpu_param:
+            return
+        pool = _get_UniMem()
+        rec.ticket = pool.fetch(self.cpu_params, rec.batch_base, rec.batch_size, rec.view_base,
+                                rec.prefetched)
+        rec.slots = [pool.abs_slot(rec.view_base + i) for i in range(rec.batch_size)]
+
+    # -- forward pipeline (MOLE/cpp/core.cpp:991-1131) -------------------------------------
+    def forward(self, dispatched: torch.Tensor, counts: torch.Tensor, requires_grad: bool):
+        """``dispatched`` ``[E_total, Cs, M]`` capacity-strided rows, ``counts`` ``[E_total]``
+        valid rows per chunk -> expert outputs in the same layout."""
+        E, Cs, M = dispatched.shape
+        W = self.world_size
+        L = self.s_experts + self.d_experts
+        assert E == L * W, "dispatched tensor does not match the expert count"
+        F = self._ffn_dim()
+        comp = torch.cuda.current_stream()
+        multi = W > 1 or self.d_experts > 0
+        sctx = ExpertStreamCtx.get(dispatched.device) if multi else None
+        comm = sctx.comm_stream() if W > 1 else comp
+
+        pool = _get_UniMem() if self.d_experts > 0 else None
+        prefetched = pool.fetch_top_prefetched_batch(self.moe_id) if pool else 0
+        self.fwd_base = 0
+        view = pool.view_pool_size() if pool else 0
+        records, groups = build_records(self.s_experts, self.d_experts, self.ebatch_size,
+                                        self.use_pool, view, prefetched)
+        self._records = records
+
+        rows_total = W * L * Cs
+        if W > 1:
+            x0 = torch.empty(W, L, Cs, M, dtype=dispatched.dtype, device=dispatched.device)
+            rcounts = torch.empty(W * L, dtype=torch.int32, device=dispatched.device)
+            out_local = torch.empty_like(x0)
+            ret = torch.empty_like(dispatched)
+            ExpertStreamCtx.wait(comm, comp)
+            with torch.cuda.stream(comm):
+                MOLEDist.all2all(rcounts, counts, stream=comm)
+            for t in (x0, rcounts, out_local, ret, dispatched, counts):
+                t.record_stream(comm)
+        else:
+            x0, rcounts, out_local = dispatched, counts, torch.empty_like(dispatched)
+            ret = out_local
+        x1 = torch.empty(rows_total, F, dtype=dispatched.dtype, device=dispatched.device)
+        h = torch.empty(rows_total, F, dtype=dispatched.dtype, device=dispatched.device)
+        es = dispatched.element_size()
+        chunk_bytes = Cs * M * es
+
+        for g in groups:
+            for ri in g:
+                rec = records[ri]
+                if W > 1:       # first exchange of this record's experts, on the comm stream
+                    MOLEDist.all2all(x0, dispatched, rec.batch_size * chunk_bytes, L * chunk_bytes,
+                                     rec.base_in_all * chunk_bytes, stream=comm)
+                self._fetch_para(rec)
+            for ri in g:
+                rec = records[ri]
+                if W > 1:
+                    ExpertStreamCtx.wait(comp, comm)
+                if rec.use_cpu_param:
+                    pool.wait_fetch(rec.ticket, comp)
+                w1, b1, w2, b2, slots, n_slots = self._weights(rec)
+                desc = self._desc(M, F, W, Cs, rec, n_slots)
+                ws = ops.ffn_workspace(desc, dispatched.device)
+                ops.ffn_fwd(desc, rcounts, x0, w1, b1, w2, b2, x1, h, out_local, ws, slots)
+                if rec.use_cpu_param:
+                    pool.mark_used(rec.view_base, rec.batch_size, comp)
+            for ri in g:
+                rec = records[ri]
+                if W > 1:       # return exchange, on the comm stream after this record's compute
+                    ExpertStreamCtx.wait(comm, comp)
+                    MOLEDist.all2all(ret, out_local, rec.batch_size * chunk_bytes, L * chunk_bytes,
+                                     rec.base_in_all * chunk_bytes, stream=comm)
+        if W > 1:
+            ExpertStreamCtx.wait(comp, comm)
+        if requires_grad:
+            s = _Saved()
+            s.x0, s.x1, s.h, s.counts, s.Cs, s.n_src = x0, x1, h, rcounts, Cs, W
+            self._saved = s
+        return ret
+
+    # -- backward pipeline (MOLE/cpp/core.cpp:1133-1300) -----------------------------------
+    def backward(self, dout: torch.Tensor, counts: torch.Tensor, input_requires_grad: bool = True):
+        s = self._saved
+        if s is None:
+            raise RuntimeError("MOLECore.backward without a matching forward")
+        E, Cs, M = dout.shape
+        W = self.world_size
+        L = self.s_experts + self.d_experts
+        F = self._ffn_dim()
+        comp = torch.cuda.current_stream()
+        multi = W > 1 or self.d_experts > 0
+        sctx = ExpertStreamCtx.get(dout.device) if multi else None
+        comm = sctx.comm_stream() if W > 1 else comp
+        pool = _get_UniMem() if self.d_experts > 0 else None
+        prefetched = pool.fetch_top_prefetched_batch(self.moe_id) if pool else 0
+        self.bwd_base = 0
+        view = pool.view_pool_size() if pool else 0
+        records, groups = build_records(self.s_experts, self.d_experts, self.ebatch_size,
+                                        self.use_pool, view, prefetched)
+        es = dout.element_size()
+        chunk_bytes = Cs * M * es
+        rows_total = W * L * Cs
+        if W > 1:
+            g_local = torch.empty(W, L, Cs, M, dtype=dout.dtype, device=dout.device)
+            dx_local = torch.empty_like(g_local) if input_requires_grad else None
+            ret = torch.empty_like(dout) if input_requires_grad else None
+            ExpertStreamCtx.wait(comm, comp)
+            for t in (g_local, dx_local, ret, dout):
+                if t is not None:
+                    t.record_stream(comm)
+        else:
+            g_local = dout
+            dx_local = torch.empty_like(dout) if input_requires_grad else None
+            ret = dx_local
+        dx1 = torch.empty(rows_total, F, dtype=dout.dtype, device=dout.device)
+        accumulate = self.acc_step > 1 and (self.step % self.acc_step) != 0
+
+        for g in groups:
+            for ri in g:
+                rec = records[ri]
+                if W > 1:
+                    MOLEDist.all2all(g_local, dout, rec.batch_size * chunk_bytes, L * chunk_bytes,
+                                     rec.base_in_all * chunk_bytes, stream=comm)
+                self._fetch_para(rec)          # weights are fetched again for backward
+            for ri in g:
+                rec = records[ri]
+                if W > 1:
+                    ExpertStreamCtx.wait(comp, comm)
+                if rec.use_cpu_param:
+                    pool.wait_fetch(rec.ticket, comp)
+                w1, _, w2, _, slots, n_slots = self._weights(rec)
+                if rec.use_cpu_param:
+                    grads, gslots, g_slots_n = self._staging_grads(rec, M, F, dout)
+                    acc = False
+                else:
+                    grads, gslots, g_slots_n = self.gpu_grads, slots, self.s_experts
+                    acc = accumulate
+                desc = self._desc(M, F, W, Cs, rec, n_slots, acc, g_slots_n)
+                ws = ops.ffn_workspace(desc, dout.device)
+                ops.ffn_bwd(desc, s.counts, g_local, s.x0, s.x1, s.h, w1, w2, dx1, dx_local,
+                            grads[0], grads[1], grads[2], grads[3], ws, slots, gslots)
+                if rec.use_cpu_param:
+                    pool.mark_used(rec.view_base, rec.batch_size, comp)
+                    self._store_grad(rec, grads, comp)
+            for ri in g:
+                rec = records[ri]
+                if W > 1 and input_requires_grad:
+                    ExpertStreamCtx.wait(comm, comp)
+                    MOLEDist.all2all(ret, dx_local, rec.batch_size * chunk_bytes, L * chunk_bytes,
+                                     rec.base_in_all * chunk_bytes, stream=comm)
+        if W > 1:
+            ExpertStreamCtx.wait(comp, comm)
+        if self.d_experts > 0:
+            check(lib.mole_ctx_synchronize(sctx.handle, 4))     # D2H gradient stores done
+            self._finish_grad_accumulate()
+        self.step += 1
+        self.unset_lazy_zero()
+        self._saved = None
+        return ret
+
+    # -- offloaded-expert gradients (MOLE/cpp/core.cpp:77-103, uparameter.cpp:68-83) ---------
+    def _staging_grads(self, rec: Record, M, F, like):
+        n = self.ebatch_size
+        if self._grad_staging is None:
+            kw = dict(dtype=like.dtype, device=like.device)
+            self._grad_staging = [torch.empty(n, F, M, **kw), torch.empty(n, F, **kw),
+                                  torch.empty(n, F, M, **kw), torch.empty(n, M, **kw)]
+            self._pending_acc = []
+        L = self.s_experts + self.d_experts
+        gslots = [0] * L
+        for i in range(rec.batch_size):
+            gslots[rec.base_in_all + i] = i
+        # the staging block is reused by the next record: order it after the previous D2H
+        sctx = ExpertStreamCtx.get(like.device)
+        ExpertStreamCtx.wait(torch.cuda.current_stream(), sctx.tran_back_stream())
+        return self._grad_staging, gslots, n
+
+    def _store_grad(self, rec: Record, grads, comp) -> None:
+        sctx = ExpertStreamCtx.get(grads[0].device)
+        lazy = getattr(self.cpu_grads[0], "lazy_zero", True)
+        for p_id in range(4):
+            host = self.cpu_grads[p_id][rec.batch_base:rec.batch_base + rec.batch_size]
+            dev = grads[p_id][:rec.batch_size]
+            nbytes = host.numel() * host.element_size()
+            if self.acc_step > 1 and not lazy:
+                stage = torch.empty_like(host).pin_memory()
+                check(lib.mole_store_to_host(sctx.handle, C.c_void_p(stage.data_ptr()),
+                                             C.c_void_p(dev.data_ptr()), nbytes,
+                                             C.c_void_p(comp.cuda_stream)))
+                self._pending_acc.append((host, stage))
+            else:
+                check(lib.mole_store_to_host(sctx.handle, C.c_void_p(host.data_ptr()),
+                                             C.c_void_p(dev.data_ptr()), nbytes,
+                                             C.c_void_p(comp.cuda_stream)))
+
+    def _finish_grad_accumulate(self) -> None:
+        for host, stage in getattr(self, "_pending_acc", []):
+            host += stage
+        self._pending_acc = []
+
+    def _ffn_dim(self) -> int:
+        for t in (self.gpu_params[0], self.cpu_params[0]):
+            if t is not None and not isinstance(t, int):
+                return t.shape[1]
+        raise RuntimeError("no expert parameters registered")

@@ -1,0 +1,153 @@
+// Expert FFN forward / backward over capacity-strided rows: tile schedule + grouped GEMMs.
+//
+// forward  (MOLE/cpp/core.cpp:350-353):  x1 = x W1^T + b1;  h = act(x1);  out = h W2 + b2
+// backward (MOLE/cpp/core.cpp:388-412):  gW2 = h^T dO;  dX1 = (dO W2^T) * act'(x1);  gb2 = sum dO;
+//                                        gW1 = dX1^T x;  gb1 = sum dX1;  dX = dX1 W1
+// with "=" or "+=" into the gradients (core.cpp:274-316).  The reference runs these on the
+// capacity-padded [B, W*C, .] tensors after a permute+contiguous re-layout; here the schedule
+// points the GEMMs at the (source rank, expert) chunks where they lie and skips empty tiles.
+#include "gemm.cuh"
+
+namespace mole {
+
+static int check_desc(const mole_ffn_desc* d) {
+  MOLE_REQUIRE(d != nullptr, "desc is null");
+  MOLE_REQUIRE(d->dtype == MOLE_F32 || d->dtype == MOLE_BF16, "dtype %d", d->dtype);
+  MOLE_REQUIRE(d->act == MOLE_ACT_GELU || d->act == MOLE_ACT_RELU, "act %d", d->act);
+  MOLE_REQUIRE(d->M > 0 && d->F > 0 && d->M % 64 == 0 && d->F % 64 == 0,
+               "M=%d and F=%d must be positive multiples of 64", d->M, d->F);
+  MOLE_REQUIRE(d->L >= 1 && d->L <= kMaxLocalExperts, "L=%d not in [1,%d]", d->L, kMaxLocalExperts);
+  MOLE_REQUIRE(d->n_src >= 1, "n_src=%d", d->n_src);
+  MOLE_REQUIRE(d->Cs > 0 && d->Cs % kTileRows == 0, "Cs=%d must be a positive multiple of 128", d->Cs);
+  MOLE_REQUIRE(0 <= d->e_begin && d->e_begin <= d->e_end && d->e_end <= d->L,
+               "expert range [%d,%d) outside [0,%d)", d->e_begin, d->e_end, d->L);
+  MOLE_REQUIRE(d->n_slots >= 1 && d->n_slots <= 32767, "n_slots=%d", d->n_slots);
+  MOLE_REQUIRE(d->n_grad_slots >= 0 && d->n_grad_slots <= 32767, "n_grad_slots=%d", d->n_grad_slots);
+  MOLE_REQUIRE((int64_t)d->L * d->n_src * d->Cs < ((int64_t)1 << 31), "row index overflows int32");
+  if (d->dtype == MOLE_BF16 && d->backend != 1 && !tc_supported(d->M, d->F))
+    return fail(MOLE_ERR_UNSUPPORTED,
+                "bf16 tensor-core path needs M and F to be multiples of 128 (M=%d F=%d)", d->M, d->F);
+  return MOLE_OK;
+}
+
+static int fill_slots(SlotMap& m, const mole_ffn_desc* d, const int32_t* host_map, int n_slots) {
+  for (int l = 0; l < kMaxLocalExperts; ++l) m.s[l] = 0;
+  for (int l = d->e_begin; l < d->e_end; ++l) {
+    const int s = host_map ? host_map[l] : l;
+    MOLE_REQUIRE(s >= 0 && s < n_slots, "slot %d of expert %d outside [0,%d)", s, l, n_slots);
+    m.s[l] = (int16_t)s;
+  }
+  return MOLE_OK;
+}
+
+static bool use_tc(const mole_ffn_desc* d) { return d->dtype == MOLE_BF16 && d->backend != 1; }
+
+static int row_gemm(const mole_ffn_desc* d, const RowGemmArgs& a, cudaStream_t st) {
+  return use_tc(d) ? tc_row_gemm(a, st) : simt_row_gemm(d->dtype, a, st);
+}
+static int wgrad(const mole_ffn_desc* d, const WgradArgs& a, cudaStream_t st) {
+  return use_tc(d) ? tc_wgrad(a, st) : simt_wgrad(d->dtype, a, st);
+}
+
+}  // namespace mole
+
+using namespace mole;
+
+extern "C" int mole_ffn_workspace_bytes(const mole_ffn_desc* d, int64_t* bytes) {
+  if (int rc = check_desc(d)) return rc;
+  MOLE_REQUIRE(bytes != nullptr, "bytes is null");
+  *bytes = schedule_bytes(d->L, d->n_src, d->Cs);
+  return MOLE_OK;
+}
+
+extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
+                            const int32_t* slot_of_expert, const void* x, const void* w1,
+                            const void* b1, const void* w2, const void* b2, void* x1, void* h,
+                            void* out, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (int rc = check_desc(d)) return rc;
+  MOLE_REQUIRE(counts && x && w1 && b1 && w2 && b2 && x1 && h && out && workspace,
+               "null pointer argument");
+  MOLE_REQUIRE(workspace_bytes >= schedule_bytes(d->L, d->n_src, d->Cs), "workspace too small");
+  if (d->e_begin == d->e_end) return MOLE_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Schedule s = carve_schedule(workspace, d->L, d->n_src, d->Cs);
+  if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+
+  RowGemmArgs a{};
+  if (int rc = fill_slots(a.wslot, d, slot_of_expert, d->n_slots)) return rc;
+  a.sched = s;
+  a.w_expert_stride = (int64_t)d->F * d->M;
+  a.n_slots = d->n_slots;
+  a.total_rows = (int64_t)d->L * d->n_src * d->Cs;
+  a.act = d->act;
+  a.gelu_bwd = d->gelu_bwd;
+  a.e_begin = d->e_begin;
+  a.n_experts = d->e_end - d->e_begin;
+  // FC1: [rows, M] x W1_e^T ([F, M] read as [N=F][K=M])
+  a.A = x; a.W = w1; a.w_nk = 1; a.N = d->F; a.K = d->M; a.bias = b1; a.aux = nullptr;
+  a.out0 = x1; a.out1 = h; a.epi = EPI_FC1;
+  if (int rc = row_gemm(d, a, st)) return rc;
+  // FC2: [rows, F] x W2_e ([F, M] read as [K=F][N=M])
+  a.A = h; a.W = w2; a.w_nk = 0; a.N = d->M; a.K = d->F; a.bias = b2;
+  a.out0 = out; a.out1 = nullptr; a.epi = EPI_BIAS;
+  return row_gemm(d, a, st);
+}
+
+extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
+                            const int32_t* slot_of_expert, const int32_t* grad_slot_of_expert,
+                            const void* dout, const void* x, const void* x1, const void* h,
+                            const void* w1, const void* w2, void* dx1, void* dx, void* gw1,
+                            void* gb1, void* gw2, void* gb2, void* workspace,
+                            int64_t workspace_bytes, void* stream) {
+  if (int rc = check_desc(d)) return rc;
+  MOLE_REQUIRE(counts && dout && x && x1 && h && w1 && w2 && dx1 && gw1 && gb1 && gw2 && gb2 &&
+               workspace, "null pointer argument");
+  MOLE_REQUIRE(workspace_bytes >= schedule_bytes(d->L, d->n_src, d->Cs), "workspace too small");
+  if (d->e_begin == d->e_end) return MOLE_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Schedule s = carve_schedule(workspace, d->L, d->n_src, d->Cs);
+  if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+  const int64_t total_rows = (int64_t)d->L * d->n_src * d->Cs;
+  const int n_experts = d->e_end - d->e_begin;
+
+  SlotMap wslot, gslot;
+  const int n_grad_slots = d->n_grad_slots > 0 ? d->n_grad_slots : d->n_slots;
+  if (int rc = fill_slots(wslot, d, slot_of_expert, d->n_slots)) return rc;
+  if (int rc = fill_slots(gslot, d, grad_slot_of_expert, n_grad_slots)) return rc;
+
+  WgradArgs g{};
+  g.sched = s; g.gslot = gslot; g.n_slots = n_grad_slots; g.total_rows = total_rows;
+  g.accumulate = d->accumulate; g.e_begin = d->e_begin; g.n_experts = n_experts;
+  g.P = d->F; g.Q = d->M;
+  ColsumArgs c{};
+  c.sched = s; c.gslot = gslot; c.accumulate = d->accumulate; c.e_begin = d->e_begin;
+  c.n_experts = n_experts;
+
+  // gW2 = h^T dO
+  g.A = h; g.B = dout; g.out = gw2;
+  if (int rc = wgrad(d, g, st)) return rc;
+  // dX1 = (dO W2^T) * act'(x1):  W2_e read as [N=F][K=M]
+  RowGemmArgs a{};
+  a.sched = s; a.wslot = wslot; a.w_expert_stride = (int64_t)d->F * d->M; a.n_slots = d->n_slots;
+  a.total_rows = total_rows; a.act = d->act; a.gelu_bwd = d->gelu_bwd;
+  a.e_begin = d->e_begin; a.n_experts = n_experts;
+  a.A = dout; a.W = w2; a.w_nk = 1; a.N = d->F; a.K = d->M; a.bias = nullptr; a.aux = x1;
+  a.out0 = dx1; a.out1 = nullptr; a.epi = EPI_DACT;
+  if (int rc = row_gemm(d, a, st)) return rc;
+  // gb2 = sum_rows dO
+  c.A = dout; c.N = d->M; c.out = gb2;
+  if (int rc = colsum(d->dtype, c, st)) return rc;
+  // gW1 = dX1^T x
+  g.A = dx1; g.B = x; g.out = gw1;
+  if (int rc = wgrad(d, g, st)) return rc;
+  // gb1 = sum_rows dX1
+  c.A = dx1; c.N = d->F; c.out = gb1;
+  if (int rc = colsum(d->dtype, c, st)) return rc;
+  // dX = dX1 W1:  W1_e read as [K=F][N=M]
+  if (dx != nullptr) {
+    a.A = dx1; a.W = w1; a.w_nk = 0; a.N = d->M; a.K = d->F; a.bias = nullptr; a.aux = nullptr;
+    a.out0 = dx; a.out1 = nullptr; a.epi = EPI_STORE;
+    if (int rc = row_gemm(d, a, st)) return rc;
+  }
+  return MOLE_OK;
+}

@@ -1,0 +1,602 @@
+// (c) Grouped expert GEMM on the sm_100a tensor cores: tcgen05.mma with TMEM accumulators,
+// operands staged in shared memory by TMA (no multicast), persistent CTAs, warp-specialised:
+//
+//   warp 0        TMA producer   (one lane): activation / weight tiles -> smem ring
+//   warp 1        MMA issuer     (one lane): tcgen05.mma over the ring, double-buffered TMEM
+//   warps 2..9    epilogue       TMEM -> registers -> fused epilogue -> global memory
+//
+// One kernel template covers the six GEMMs of the expert FFN (MOLE/cpp/core.cpp:350-353
+// forward, :388-412 backward):
+//
+//   rows mode   out[r, n] = epi(sum_k A[r, k] W_e(k, n))     per scheduled 128-row tile
+//      FC1   A = x   (K-major), W1_e as [N=F][K=M] (K-major)   epi: +b1, store x1 and act(x1)
+//      FC2   A = h   (K-major), W2_e as [K=F][N=M] (N-major)   epi: +b2
+//      dX2   A = dO  (K-major), W2_e as [N=F][K=M] (K-major)   epi: * act'(x1)
+//      dX    A = dX1 (K-major), W1_e as [K=F][N=M] (N-major)   epi: store
+//   wgrad mode  out_e[p, q] (+)= sum_{r in tiles of e} A[r, p] B[r, q]    (both operands MN-major)
+//      dW2   A = h, B = dO;   dW1   A = dX1, B = x
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel records a code in the
+// library's fault word, stops waiting for the rest of its run, still frees its TMEM and exits.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "gemm.cuh"
+
+namespace mole {
+
+constexpr int kBM = 128;          // rows of one UMMA (cta_group::1)
+constexpr int kBK = 64;           // K elements per stage = one 128-byte swizzle span of bf16
+constexpr int kUmmaK = 16;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr uint32_t kABytes = kBM * kBK * 2;
+
+enum TcMode : int { TC_ROWS = 0, TC_WGRAD = 1 };
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  `abort_flag` lives in shared memory: once any wait of this CTA has run out,
+// later waits return at once so the kernel drains quickly.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* fault, int code) {
+  if (mbar_try_wait(bar, parity)) return;
+  if (*abort_flag) return;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 0x3ff) == 0) {
+      if (*abort_flag) return;
+      if (globaltimer_ns() - t0 > 2000000000ull) {     // 2 s
+        *abort_flag = 1;
+        atomicCAS(fault, 0, code);
+        return;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, bf16 (layouts as documented for UMMA):
+//   K-major  : rows of 128 B (64 K elements), 8-row groups 1024 B apart (SBO); LBO unused
+//   MN-major : 64 MN elements (128 B) contiguous per K row, 8 K rows per 1024-byte group (SBO),
+//              next 64 MN elements `lbo_bytes` further (LBO)
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffff) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;      // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;      // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* p, float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p + 8 * i);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+      v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
+}
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* p, const float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    *reinterpret_cast<uint4*>(p + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+struct TcParams {
+  // schedule
+  const int32_t* n_tiles;
+  const int32_t* expert_tile_start;
+  const int32_t* tile_row0;
+  const int32_t* tile_expert;
+  int n_experts, e_begin;
+  int N, K;                 // rows mode: output columns / reduction.  wgrad: Q / unused
+  int P;                    // wgrad: output rows per expert
+  int epi, act, gelu_bwd, accumulate;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux;
+  __nv_bfloat16* out0;
+  __nv_bfloat16* out1;
+  int32_t* fault;
+  SlotMap slot;
+};
+
+struct WorkItem {
+  int valid;
+  int row0;       // rows mode: first row of the tile.  wgrad: p0
+  int n0;         // first output column
+  int el;         // expert index relative to e_begin
+  int t0, t1;     // wgrad: tile range of the expert
+};
+
+template <int MODE, int BN>
+__device__ __forceinline__ WorkItem decode_item(const TcParams& p, int item) {
+  WorkItem w;
+  w.valid = 0;
+  if (MODE == TC_ROWS) {
+    const int nb = p.N / BN;
+    const int total = (*p.n_tiles) * nb;
+    if (item >= total) return w;
+    int lo = 0, hi = p.n_experts;            // last expert with tile_start * nb <= item
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.expert_tile_start[mid] * nb <= item) lo = mid; else hi = mid;
+    }
+    const int s = p.expert_tile_start[lo], nt = p.expert_tile_start[lo + 1] - s;
+    const int local = item - s * nb;
+    const int tile = s + local % nt;
+    w.valid = 1;
+    w.el = lo;
+    w.row0 = p.tile_row0[tile];
+    w.n0 = (local / nt) * BN;
+    w.t0 = w.t1 = 0;
+  } else {
+    const int pb = p.P / kBM, qb = p.N / BN;
+    if (item >= p.n_experts * pb * qb) return w;
+    w.valid = 1;
+    w.el = item / (pb * qb);
+    const int r = item - w.el * pb * qb;
+    w.row0 = (r / qb) * kBM;
+    w.n0 = (r % qb) * BN;
+    w.t0 = p.expert_tile_start[w.el];
+    w.t1 = p.expert_tile_start[w.el + 1];
+  }
+  return w;
+}
+
+template <int MODE, bool B_KMAJOR, int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ TcParams p) {
+  constexpr uint32_t kBBytes = BN * kBK * 2;
+  constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kTmemCols = 2 * BN;     // two accumulator stages (256 or 512 columns)
+  constexpr bool A_MN = (MODE == TC_WGRAD);
+  constexpr bool B_MN = (MODE == TC_WGRAD) || !B_KMAJOR;
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                              ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                              ((uint32_t)(kBM >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, kEpiWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int item = blockIdx.x;; item += gridDim.x) {
+        const WorkItem w = decode_item<MODE, BN>(p, item);
+        if (!w.valid) break;
+        const int slot = p.slot.s[p.e_begin + w.el];
+        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
+        for (int kb = 0; kb < nkb; ++kb) {
+          mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1);
+          const uint32_t bar = full0 + 8 * stage;
+          const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
+          mbar_expect_tx(bar, kStageBytes);
+          if (MODE == TC_ROWS) {
+            tma_load_2d(sa, &tmap_a, bar, kb * kBK, w.row0);
+            if (B_KMAJOR) {
+              tma_load_3d(sb, &tmap_b, bar, kb * kBK, w.n0, slot);
+            } else {
+#pragma unroll
+              for (int i = 0; i < BN / 64; ++i)
+                tma_load_3d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, kb * kBK, slot);
+            }
+          } else {
+            const int row = p.tile_row0[w.t0 + (kb >> 1)] + (kb & 1) * kBK;
+#pragma unroll
+            for (int i = 0; i < kBM / 64; ++i)
+              tma_load_2d(sa + i * 8192, &tmap_a, bar, w.row0 + 64 * i, row);
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, row);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int item = blockIdx.x;; item += gridDim.x) {
+        const WorkItem w = decode_item<MODE, BN>(p, item);
+        if (!w.valid) break;
+        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
+        if (nkb == 0) continue;                       // empty expert: epilogue writes zeros
+        mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 2);
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 3);
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
+            const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
+                                     : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
+            const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
+                                     : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
+            tcgen05_mma_bf16(d_tmem, ad, bd, kIdesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          tcgen05_commit(empty0 + 8 * stage);         // frees the smem stage when the MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        tcgen05_commit(tfull0 + 8 * acc);             // accumulator ready for the epilogue
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -----------------------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;                     // TMEM lanes this warp may read
+    const int chalf = ew >> 2;                        // which half of the BN columns
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int item = blockIdx.x;; item += gridDim.x) {
+      const WorkItem w = decode_item<MODE, BN>(p, item);
+      if (!w.valid) break;
+      const int e = p.e_begin + w.el;
+      const int slot = p.slot.s[e];
+      const bool empty = MODE == TC_WGRAD && w.t1 == w.t0;
+      if (!empty) {
+        mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4);
+        tcgen05_fence_after();
+      }
+      const int lrow = quarter * 32 + lane;
+      int64_t obase;            // element offset of (row, n0) in the output
+      if (MODE == TC_ROWS) obase = (int64_t)(w.row0 + lrow) * p.N + w.n0;
+      else obase = ((int64_t)slot * p.P + w.row0 + lrow) * p.N + w.n0;
+      const __nv_bfloat16* bias =
+          (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
+#pragma unroll 1
+      for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
+        float v[32];
+        if (!empty) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        }
+        if (MODE == TC_WGRAD) {
+          if (p.accumulate) {
+            float old[32];
+            load_bf16x32(p.out0 + obase + c0, old);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += old[i];
+          }
+          store_bf16x32(p.out0 + obase + c0, v);
+        } else if (p.epi == EPI_FC1) {
+          float b[32], h[32];
+          if (bias) load_bf16x32(bias + c0, b);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v[i] += bias ? b[i] : 0.f;
+            // the saved pre-activation is bf16: the activation is taken of the rounded value so
+            // that backward's act'(x1) and forward's act(x1) see the same x1
+            v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+            h[i] = act_fwd(v[i], p.act);
+          }
+          store_bf16x32(p.out0 + obase + c0, v);
+          store_bf16x32(p.out1 + obase + c0, h);
+        } else if (p.epi == EPI_BIAS) {
+          float b[32];
+          if (bias) {
+            load_bf16x32(bias + c0, b);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += b[i];
+          }
+          store_bf16x32(p.out0 + obase + c0, v);
+        } else if (p.epi == EPI_DACT) {
+          float x1[32];
+          load_bf16x32(p.aux + obase + c0, x1);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= act_grad(x1[i], p.act, p.gelu_bwd);
+          store_bf16x32(p.out0 + obase + c0, v);
+        } else {
+          store_bf16x32(p.out0 + obase + c0, v);
+        }
+      }
+      if (!empty) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// bf16 tensor, innermost dimension contiguous, 128-byte swizzle, box inner extent 64 elements
+static int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                    const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(MOLE_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+  cuuint64_t gdim[3], gstride[2];
+  cuuint32_t bdim[3], estr[3] = {1, 1, 1};
+  uint64_t stride = 2;
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    stride *= dims[i];
+    if (i < rank - 1) gstride[i] = stride;
+  }
+  MOLE_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor base %p not 16-byte aligned", base);
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim,
+                        gstride, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MOLE_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return MOLE_OK;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+bool tc_supported(int M, int F) { return M % 128 == 0 && F % 128 == 0 && M >= 128 && F >= 128; }
+
+template <int MODE, bool B_KMAJOR, int BN>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_items,
+                     cudaStream_t st) {
+  constexpr int STAGES = BN == 256 ? 4 : 6;
+  constexpr size_t smem = (size_t)STAGES * (kABytes + BN * kBK * 2) + 1024;
+  auto kern = tc_gemm_kernel<MODE, B_KMAJOR, BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  int grid = sm_count();
+  if (max_items < grid) grid = max_items;
+  if (grid <= 0) return MOLE_OK;
+  kern<<<grid, kThreads, smem, st>>>(ma, mb, p);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+static void fill_sched(TcParams& p, const Schedule& s) {
+  p.n_tiles = s.n_tiles;
+  p.expert_tile_start = s.expert_tile_start;
+  p.tile_row0 = s.tile_row0;
+  p.tile_expert = s.tile_expert;
+}
+
+int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
+  MOLE_REQUIRE(a.N % 128 == 0 && a.K % kBK == 0, "tensor-core GEMM needs N %% 128 == 0 and K %% 64 == 0 (N=%d K=%d)", a.N, a.K);
+  MOLE_REQUIRE(a.total_rows % kTileRows == 0, "row buffers must hold whole 128-row tiles");
+  const int BN = a.N % 256 == 0 ? 256 : 128;
+  CUtensorMap ma, mb;
+  {
+    const uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.total_rows};
+    const uint32_t box[2] = {kBK, kBM};
+    if (int rc = make_map(&ma, a.A, 2, dims, box)) return rc;
+  }
+  {
+    // the weights are [n_slots][F][M] with M contiguous; as [N][K] that is N = F, K = M, as
+    // [K][N] it is K = F, N = M: either way dims = {M, F, n_slots}
+    const uint64_t inner = a.w_nk ? (uint64_t)a.K : (uint64_t)a.N;
+    const uint64_t outer = a.w_nk ? (uint64_t)a.N : (uint64_t)a.K;
+    MOLE_REQUIRE((int64_t)(inner * outer) == a.w_expert_stride, "weight stride mismatch");
+    const uint64_t dims[3] = {inner, outer, (uint64_t)a.n_slots};
+    const uint32_t box_k[3] = {kBK, (uint32_t)BN, 1};
+    const uint32_t box_n[3] = {64, kBK, 1};
+    if (int rc = make_map(&mb, a.W, 3, dims, a.w_nk ? box_k : box_n)) return rc;
+  }
+  TcParams p{};
+  fill_sched(p, a.sched);
+  p.n_experts = a.n_experts;
+  p.e_begin = a.e_begin;
+  p.N = a.N;
+  p.K = a.K;
+  p.P = 0;
+  p.epi = a.epi;
+  p.act = a.act;
+  p.gelu_bwd = a.gelu_bwd;
+  p.accumulate = 0;
+  p.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  p.aux = static_cast<const __nv_bfloat16*>(a.aux);
+  p.out0 = static_cast<__nv_bfloat16*>(a.out0);
+  p.out1 = static_cast<__nv_bfloat16*>(a.out1);
+  p.fault = device_fault_word();
+  p.slot = a.wslot;
+  const int max_items = a.sched.max_tiles * (a.N / BN);
+  if (a.w_nk) {
+    return BN == 256 ? launch_tc<TC_ROWS, true, 256>(ma, mb, p, max_items, st)
+                     : launch_tc<TC_ROWS, true, 128>(ma, mb, p, max_items, st);
+  }
+  return BN == 256 ? launch_tc<TC_ROWS, false, 256>(ma, mb, p, max_items, st)
+                   : launch_tc<TC_ROWS, false, 128>(ma, mb, p, max_items, st);
+}
+
+int tc_wgrad(const WgradArgs& a, cudaStream_t st) {
+  MOLE_REQUIRE(a.P % kBM == 0 && a.Q % 128 == 0, "tensor-core wgrad needs F %% 128 == 0 and M %% 128 == 0");
+  MOLE_REQUIRE(a.total_rows % kTileRows == 0, "row buffers must hold whole 128-row tiles");
+  if (a.n_experts <= 0) return MOLE_OK;
+  const int BN = a.Q % 256 == 0 ? 256 : 128;
+  CUtensorMap ma, mb;
+  const uint32_t box[2] = {64, kBK};
+  {
+    const uint64_t dims[2] = {(uint64_t)a.P, (uint64_t)a.total_rows};
+    if (int rc = make_map(&ma, a.A, 2, dims, box)) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)a.Q, (uint64_t)a.total_rows};
+    if (int rc = make_map(&mb, a.B, 2, dims, box)) return rc;
+  }
+  TcParams p{};
+  fill_sched(p, a.sched);
+  p.n_experts = a.n_experts;
+  p.e_begin = a.e_begin;
+  p.N = a.Q;
+  p.K = 0;
+  p.P = a.P;
+  p.epi = EPI_WGRAD;
+  p.accumulate = a.accumulate;
+  p.out0 = static_cast<__nv_bfloat16*>(a.out);
+  p.fault = device_fault_word();
+  p.slot = a.gslot;
+  const int max_items = a.n_experts * (a.P / kBM) * (a.Q / BN);
+  return BN == 256 ? launch_tc<TC_WGRAD, true, 256>(ma, mb, p, max_items, st)
+                   : launch_tc<TC_WGRAD, true, 128>(ma, mb, p, max_items, st);
+}
+
+}  // namespace mole

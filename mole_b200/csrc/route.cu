@@ -1,0 +1,556 @@
+// (a) Gate and routing-index build.
+//
+// gate_topk_kernel     x @ Wg^T (+bias) -> softmax -> top-k, per-block expert histograms and
+//                      per-block partial score sums.  Replaces MOLETopk.forward
+//                      (MOLE/utils/Ugate.py:11-14) and the selection half of the
+//                      extract_critical call (MOLE/moe/layer.py:445-447).
+// route_scan_kernel    ordered exclusive scan of the histograms over (choice, token block):
+//                      slot bases, counts = min(hist, C), offsets, first-choice histogram, l_aux.
+// route_slot_kernel    slot of every (token, choice) pair, kept mask folded into the gate
+//                      weights, token permutation.
+// gate_bwd_kernel      dlogits from d(gates) and d(l_aux).
+// gate_wgrad_kernel    dWg += dlogits^T @ x (split over tokens, fp32 atomics).
+//
+// All integer outputs are produced by integer arithmetic in a fixed order: no atomics decide
+// a slot, so the result is a pure function of the scores.
+#include "common.cuh"
+
+namespace mole {
+
+constexpr int kGateTok = 64;     // tokens per block in every routing kernel
+constexpr int kGateKC = 32;      // K chunk of the gate GEMM
+constexpr int kGateThreads = 256;
+constexpr int kMaxExperts = 256;
+constexpr int kMaxTopK = 8;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Second half of the gate kernel, also used on caller-provided scores.
+// ls: [kGateTok][E + 1] fp32 in shared memory holding logits (softmax_needed) or scores.
+__device__ void softmax_topk_block(float* ls, int* hist_s, int64_t tok0, int64_t T, int E, int k,
+                                   int normalize, bool softmax_needed, float* scores,
+                                   int32_t* idx, float* gates, int32_t* hist, float* me_part,
+                                   int nblk) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ldl = E + 1;
+  for (int i = tid; i < k * E; i += kGateThreads) hist_s[i] = 0;
+  __syncthreads();
+
+  constexpr int kPerLane = kMaxExperts / 32;
+  for (int tt = 0; tt < kGateTok / 8; ++tt) {
+    const int tl = warp * (kGateTok / 8) + tt;
+    const int64_t t = tok0 + tl;
+    if (t >= T) break;           // warp-uniform
+    float v[kPerLane];
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = lane + 32 * j;
+      v[j] = e < E ? ls[tl * ldl + e] : -INFINITY;
+    }
+    if (softmax_needed) {
+      float m = v[0];
+#pragma unroll
+      for (int j = 1; j < kPerLane; ++j) m = fmaxf(m, v[j]);
+      m = warp_max(m);
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {
+        v[j] = (lane + 32 * j) < E ? expf(v[j] - m) : 0.f;
+        s += v[j];
+      }
+      s = warp_sum(s);
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = v[j] / s;
+        if (e < E) {
+          ls[tl * ldl + e] = v[j];
+          scores[t * E + e] = v[j];
+        } else {
+          v[j] = -INFINITY;
+        }
+      }
+    }
+    // top-k on the scores: largest value, ties to the lower expert id
+    float gsel[kMaxTopK];
+    int esel[kMaxTopK];
+    float gsum = 0.f;
+    for (int c = 0; c < k; ++c) {
+      float bv = -INFINITY;
+      int be = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {      // ascending e: strict > keeps the lower id
+        if (v[j] > bv) { bv = v[j]; be = lane + 32 * j; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+      }
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j)
+        if (lane + 32 * j == be) v[j] = -INFINITY;
+      gsel[c] = bv;
+      esel[c] = be;
+      gsum += bv;
+    }
+    if (lane == 0) {
+      const float inv = normalize ? 1.0f / fmaxf(gsum, 1e-9f) : 1.0f;
+      for (int c = 0; c < k; ++c) {
+        idx[t * k + c] = esel[c];
+        gates[t * k + c] = normalize ? gsel[c] * inv : gsel[c];
+        atomicAdd(&hist_s[c * E + esel[c]], 1);
+      }
+    }
+  }
+  __syncthreads();
+  const int blk = blockIdx.x;
+  for (int i = tid; i < k * E; i += kGateThreads) {
+    const int c = i / E, e = i - c * E;
+    hist[((int64_t)c * nblk + blk) * E + e] = hist_s[i];
+  }
+  const int nvalid = (int)min((int64_t)kGateTok, T - tok0);
+  for (int e = tid; e < E; e += kGateThreads) {
+    float s = 0.f;
+    for (int tl = 0; tl < nvalid; ++tl) s += ls[tl * ldl + e];
+    me_part[(int64_t)blk * E + e] = s;
+  }
+}
+
+template <typename T, int EJ>
+__global__ void __launch_bounds__(kGateThreads)
+gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float* __restrict__ bias,
+                 int64_t Ttok, int M, int E, int k, int normalize, float* __restrict__ scores,
+                 int32_t* __restrict__ idx, float* __restrict__ gates, int32_t* __restrict__ hist,
+                 float* __restrict__ me_part, int nblk) {
+  extern __shared__ float smem[];
+  constexpr int LD = kGateKC + 1;
+  float* xs = smem;                              // [64][33]
+  float* ws = smem + kGateTok * LD;              // [EJ*16][33]
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int64_t tok0 = (int64_t)blockIdx.x * kGateTok;
+
+  float acc[4][EJ];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < EJ; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < M; k0 += kGateKC) {
+#pragma unroll
+    for (int r = 0; r < kGateTok * kGateKC / kGateThreads; ++r) {
+      const int i = tid + kGateThreads * r;
+      const int tl = i >> 5, kk = i & 31;
+      const int64_t t = tok0 + tl;
+      float v = 0.f;
+      if (t < Ttok && k0 + kk < M) v = Elem<T>::to_f(x[t * M + k0 + kk]);
+      xs[tl * LD + kk] = v;
+    }
+#pragma unroll
+    for (int r = 0; r < EJ * 16 * kGateKC / kGateThreads; ++r) {
+      const int i = tid + kGateThreads * r;
+      const int e = i >> 5, kk = i & 31;
+      float v = 0.f;
+      if (e < E && k0 + kk < M) v = Elem<T>::to_f(wg[(int64_t)e * M + k0 + kk]);
+      ws[e * LD + kk] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < kGateKC; ++kk) {
+      float a[4], b[EJ];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[(ty * 4 + i) * LD + kk];
+#pragma unroll
+      for (int j = 0; j < EJ; ++j) b[j] = ws[(tx + 16 * j) * LD + kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < EJ; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  // logits tile to shared memory (the operand tiles are dead now)
+  float* ls = smem;
+  const int ldl = E + 1;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < EJ; ++j) {
+      const int e = tx + 16 * j;
+      if (e < E) ls[(ty * 4 + i) * ldl + e] = acc[i][j] + (bias ? bias[e] : 0.f);
+    }
+  int* hist_s = reinterpret_cast<int*>(smem + kGateTok * ldl);
+  __syncthreads();
+  softmax_topk_block(ls, hist_s, tok0, Ttok, E, k, normalize, true, scores, idx, gates, hist,
+                     me_part, nblk);
+}
+
+__global__ void __launch_bounds__(kGateThreads)
+topk_from_scores_kernel(const float* __restrict__ scores, int64_t Ttok, int E, int k,
+                        int normalize, int32_t* __restrict__ idx, float* __restrict__ gates,
+                        int32_t* __restrict__ hist, float* __restrict__ me_part, int nblk) {
+  extern __shared__ float smem[];
+  float* ls = smem;
+  const int ldl = E + 1;
+  const int64_t tok0 = (int64_t)blockIdx.x * kGateTok;
+  for (int i = threadIdx.x; i < kGateTok * E; i += kGateThreads) {
+    const int tl = i / E, e = i - tl * E;
+    const int64_t t = tok0 + tl;
+    ls[tl * ldl + e] = t < Ttok ? scores[t * E + e] : 0.f;
+  }
+  int* hist_s = reinterpret_cast<int*>(smem + kGateTok * ldl);
+  __syncthreads();
+  softmax_topk_block(ls, hist_s, tok0, Ttok, E, k, normalize, false, nullptr, idx, gates, hist,
+                     me_part, nblk);
+}
+
+// One block.  hist [k][nblk][E] is turned in place into the slot base of every
+// (choice, block, expert): all earlier choices of all tokens, then earlier blocks.
+__global__ void __launch_bounds__(kMaxExperts)
+route_scan_kernel(int32_t* __restrict__ hist, const float* __restrict__ me_part, int64_t T,
+                  int E, int k, int C, int nblk, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ offsets, int32_t* __restrict__ first_hist,
+                  float* __restrict__ l_aux) {
+  __shared__ float prod[kMaxExperts];
+  __shared__ int cnt[kMaxExperts];
+  const int e = threadIdx.x;
+  if (e < E) {
+    int running = 0;
+    int first = 0;
+    for (int c = 0; c < k; ++c) {
+      int32_t* h = hist + (int64_t)c * nblk * E + e;
+#pragma unroll 8
+      for (int b = 0; b < nblk; ++b) {
+        const int v = h[(int64_t)b * E];
+        h[(int64_t)b * E] = running;
+        running += v;
+      }
+      if (c == 0) first = running;
+    }
+    float me = 0.f;
+#pragma unroll 8
+    for (int b = 0; b < nblk; ++b) me += me_part[(int64_t)b * E + e];
+    const float fT = (float)T;
+    prod[e] = (me / fT) * ((float)first / fT);
+    cnt[e] = min(running, C);
+    counts[e] = cnt[e];
+    first_hist[e] = first;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    float s = 0.f;
+    for (int i = 0; i < E; ++i) {
+      offsets[i] = off;
+      off += cnt[i];
+      s += prod[i];
+    }
+    offsets[E] = off;
+    *l_aux = (float)E * s;
+  }
+}
+
+__global__ void __launch_bounds__(kGateTok)
+route_slot_kernel(const int32_t* __restrict__ idx, const int32_t* __restrict__ base,
+                  const int32_t* __restrict__ offsets, int64_t T, int E, int k, int C, int nblk,
+                  int32_t* __restrict__ slot, float* __restrict__ gates,
+                  int32_t* __restrict__ perm) {
+  __shared__ int cnt0[kMaxExperts];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t t = (int64_t)blockIdx.x * kGateTok + tid;
+  for (int c = 0; c < k; ++c) {
+    for (int i = tid; i < E; i += kGateTok) cnt0[i] = 0;
+    __syncthreads();
+    const int e = t < T ? idx[t * k + c] : -1 - lane;       // inactive lanes never match
+    const unsigned mask = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(mask & ((1u << lane) - 1u));
+    if (warp == 0 && rank == 0 && e >= 0) cnt0[e] = __popc(mask);
+    __syncthreads();
+    if (t < T) {
+      const int s = base[((int64_t)c * nblk + blockIdx.x) * E + e] + (warp == 1 ? cnt0[e] : 0) + rank;
+      slot[t * k + c] = s;
+      if (s < C) {
+        perm[offsets[e] + s] = (int32_t)(t * k + c);
+      } else {
+        gates[t * k + c] = 0.f;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256)
+gate_bwd_kernel(const float* __restrict__ scores, const int32_t* __restrict__ idx,
+                const int32_t* __restrict__ slot, const float* __restrict__ dgates,
+                const float* __restrict__ d_l_aux, const int32_t* __restrict__ first_hist,
+                int64_t T, int E, int k, int C, int normalize, float* __restrict__ dlogits) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  constexpr int kPerLane = kMaxExperts / 32;
+  const float fT = (float)T;
+  const float coef = d_l_aux ? (*d_l_aux) * (float)E / (fT * fT) : 0.f;
+  float s[kPerLane], ds[kPerLane];
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int e = lane + 32 * j;
+    s[j] = e < E ? scores[t * E + e] : 0.f;
+    ds[j] = e < E ? coef * (float)first_hist[e] : 0.f;
+  }
+  float S = 1.f, a = 0.f;
+  if (normalize) {
+    S = 0.f;
+    for (int c = 0; c < k; ++c) S += scores[t * E + idx[t * k + c]];
+    S = fmaxf(S, 1e-9f);
+    for (int c = 0; c < k; ++c) {
+      const bool kept = slot[t * k + c] < C;
+      if (kept) a += dgates[t * k + c] * scores[t * E + idx[t * k + c]] / S;
+    }
+  }
+  for (int c = 0; c < k; ++c) {
+    const int e = idx[t * k + c];
+    const bool kept = slot[t * k + c] < C;
+    float d = kept ? dgates[t * k + c] : 0.f;
+    if (normalize) d = (d - a) / S;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j)
+      if (lane + 32 * j == e) ds[j] += d;
+  }
+  float inner = 0.f;
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) inner += s[j] * ds[j];
+  inner = warp_sum(inner);
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int e = lane + 32 * j;
+    if (e < E) dlogits[t * E + e] = s[j] * (ds[j] - inner);
+  }
+}
+
+// dWg[e, m] += sum_t dlogits[t, e] * x[t, m].  Block: 128 tokens x 64 columns, all experts.
+constexpr int kWgTok = 128, kWgCols = 64, kWgKC = 32;
+template <typename T, int EJ>
+__global__ void __launch_bounds__(256)
+gate_wgrad_kernel(const float* __restrict__ dlogits, const T* __restrict__ x, int64_t Ttok, int M,
+                  int E, float* __restrict__ dwg) {
+  __shared__ float dl_s[kWgKC][EJ * 16 + 1];
+  __shared__ float x_s[kWgKC][kWgCols + 1];
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;   // ty: expert group, tx: columns
+  const int col0 = blockIdx.x * kWgCols;
+  const int64_t tok0 = (int64_t)blockIdx.y * kWgTok;
+  float acc[EJ][4];
+#pragma unroll
+  for (int j = 0; j < EJ; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+  for (int t0 = 0; t0 < kWgTok; t0 += kWgKC) {
+    for (int i = tid; i < kWgKC * EJ * 16; i += 256) {
+      const int tl = i / (EJ * 16), e = i - tl * (EJ * 16);
+      const int64_t t = tok0 + t0 + tl;
+      dl_s[tl][e] = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
+    }
+    for (int i = tid; i < kWgKC * kWgCols; i += 256) {
+      const int tl = i / kWgCols, c = i - tl * kWgCols;
+      const int64_t t = tok0 + t0 + tl;
+      x_s[tl][c] = (t < Ttok && col0 + c < M) ? Elem<T>::to_f(x[t * M + col0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int tl = 0; tl < kWgKC; ++tl) {
+      float a[EJ], b[4];
+#pragma unroll
+      for (int j = 0; j < EJ; ++j) a[j] = dl_s[tl][ty + 16 * j];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) b[c] = x_s[tl][tx + 16 * c];
+#pragma unroll
+      for (int j = 0; j < EJ; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][c] = fmaf(a[j], b[c], acc[j][c]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < EJ; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int e = ty + 16 * j, m = col0 + tx + 16 * c;
+      if (e < E && m < M) atomicAdd(&dwg[(int64_t)e * M + m], acc[j][c]);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------
+static inline int nblocks(int64_t T) { return (int)((T + kGateTok - 1) / kGateTok); }
+
+static int check_route_args(int64_t T, int E, int k, int C) {
+  MOLE_REQUIRE(T > 0 && T < (int64_t)1 << 30, "T=%lld out of range", (long long)T);
+  MOLE_REQUIRE(E >= 1 && E <= kMaxExperts, "E=%d not in [1,%d]", E, kMaxExperts);
+  MOLE_REQUIRE(k >= 1 && k <= kMaxTopK && k <= E, "k=%d not in [1,min(E,%d)]", k, kMaxTopK);
+  MOLE_REQUIRE(C >= 1, "capacity %d < 1", C);
+  MOLE_REQUIRE(T * k < (int64_t)1 << 31, "T*k overflows int32");
+  return MOLE_OK;
+}
+
+struct RouteWs {
+  int32_t* hist;
+  float* me_part;
+};
+static int64_t route_ws_bytes(int64_t T, int E, int k) {
+  const int64_t nb = nblocks(T);
+  return ((int64_t)k * nb * E + nb * E) * 4;
+}
+static RouteWs carve(void* ws, int64_t T, int E, int k) {
+  const int64_t nb = nblocks(T);
+  RouteWs r;
+  r.hist = static_cast<int32_t*>(ws);
+  r.me_part = reinterpret_cast<float*>(r.hist + (int64_t)k * nb * E);
+  return r;
+}
+
+static int route_tail(RouteWs w, int64_t T, int E, int k, int C, int32_t* idx, int32_t* slot,
+                      float* gates, int32_t* counts, int32_t* offsets, int32_t* perm,
+                      int32_t* first_hist, float* l_aux, cudaStream_t st) {
+  const int nb = nblocks(T);
+  MOLE_CUDA_OK(cudaMemsetAsync(perm, 0xff, (size_t)T * k * 4, st));
+  route_scan_kernel<<<1, kMaxExperts, 0, st>>>(w.hist, w.me_part, T, E, k, C, nb, counts, offsets,
+                                               first_hist, l_aux);
+  MOLE_LAUNCH_OK();
+  route_slot_kernel<<<nb, kGateTok, 0, st>>>(idx, w.hist, offsets, T, E, k, C, nb, slot, gates,
+                                             perm);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+template <typename T, int EJ>
+static int launch_gate(const void* x, const void* wg, const float* bias, int64_t Ttok, int M, int E,
+                       int k, int normalize, float* scores, int32_t* idx, float* gates, RouteWs w,
+                       cudaStream_t st) {
+  const int nb = nblocks(Ttok);
+  const size_t tiles = (size_t)(kGateTok + EJ * 16) * (kGateKC + 1) * 4;
+  const size_t tail = (size_t)kGateTok * (E + 1) * 4 + (size_t)k * E * 4;
+  const size_t smem = tiles > tail ? tiles : tail;
+  auto kern = gate_topk_kernel<T, EJ>;
+  MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<nb, kGateThreads, smem, st>>>(static_cast<const T*>(x), static_cast<const T*>(wg), bias,
+                                       Ttok, M, E, k, normalize, scores, idx, gates, w.hist,
+                                       w.me_part, nb);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+template <typename T>
+static int dispatch_gate(int E, const void* x, const void* wg, const float* bias, int64_t Ttok,
+                         int M, int k, int normalize, float* scores, int32_t* idx, float* gates,
+                         RouteWs w, cudaStream_t st) {
+  const int ej = (E + 15) / 16;
+  if (ej <= 1) return launch_gate<T, 1>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+  if (ej <= 2) return launch_gate<T, 2>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+  if (ej <= 4) return launch_gate<T, 4>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+  if (ej <= 8) return launch_gate<T, 8>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+  return launch_gate<T, 16>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+}
+
+}  // namespace mole
+
+using namespace mole;
+
+extern "C" int mole_route_workspace_bytes(int64_t T, int32_t E, int32_t k, int64_t* bytes) {
+  MOLE_REQUIRE(bytes != nullptr, "bytes is null");
+  if (int rc = check_route_args(T, E, k, 1)) return rc;
+  *bytes = route_ws_bytes(T, E, k);
+  return MOLE_OK;
+}
+
+extern "C" int mole_gate_route_fwd(const void* x, const void* wg, const float* logit_bias,
+                                   int64_t T, int32_t M, int32_t E, int32_t k, int32_t C,
+                                   int32_t normalize_gate, int32_t dtype, float* scores,
+                                   int32_t* idx, int32_t* slot, float* gates, int32_t* counts,
+                                   int32_t* offsets, int32_t* perm, int32_t* first_hist,
+                                   float* l_aux, void* workspace, int64_t workspace_bytes,
+                                   void* stream) {
+  if (int rc = check_route_args(T, E, k, C)) return rc;
+  MOLE_REQUIRE(x && wg && scores && idx && slot && gates && counts && offsets && perm &&
+               first_hist && l_aux && workspace, "null pointer argument");
+  MOLE_REQUIRE(M >= 1, "M=%d", M);
+  MOLE_REQUIRE(workspace_bytes >= route_ws_bytes(T, E, k), "workspace too small: %lld < %lld",
+               (long long)workspace_bytes, (long long)route_ws_bytes(T, E, k));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  RouteWs w = carve(workspace, T, E, k);
+  int rc;
+  if (dtype == MOLE_F32)
+    rc = dispatch_gate<float>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else if (dtype == MOLE_BF16)
+    rc = dispatch_gate<__nv_bfloat16>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else
+    return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
+  if (rc) return rc;
+  return route_tail(w, T, E, k, C, idx, slot, gates, counts, offsets, perm, first_hist, l_aux, st);
+}
+
+extern "C" int mole_route_from_scores(const float* scores, int64_t T, int32_t E, int32_t k,
+                                      int32_t C, int32_t normalize_gate, int32_t* idx,
+                                      int32_t* slot, float* gates, int32_t* counts,
+                                      int32_t* offsets, int32_t* perm, int32_t* first_hist,
+                                      float* l_aux, void* workspace, int64_t workspace_bytes,
+                                      void* stream) {
+  if (int rc = check_route_args(T, E, k, C)) return rc;
+  MOLE_REQUIRE(scores && idx && slot && gates && counts && offsets && perm && first_hist &&
+               l_aux && workspace, "null pointer argument");
+  MOLE_REQUIRE(workspace_bytes >= route_ws_bytes(T, E, k), "workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  RouteWs w = carve(workspace, T, E, k);
+  const int nb = nblocks(T);
+  const size_t smem = (size_t)kGateTok * (E + 1) * 4 + (size_t)k * E * 4;
+  MOLE_CUDA_OK(cudaFuncSetAttribute(topk_from_scores_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  topk_from_scores_kernel<<<nb, kGateThreads, smem, st>>>(scores, T, E, k, normalize_gate, idx,
+                                                          gates, w.hist, w.me_part, nb);
+  MOLE_LAUNCH_OK();
+  return route_tail(w, T, E, k, C, idx, slot, gates, counts, offsets, perm, first_hist, l_aux, st);
+}
+
+extern "C" int mole_gate_bwd(const float* scores, const int32_t* idx, const int32_t* slot,
+                             const float* dgates, const float* d_l_aux,
+                             const int32_t* first_hist, int64_t T, int32_t E, int32_t k, int32_t C,
+                             int32_t normalize_gate, float* dlogits, void* stream) {
+  if (int rc = check_route_args(T, E, k, C)) return rc;
+  MOLE_REQUIRE(scores && idx && slot && dgates && first_hist && dlogits, "null pointer argument");
+  gate_bwd_kernel<<<(unsigned)((T + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      scores, idx, slot, dgates, d_l_aux, first_hist, T, E, k, C, normalize_gate, dlogits);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+template <typename T>
+static int launch_wgrad(const float* dlogits, const void* x, int64_t Ttok, int M, int E, float* dwg,
+                        cudaStream_t st) {
+  dim3 grid((M + kWgCols - 1) / kWgCols, (unsigned)((Ttok + kWgTok - 1) / kWgTok));
+  const int ej = (E + 15) / 16;
+  const T* xp = static_cast<const T*>(x);
+  if (ej <= 1) gate_wgrad_kernel<T, 1><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
+  else if (ej <= 2) gate_wgrad_kernel<T, 2><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
+  else if (ej <= 4) gate_wgrad_kernel<T, 4><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
+  else if (ej <= 8) gate_wgrad_kernel<T, 8><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
+  else gate_wgrad_kernel<T, 16><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+extern "C" int mole_gate_wgrad(const float* dlogits, const void* x, int64_t T, int32_t M,
+                               int32_t E, int32_t dtype, float* dwg32, void* stream) {
+  if (int rc = check_route_args(T, E, 1, 1)) return rc;
+  MOLE_REQUIRE(dlogits && x && dwg32, "null pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MOLE_F32) return launch_wgrad<float>(dlogits, x, T, M, E, dwg32, st);
+  if (dtype == MOLE_BF16) return launch_wgrad<__nv_bfloat16>(dlogits, x, T, M, E, dwg32, st);
+  return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
+}

@@ -1,0 +1,127 @@
+"""Autograd functions of the MoE layer.  Each stage of the reference ``forward``
+(MOLE/moe/layer.py:429-476) is one ``torch.autograd.Function`` over the C ABI:
+
+  GateRoute       gate + extract_critical   (layer.py:442-447)   -> gates, l_aux, routing plan
+  Dispatch        fast_encode               (layer.py:448-449)   -> [E, Cs, M] rows
+  BatchFusedFWD   the expert pipeline       (layer.py:453)       -> [E, Cs, M] rows
+  Combine         fast_decode               (layer.py:456-458)   -> [T, M]
+  pfetchbwd       backward-prefetch trigger (layer.py:435-436)
+
+``BatchFusedFWD`` and ``pfetchbwd`` are used by the reference layer but defined nowhere in its
+tree; they are written here from their call sites and from ``_MOLECore::forward/backward``
+(MOLE/cpp/define.hpp:594-606).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+
+
+class GateRoute(torch.autograd.Function):
+    """``(x, wg) -> (gates [T, k] f32, l_aux [] f32)``; the integer routing plan is returned
+    through ``holder['plan']``."""
+
+    @staticmethod
+    def forward(ctx, x, wg, logit_bias, k, cap, normalize, holder):
+        plan = ops.gate_route(x, wg, k, cap, logit_bias, normalize)
+        holder["plan"] = plan
+        ctx.plan = plan
+        ctx.save_for_backward(x, wg)
+        return plan.gates, plan.l_aux.view(())
+
+    @staticmethod
+    def backward(ctx, dgates, dl_aux):
+        x, wg = ctx.saved_tensors
+        plan = ctx.plan
+        if dgates is None:
+            dgates = torch.zeros_like(plan.gates)
+        dl = None if dl_aux is None else dl_aux.reshape(1).float().contiguous()
+        dlogits = ops.gate_bwd(plan, dgates.contiguous(), dl)
+        dwg = dx = None
+        if ctx.needs_input_grad[1]:
+            dwg = ops.gate_wgrad(dlogits, x).to(wg.dtype)
+        if ctx.needs_input_grad[0]:
+            dx = ops.dispatch_bwd(None, plan, x.shape[1], x.dtype, x.device, dlogits, wg)
+        return dx, dwg, None, None, None, None, None
+
+
+class Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, plan):
+        ctx.plan = plan
+        ctx.meta = (x.shape[1], x.dtype, x.device)
+        return ops.dispatch(x, plan)
+
+    @staticmethod
+    def backward(ctx, ddisp):
+        M, dtype, device = ctx.meta
+        return ops.dispatch_bwd(ddisp.contiguous(), ctx.plan, M, dtype, device), None
+
+
+class Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows, gates, plan):
+        ctx.plan = plan
+        ctx.save_for_backward(rows, gates)
+        return ops.combine(rows, plan, gates)
+
+    @staticmethod
+    def backward(ctx, dy):
+        rows, gates = ctx.saved_tensors
+        drows, dgates = ops.combine_bwd(dy.contiguous(), rows, ctx.plan, gates)
+        return drows, dgates, None
+
+
+class BatchFusedFWD(torch.autograd.Function):
+    """``apply(dispatched_input, module, dummy_param, time_it, prefetch)`` as the reference layer
+    calls it.  ``module._route_counts`` (set by the layer) holds the valid rows of every
+    (expert) chunk; without it every chunk is taken as full, which is the reference's
+    capacity-padded computation."""
+
+    @staticmethod
+    def forward(ctx, dispatched_input, module, dummy_param, time_it=False, prefetch=False):
+        core = module.MOLECore
+        counts = getattr(module, "_route_counts", None)
+        E, Cs, M = dispatched_input.shape
+        if counts is None:
+            counts = torch.full((E,), Cs, dtype=torch.int32, device=dispatched_input.device)
+        ctx.core = core
+        ctx.counts = counts
+        ctx.input_requires_grad = dispatched_input.requires_grad
+        ctx.dummy_shape = dummy_param.shape
+        timer = module.timer if time_it and hasattr(module, "timer") else None
+        if timer:
+            timer.start_fwd()
+        out = core.forward(dispatched_input.contiguous(), counts, True)
+        if timer:
+            timer.stop_fwd()
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        dx = ctx.core.backward(grad_out.contiguous(), ctx.counts, ctx.input_requires_grad)
+        dummy_grad = torch.zeros(ctx.dummy_shape, device=grad_out.device, dtype=grad_out.dtype)
+        return dx, None, dummy_grad, None, None
+
+
+class pfetchbwd(torch.autograd.Function):
+    """Identity in forward; in backward (which runs after the layer's own backward) it starts the
+    host-to-device prefetch for the previous layer's backward, mirroring how forward prefetches
+    the next layer (MOLE/moe/layer.py:464-472)."""
+
+    @staticmethod
+    def forward(ctx, input_, module):
+        ctx.module = module
+        return input_.view_as(input_)
+
+    @staticmethod
+    def backward(ctx, grad):
+        m = ctx.module
+        inst = type(m)._instance
+        if m.moe_id > 0:
+            prev = inst[m.moe_id - 1]
+            if m.global_prefetch:
+                prev.global_prefetch_bwd()
+            prev.local_prefetch_bwd()
+        return grad, None
