@@ -57,6 +57,15 @@ int64_t mole_capacity_stride(int64_t capacity);
  * out; *fault == 0 means none.  Synchronises `stream`. */
 int mole_device_fault(void* stream, int32_t* fault);
 
+/* kernels this library has launched in this process (the benchmark reports it) */
+int mole_launch_count(int64_t* n);
+/* while enabled every tensor-core grouped-GEMM launch is bracketed by CUDA events on its own
+ * stream; mole_profile_read waits for them and returns the durations in launch order with
+ * kind 0 = FC1, 1 = FC2, 2 = dX2, 3 = dX, 4 = weight gradient.  No counterpart in the
+ * reference, which times whole phases (MOLE/utils/Utimer.py). */
+int mole_profile_gemm(int32_t enable);
+int mole_profile_read(float* ms, int32_t* kind, int32_t capacity, int32_t* n);
+
 /* ------------------------------------------------------------------------------------
  * (a) gate + routing-index build.
  * Replaces MOLETopk.forward (MOLE/utils/Ugate.py:11-14) and the extract_critical call at

@@ -40,6 +40,9 @@ SIGNATURES = {
     "mole_last_error_string": (C.c_char_p, []),
     "mole_capacity_stride": (_i64, [_i64]),
     "mole_device_fault": (C.c_int, [_p, _pi32]),
+    "mole_launch_count": (C.c_int, [_pi64]),
+    "mole_profile_gemm": (C.c_int, [_i32]),
+    "mole_profile_read": (C.c_int, [C.POINTER(C.c_float), _pi32, _i32, _pi32]),
     "mole_route_workspace_bytes": (C.c_int, [_i64, _i32, _i32, _pi64]),
     "mole_gate_route_fwd": (C.c_int, [_p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
                                       _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _p]),
@@ -88,7 +91,7 @@ def _load() -> C.CDLL:
         raise ImportError(
             f"{LIB_PATH} is missing: the CUDA library is the only implementation of this "
             "package (there is no CPU or PyTorch fallback).  Build it with "
-            "`python -m mole_b200.build` (needs nvcc).")
+            "`python mole_b200/build.py` (needs nvcc).")
     lib = C.CDLL(str(LIB_PATH))
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)          # AttributeError if the library lacks a declared symbol

@@ -1,6 +1,7 @@
 """Builds ``libmole_b200.so`` in-tree with nvcc for sm_100a.
 
-Run as ``python -m mole_b200.build`` (add ``-v`` for ptxas resource usage).  The library is
+Run as ``python mole_b200/build.py`` (add ``-v`` for ptxas resource usage); it is loaded by path,
+not through the package, because importing the package needs the library it builds.  The library is
 a plain C-ABI shared object: no torch headers, no pybind.
 """
 from __future__ import annotations
@@ -45,7 +46,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         return LIB
     nvcc = _nvcc()
     OUT_DIR.mkdir(exist_ok=True)
-    obj_dir = HERE / "build"
+    obj_dir = HERE / "_obj"
     obj_dir.mkdir(exist_ok=True)
     common = [nvcc, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", *_nccl_include()]

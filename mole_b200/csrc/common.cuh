@@ -36,7 +36,18 @@ inline int fail(int code, const char* fmt, ...) {
     if (!(cond)) return ::mole::fail(MOLE_ERR_INVALID, __VA_ARGS__);  \
   } while (0)
 
-#define MOLE_LAUNCH_OK()  MOLE_CUDA_OK(cudaGetLastError())
+// after every kernel launch: counts it (mole_launch_count) and surfaces launch errors
+void count_launch();
+#define MOLE_LAUNCH_OK()          \
+  do {                            \
+    ::mole::count_launch();       \
+    MOLE_CUDA_OK(cudaGetLastError()); \
+  } while (0)
+
+// optional per-launch timing of the grouped GEMMs (mole_profile_gemm / mole_profile_read)
+bool profile_enabled();
+void profile_begin(cudaStream_t st, int kind);
+void profile_end(cudaStream_t st);
 
 // device-side fault word: kernels with bounded waits record where they gave up
 int32_t* device_fault_word();   // lazily allocated once per process (4 bytes), zeroed

@@ -508,7 +508,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   int grid = sm_count();
   if (max_items < grid) grid = max_items;
   if (grid <= 0) return MOLE_OK;
+  if (profile_enabled()) profile_begin(st, p.epi);
   kern<<<grid, kThreads, smem, st>>>(ma, mb, p);
+  if (profile_enabled()) profile_end(st);
   MOLE_LAUNCH_OK();
   return MOLE_OK;
 }

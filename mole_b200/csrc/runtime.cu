@@ -8,6 +8,8 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <atomic>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -30,9 +32,52 @@ int32_t* device_fault_word() {
   return word;
 }
 
+static std::atomic<int64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+struct ProfileEntry { cudaEvent_t a, b; int kind; };
+static bool g_profile = false;
+static std::vector<ProfileEntry> g_entries;
+bool profile_enabled() { return g_profile; }
+void profile_begin(cudaStream_t st, int kind) {
+  ProfileEntry e;
+  e.kind = kind;
+  if (cudaEventCreate(&e.a) != cudaSuccess || cudaEventCreate(&e.b) != cudaSuccess) return;
+  cudaEventRecord(e.a, st);
+  g_entries.push_back(e);
+}
+void profile_end(cudaStream_t st) {
+  if (!g_entries.empty()) cudaEventRecord(g_entries.back().b, st);
+}
+
 }  // namespace mole
 
 using namespace mole;
+
+extern "C" int mole_launch_count(int64_t* n) {
+  MOLE_REQUIRE(n != nullptr, "n is null");
+  *n = g_launches.load();
+  return MOLE_OK;
+}
+extern "C" int mole_profile_gemm(int32_t enable) {
+  g_profile = enable != 0;
+  return MOLE_OK;
+}
+extern "C" int mole_profile_read(float* ms, int32_t* kind, int32_t capacity, int32_t* n) {
+  MOLE_REQUIRE(n != nullptr, "n is null");
+  *n = (int)g_entries.size();
+  for (size_t i = 0; i < g_entries.size(); ++i) {
+    ProfileEntry& e = g_entries[i];
+    float t = 0.f;
+    MOLE_CUDA_OK(cudaEventSynchronize(e.b));
+    MOLE_CUDA_OK(cudaEventElapsedTime(&t, e.a, e.b));
+    if (ms && kind && (int)i < capacity) { ms[i] = t; kind[i] = e.kind; }
+    cudaEventDestroy(e.a);
+    cudaEventDestroy(e.b);
+  }
+  g_entries.clear();
+  return MOLE_OK;
+}
 
 extern "C" int mole_version(void) { return 100; }
 extern "C" const char* mole_last_error_string(void) { return last_error_buffer(); }

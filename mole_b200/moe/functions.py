@@ -88,7 +88,7 @@ class BatchFusedFWD(torch.autograd.Function):
             counts = torch.full((E,), Cs, dtype=torch.int32, device=dispatched_input.device)
         ctx.core = core
         ctx.counts = counts
-        ctx.input_requires_grad = dispatched_input.requires_grad
+        ctx.input_requires_grad = ctx.needs_input_grad[0]
         ctx.dummy_shape = dummy_param.shape
         timer = module.timer if time_it and hasattr(module, "timer") else None
         if timer:

@@ -21,6 +21,7 @@ from .. import core, ops
 from ..core import MOLECore
 from ..utils import Ugate
 from ..utils.Uact import build_activation_fwd
+from ..utils.Udist import MOLEDist
 from ..utils.Uparam import CPUHostBatchedParameter, GPUHostBatchedParameter, UnifiedCPUTensor
 from ..utils.Utimer import UATimer
 from .functions import BatchFusedFWD, Combine, Dispatch, GateRoute, pfetchbwd
@@ -52,6 +53,7 @@ class MOLEModule(torch.nn.Module):
         self.world_size = dist["world_size"]
         self.rank = dist["rank"]
         self.device = torch.device(f"cuda:{self.local_rank}")
+        MOLEDist(local_rank=self.local_rank)      # the expert-parallel communicator (singleton)
 
         assert total_d_experts % self.world_size == 0
         assert total_s_experts % self.world_size == 0

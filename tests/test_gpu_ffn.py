@@ -1,0 +1,179 @@
+"""(c) Grouped expert FFN on capacity-strided rows against the oracle's ``expert_ffn``
+(forward, and backward through autograd).  fp32 runs on the CUDA-core kernels (rtol 1e-5),
+bf16 on the tcgen05 kernels (rtol 1e-2) and, to bisect, on the CUDA-core kernels too."""
+import pytest
+import torch
+
+from oracle import moe_ref as O
+from util import assert_close, rel_fro
+
+pytestmark = pytest.mark.gpu
+
+
+class Case:
+    def __init__(self, M, F, L, n_src, Cs, counts, dtype, seed=0, bias=True, act="gelu"):
+        g = torch.Generator().manual_seed(seed)
+        self.M, self.F, self.L, self.n_src, self.Cs, self.dtype, self.act = M, F, L, n_src, Cs, dtype, act
+        self.counts = torch.tensor(counts, dtype=torch.int32).view(n_src, L)
+        self.w1 = (torch.randn(L, F, M, generator=g) * 0.05).to(dtype)
+        self.w2 = (torch.randn(L, F, M, generator=g) * 0.05).to(dtype)
+        self.b1 = (torch.randn(L, F, generator=g) * (0.1 if bias else 0)).to(dtype)
+        self.b2 = (torch.randn(L, M, generator=g) * (0.1 if bias else 0)).to(dtype)
+        rows = n_src * L * Cs
+        # valid rows random, pad rows of each 128-row tile zero, everything beyond NaN
+        self.x = torch.full((n_src, L, Cs, M), float("nan")).to(dtype)
+        self.dout = torch.full((n_src, L, Cs, M), float("nan")).to(dtype)
+        for w in range(n_src):
+            for l in range(L):
+                c = int(self.counts[w, l])
+                pad = (c + 127) // 128 * 128
+                self.x[w, l, :pad] = 0
+                self.dout[w, l, :pad] = 0
+                self.x[w, l, :c] = torch.randn(c, M, generator=g).to(dtype)
+                self.dout[w, l, :c] = torch.randn(c, M, generator=g).to(dtype)
+
+    def expert_rows(self, t, l):
+        return torch.cat([t[w, l, :int(self.counts[w, l])] for w in range(self.n_src)], 0)
+
+    def oracle(self, l):
+        """Forward and backward of local expert l on its valid rows, fp32 math."""
+        x = self.expert_rows(self.x, l).float().requires_grad_(True)
+        ws = [t[l:l + 1].float().clone().requires_grad_(True) for t in (self.w1, self.b1, self.w2, self.b2)]
+        out = O.expert_ffn(x.unsqueeze(0), *ws, act=self.act)
+        out.backward(self.expert_rows(self.dout, l).float().unsqueeze(0))
+        return out.detach()[0], x.grad, [w.grad[0] for w in ws]
+
+
+def run_gpu(case, e_begin=0, e_end=None, backend=0, accumulate=False, slots=None, grads=None):
+    from mole_b200 import ops
+    c = case
+    e_end = c.L if e_end is None else e_end
+    dev = torch.device("cuda")
+    n_slots = c.L if slots is None else max(slots) + 1
+    desc = ops.make_ffn_desc(c.dtype, c.act, "exact", c.M, c.F, c.L, c.n_src, c.Cs, e_begin, e_end,
+                             n_slots, accumulate, backend)
+    ws = ops.ffn_workspace(desc, dev)
+    rows = c.n_src * c.L * c.Cs
+    x = c.x.view(rows, c.M).cuda()
+    dout = c.dout.view(rows, c.M).cuda()
+    w1, b1, w2, b2 = (t.cuda() for t in (c.w1, c.b1, c.w2, c.b2))
+    if slots is not None:      # scatter the weights into their slots
+        def place(t):
+            o = torch.zeros(n_slots, *t.shape[1:], dtype=t.dtype, device=dev)
+            for l, s in enumerate(slots):
+                o[s] = t[l]
+            return o
+        w1, b1, w2, b2 = (place(t) for t in (w1, b1, w2, b2))
+    nan = float("nan")
+    x1 = torch.full((rows, c.F), nan, dtype=c.dtype, device=dev)
+    h = torch.full((rows, c.F), nan, dtype=c.dtype, device=dev)
+    out = torch.full((rows, c.M), nan, dtype=c.dtype, device=dev)
+    counts = c.counts.flatten().cuda()
+    ops.ffn_fwd(desc, counts, x, w1, b1, w2, b2, x1, h, out, ws, slots)
+    dx1 = torch.full((rows, c.F), nan, dtype=c.dtype, device=dev)
+    dx = torch.full((rows, c.M), nan, dtype=c.dtype, device=dev)
+    if grads is None:
+        grads = [torch.full_like(t, nan) for t in (w1, b1, w2, b2)]
+    ops.ffn_bwd(desc, counts, dout, x, x1, h, w1, w2, dx1, dx, grads[0], grads[1], grads[2],
+                grads[3], ws, slots, slots)
+    assert ops.device_fault() == 0
+    torch.cuda.synchronize()
+    shape = (c.n_src, c.L, c.Cs)
+    return out.view(*shape, c.M).cpu(), dx.view(*shape, c.M).cpu(), [g.cpu() for g in grads]
+
+
+def check(case, out, dx, grads, experts, slots=None, wscale=1.0):
+    names = ("gW1", "gb1", "gW2", "gb2")
+    for l in experts:
+        o_ref, dx_ref, g_ref = case.oracle(l)
+        n = o_ref.shape[0]
+        s = l if slots is None else slots[l]
+        if n:
+            assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out, expert {l}")
+            assert_close(case.expert_rows(dx, l), dx_ref, case.dtype, f"dx, expert {l}")
+        for name, got, ref in zip(names, grads, g_ref):
+            if n == 0:
+                assert (got[s] == 0).all(), f"{name}, empty expert {l}: gradient must be zero"
+            else:
+                assert_close(got[s], ref, case.dtype, f"{name}, expert {l}", scale=wscale)
+
+
+RAGGED = [0, 1, 127, 128, 129, 200, 256, 5]
+
+
+def test_ffn_fp32_cuda_cores():
+    case = Case(M=128, F=256, L=8, n_src=1, Cs=256, counts=RAGGED, dtype=torch.float32)
+    out, dx, grads = run_gpu(case)
+    check(case, out, dx, grads, range(8), wscale=4.0)
+
+
+def test_ffn_fp32_two_sources_and_relu():
+    counts = [3, 130, 0, 64, 128, 0, 0, 17]        # [n_src=2][L=4]; expert 2 is empty everywhere
+    case = Case(M=64, F=192, L=4, n_src=2, Cs=256, counts=counts, dtype=torch.float32, act="relu")
+    out, dx, grads = run_gpu(case)
+    check(case, out, dx, grads, range(4), wscale=4.0)
+
+
+@pytest.mark.parametrize("backend", [1, 0], ids=["cuda_cores", "tcgen05"])
+def test_ffn_bf16(backend):
+    case = Case(M=256, F=512, L=8, n_src=1, Cs=256, counts=RAGGED, dtype=torch.bfloat16, seed=1)
+    out, dx, grads = run_gpu(case, backend=backend)
+    check(case, out, dx, grads, range(8))
+
+
+def test_ffn_bf16_tcgen05_narrow_tiles_two_sources():
+    # M = 128 exercises the 128-column tile variant; two source ranks per expert
+    counts = [100, 0, 256, 1, 0, 0, 130, 128]
+    case = Case(M=128, F=384, L=4, n_src=2, Cs=256, counts=counts, dtype=torch.bfloat16, seed=2)
+    out, dx, grads = run_gpu(case)
+    check(case, out, dx, grads, range(4))
+
+
+def test_ffn_bf16_expert_range_slots_and_accumulate():
+    """A record of experts [2, 5) with weights living in permuted slots and gradients
+    accumulated onto existing values (the offload pipeline's way of calling the FFN)."""
+    from mole_b200 import ops
+    case = Case(M=256, F=256, L=6, n_src=1, Cs=128, counts=[5, 9, 100, 128, 64, 3],
+                dtype=torch.bfloat16, seed=3)
+    slots = [7, 6, 3, 0, 5, 1]
+    base = [torch.full((8, 256, 256), 0.5), torch.full((8, 256), 0.5),
+            torch.full((8, 256, 256), 0.5), torch.full((8, 256), 0.5)]
+    grads = [b.bfloat16().cuda() for b in base]
+    out, dx, grads = run_gpu(case, e_begin=2, e_end=5, accumulate=True, slots=slots, grads=grads)
+    for l in (2, 3, 4):
+        o_ref, dx_ref, g_ref = case.oracle(l)
+        assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
+        assert_close(case.expert_rows(dx, l), dx_ref, case.dtype, f"dx {l}")
+        for got, ref in zip(grads, g_ref):
+            assert_close(got[slots[l]], ref + 0.5, case.dtype, f"accumulated grad {l}")
+    for l in (0, 1, 5):        # untouched experts: outputs never written, gradients unchanged
+        assert torch.isnan(out[0, l].float()).all()
+        for got in grads:
+            assert (got[slots[l]] == 0.5).all()
+
+
+def test_ffn_bf16_full_size_spot_check():
+    """Benchmark shape (64 experts, M = 1024, F = 4096, ~512 rows per expert): the tcgen05 path
+    against the oracle on a sample of rows, and against the CUDA-core path through the Frobenius
+    norm of every output."""
+    g = torch.Generator().manual_seed(5)
+    L, M, F, Cs = 64, 1024, 4096, 640
+    counts = torch.randint(400, 641, (L,), generator=g).tolist()
+    counts[3], counts[10] = 0, 640
+    case = Case(M, F, L, 1, Cs, counts, torch.bfloat16, seed=6)
+    out, dx, grads = run_gpu(case)
+    out2, dx2, grads2 = run_gpu(case, backend=1)
+    valid = torch.zeros(1, L, Cs, dtype=torch.bool)
+    for l in range(L):
+        valid[0, l, :counts[l]] = True
+    assert rel_fro(out[valid], out2[valid]) < 4e-3
+    assert rel_fro(dx[valid], dx2[valid]) < 4e-3
+    for a, b in zip(grads, grads2):
+        assert rel_fro(a, b) < 4e-3
+    for l in (0, 10, 37):
+        o_ref, dx_ref, g_ref = case.oracle(l)
+        assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
+        assert_close(case.expert_rows(dx, l), dx_ref, case.dtype, f"dx {l}")
+        for got, ref in zip(grads, g_ref):
+            assert_close(got[l], ref, case.dtype, f"grad {l}")
+    assert (grads[0][3] == 0).all() and (grads[2][3] == 0).all()

@@ -1,0 +1,154 @@
+"""The whole layer (``MOLEModule`` forward + backward through the C ABI) against the oracle."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_ref as O
+from util import assert_close
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+DIST1 = {"local_rank": 0, "world_size": 1, "rank": 0}
+
+
+def build_module(inp, E, M, F, k, dtype, d_experts=0, pool_size=-1, ebatch=64, **kw):
+    from mole_b200 import MOLEModule
+    m = MOLEModule(d_experts, E - d_experts, M, F, pool_size, k, ebatch, DIST1, "gelu", 1, False,
+                   pool_size != -1, dtype=dtype, **kw)
+    state = {"gate": [inp["wg"], None],
+             "experts": [[inp["w1"][e], inp["b1"][e], inp["w2"][e], inp["b2"][e]] for e in range(E)]}
+    m.set_layer_state(state, grad=False)
+    return m
+
+
+def run_module(m, inp, cf, dtype, l_aux_weight=0.0):
+    x = inp["x"].to(dtype).cuda().requires_grad_(True)
+    y = m(x, capacity_factor=cf)
+    loss = (y.float() * inp["gy"].cuda()).sum() + l_aux_weight * m.l_aux
+    loss.backward()
+    torch.cuda.synchronize()
+    return x, y
+
+
+def run_oracle(inp, k, cf, dtype, scores=None, l_aux_weight=0.0):
+    rd = lambda t: t.to(dtype).float()      # the oracle sees the values the GPU sees
+    x = rd(inp["x"]).requires_grad_(True)
+    ws = [rd(inp[n]).requires_grad_(True) for n in ("wg", "w1", "b1", "w2", "b2")]
+    if scores is None:
+        out = O.moe_layer(x, *ws, k=k, capacity_factor=cf)
+    else:
+        # routing decisions from the GPU's scores (rounding-level ties), gate values and their
+        # gradient from the oracle's own
+        own = O.gate_scores(x, ws[0])
+        r = O.route(scores, k, cf)
+        g = torch.gather(own, 1, r.idx.long()) * r.kept
+        me, ce = own.mean(0), torch.nn.functional.one_hot(r.idx[:, 0].long(), own.shape[1]).float().mean(0)
+        r = O.Routing(r.idx, r.slot, r.kept, g, r.counts, r.offsets, r.perm, r.capacity,
+                      own.shape[1] * (me * ce).sum())
+        E = ws[1].shape[0]
+        y = O.decode(O.expert_ffn(O.encode(x, r, E), *ws[1:]), r)
+        out = O.LayerOut(y, r, own)
+    ((out.y * inp["gy"]).sum() + l_aux_weight * out.routing.l_aux).backward()
+    return x, ws, out
+
+
+def compare(m, x, y, ox, ows, oout, dtype, E):
+    plan = m.last_plan
+    r = oout.routing
+    for name in ("idx", "slot", "counts", "offsets", "perm"):
+        assert torch.equal(getattr(plan, name).cpu(), getattr(r, name)), name
+    assert_close(y, oout.y, dtype, "y")
+    assert_close(x.grad, ox.grad, dtype, "dx")
+    assert_close(m.gate[0].linear.weight.grad, ows[0].grad, dtype, "dWg", scale=4.0)
+    got = [m.FC1_W_GPU.grad_tensors, m.FC1_B_GPU.grad_tensors, m.FC2_W_GPU.grad_tensors,
+           m.FC2_B_GPU.grad_tensors]
+    for name, g, w in zip(("gW1", "gb1", "gW2", "gb2"), got, ows[1:]):
+        assert_close(g, w.grad, dtype, name, scale=4.0 if dtype == torch.float32 else 1.0)
+    torch.testing.assert_close(m.l_aux.detach().cpu(), r.l_aux.detach(), rtol=1e-4, atol=1e-6)
+
+
+def test_layer_fp32_config1_matches_oracle_and_golden():
+    """Benchmark config 1: 4096 x 512, 8 experts, top-2, d_ffn 2048, cf 1.25, fp32, seed 0."""
+    cfg = O.CONFIGS["c1"]
+    inp = O.make_inputs(cfg["T"], cfg["M"], cfg["E"], cfg["F"], cfg["seed"])
+    m = build_module(inp, cfg["E"], cfg["M"], cfg["F"], cfg["k"], torch.float32)
+    x, y = run_module(m, inp, cfg["cf"], torch.float32, l_aux_weight=0.01)
+    ox, ows, oout = run_oracle(inp, cfg["k"], cfg["cf"], torch.float32, l_aux_weight=0.01)
+    compare(m, x, y, ox, ows, oout, torch.float32, cfg["E"])
+    g = np.load(GOLDEN / "c1_routing.npz")
+    assert np.array_equal(m.last_plan.idx.cpu().numpy(), g["idx"].astype(np.int32))
+    assert np.array_equal(m.last_plan.slot.cpu().numpy(), g["slot"].astype(np.int32))
+    assert np.array_equal(m.last_plan.counts.cpu().numpy(), g["counts"])
+    assert float(y.double().sum()) == pytest.approx(float(g["y"]), abs=1e-4 * float(g["y_abs"]))
+
+
+def test_layer_fp32_golden_small_with_drops():
+    g = np.load(GOLDEN / "small.npz")
+    inp = {n: torch.from_numpy(g[n]) for n in ("x", "gy", "wg", "w1", "b1", "w2", "b2")}
+    E, M, F, k = int(g["E"]), int(g["M"]), int(g["F"]), int(g["k"])
+    m = build_module(inp, E, M, F, k, torch.float32)
+    x, y = run_module(m, inp, float(g["cf"]), torch.float32)
+    plan = m.last_plan
+    for name in ("idx", "slot", "counts", "offsets", "perm"):
+        assert np.array_equal(getattr(plan, name).cpu().numpy(), g[name]), name
+    assert_close(y, torch.from_numpy(g["y"]), torch.float32, "y")
+    assert_close(x.grad, torch.from_numpy(g["dx"]), torch.float32, "dx", scale=4.0)
+    assert_close(m.FC1_W_GPU.grad_tensors, torch.from_numpy(g["dw1"]), torch.float32, "gW1", scale=4.0)
+    assert_close(m.FC2_B_GPU.grad_tensors, torch.from_numpy(g["db2"]), torch.float32, "gb2", scale=4.0)
+    assert_close(m.gate[0].linear.weight.grad, torch.from_numpy(g["dwg"]), torch.float32, "dWg", scale=4.0)
+
+
+@pytest.mark.parametrize("backend", [1, 0], ids=["cuda_cores", "tcgen05"])
+@pytest.mark.parametrize("cf", [1.25, 0.5])
+def test_layer_bf16_matches_oracle(backend, cf):
+    T, M, E, F, k = 2048, 256, 16, 512, 2
+    inp = O.make_inputs(T, M, E, F, seed=21)
+    inp["wg"] = inp["wg"] * 5
+    inp["b1"] = torch.randn(E, F, generator=torch.Generator().manual_seed(1)) * 0.05
+    inp["b2"] = torch.randn(E, M, generator=torch.Generator().manual_seed(2)) * 0.05
+    m = build_module(inp, E, M, F, k, torch.bfloat16, ffn_backend=backend)
+    x, y = run_module(m, inp, cf, torch.bfloat16)
+    ox, ows, oout = run_oracle(inp, k, cf, torch.bfloat16, scores=m.last_plan.scores.cpu())
+    compare(m, x, y, ox, ows, oout, torch.bfloat16, E)
+
+
+def test_layer_bf16_skewed_routing():
+    """Zipf-biased gate logits: expert loads from 0 to capacity, heavy drops."""
+    T, M, E, F, k = 4096, 256, 32, 256, 2
+    inp = O.make_inputs(T, M, E, F, seed=2, zipf=1.2)
+    m = build_module(inp, E, M, F, k, torch.bfloat16)
+    m.gate[0].logit_bias = (inp["logit_bias"] * 4).cuda()
+    x, y = run_module(m, inp, 1.25, torch.bfloat16)
+    counts = m.last_plan.counts.cpu()
+    assert counts.max() == m.last_plan.C and counts.min() < 64
+    rd = lambda t: t.bfloat16().float()
+    xo = rd(inp["x"]).requires_grad_(True)
+    ws = [rd(inp[n]).requires_grad_(True) for n in ("wg", "w1", "b1", "w2", "b2")]
+    r = O.route(m.last_plan.scores.cpu(), k, 1.25)
+    for name in ("idx", "slot", "counts", "perm"):
+        assert torch.equal(getattr(m.last_plan, name).cpu(), getattr(r, name)), name
+    yo = O.decode(O.expert_ffn(O.encode(xo, r, E), *ws[1:]), r)
+    assert_close(y, yo, torch.bfloat16, "y")
+
+
+def test_offloaded_experts_match_resident():
+    """Same weights once GPU-resident and once streamed from pinned host memory through a
+    4-slot pool in batches of 2: identical kernels in identical order, so identical bits."""
+    T, M, E, F, k = 1024, 256, 8, 512, 1
+    inp = O.make_inputs(T, M, E, F, seed=8)
+    from mole_b200 import core as mcore
+    res = build_module(inp, E, M, F, k, torch.bfloat16, ebatch=2)
+    x1, y1 = run_module(res, inp, 1.25, torch.bfloat16)
+    mcore.UniMem._instance = None
+    off = build_module(inp, E, M, F, k, torch.bfloat16, d_experts=E, pool_size=4, ebatch=2)
+    off.prefetch_fwd(2)
+    x2, y2 = run_module(off, inp, 1.25, torch.bfloat16)
+    assert torch.equal(y1, y2)
+    assert torch.equal(x1.grad, x2.grad)
+    assert torch.equal(res.FC1_W_GPU.grad_tensors.cpu(), off.FC1_W_CPU.all_tensors.grad_)
+    assert torch.equal(res.FC2_W_GPU.grad_tensors.cpu(), off.FC2_W_CPU.all_tensors.grad_)
+    assert torch.equal(res.FC1_B_GPU.grad_tensors.cpu(), off.FC1_B_CPU.all_tensors.grad_)
+    assert torch.equal(res.FC2_B_GPU.grad_tensors.cpu(), off.FC2_B_CPU.all_tensors.grad_)
+    mcore.UniMem._instance = None
