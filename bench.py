@@ -20,7 +20,6 @@ import ctypes as C
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -72,52 +71,63 @@ def peaks():
 # clocks
 # --------------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and clock-event (throttle) reasons through NVML (read-only) in a thread
+    while the timed region runs."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.sm, self.mask, self.max_mhz, self.error = [], 0, None, None
+        self._stop = threading.Event()
+        self.thread = None
+
+    def _handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+        if not uuid.startswith("GPU-"):
+            uuid = "GPU-" + uuid
+        try:
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid)
+
+    def _run(self, pynvml, h):
+        get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons",
+                              getattr(pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+        while not self._stop.is_set():
+            try:
+                self.sm.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                if get_reasons:
+                    self.mask |= int(get_reasons(h))
+            except Exception as e:          # keep the benchmark running without clock data
+                self.error = repr(e)
+                return
+            time.sleep(self.period)
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            pynvml, h = self._handle()
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._run, args=(pynvml, h), daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception as e:
+            self.error = repr(e)
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line)
-
     def __exit__(self, *exc):
-        if self.proc:
-            self.proc.terminate()
-            self.proc.wait(timeout=5)
+        self._stop.set()
+        if self.thread:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], 0, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            f = [s.strip() for s in line.split(",")]
-            if len(f) < 8:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx = max(mx, float(f[2]))
-            except ValueError:
-                continue
-            for n, v in zip(names, f[4:8]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        busy = [v for v in sm if v > 0]
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(busy)}
+        out = {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+               "reasons": sorted(n for bit, n in self.REASONS.items() if self.mask & bit),
+               "samples": len(self.sm)}
+        if self.error:
+            out["error"] = self.error
+        return out
 
 
 # --------------------------------------------------------------------------------------------

@@ -135,8 +135,10 @@ simt_row_gemm_kernel(const __grid_constant__ RowGemmArgs a) {
       const float bv = bias ? Elem<T>::to_f(bias[n]) : 0.f;
       const float xv = a.epi == EPI_DACT ? Elem<T>::to_f(aux[r * N + n]) : 0.f;
       const EpiOut o = epilogue_apply(a.epi, acc[i][j], bv, xv, a.act, a.gelu_bwd);
-      out0[r * N + n] = Elem<T>::from_f(o.v0);
-      if (a.epi == EPI_FC1) out1[r * N + n] = Elem<T>::from_f(o.v1);
+      const T stored = Elem<T>::from_f(o.v0);
+      out0[r * N + n] = stored;
+      // the activation is taken of the stored (rounded) pre-activation, the value backward sees
+      if (a.epi == EPI_FC1) out1[r * N + n] = Elem<T>::from_f(act_fwd(Elem<T>::to_f(stored), a.act));
     }
   }
 }

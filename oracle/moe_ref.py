@@ -299,3 +299,102 @@ def make_inputs(T: int, M: int, E: int, F: int, seed: int, zipf: float = 0.0,
         ranks = torch.randperm(E, generator=torch.Generator().manual_seed(seed + 99)) + 1
         bias = -zipf * torch.log(ranks.float())
     return dict(x=x, gy=gy, wg=wg, w1=w1, b1=b1, w2=w2, b2=b2, logit_bias=bias)
+
+
+# --------------------------------------------------------------------------- #
+# explicit forward + backward with the layer's storage dtype
+# --------------------------------------------------------------------------- #
+# When the reference's op sequence runs on tensors of dtype D, every at::Tensor it
+# materialises (x1, gelu(x1), the FFN output, the activation gradient, every weight gradient;
+# MOLE/cpp/core.cpp:350-353, 388-412) holds values rounded to D, while each matmul accumulates in
+# fp32.  The functions below restate that: fp32 arithmetic with a rounding to D wherever a
+# tensor is stored.  For D = float32 they coincide with autograd of ``expert_ffn``.
+
+def _act_and_grad(x1: torch.Tensor, act: str, gelu_bwd: str):
+    if act == "relu":
+        return torch.relu(x1), (x1 > 0).to(x1.dtype)
+    h = F.gelu(x1)
+    if gelu_bwd == "tanh":
+        return h, gelu_tanh_derivative(x1)
+    cdf = 0.5 * (1.0 + torch.erf(x1 * 0.7071067811865476))
+    pdf = torch.exp(-0.5 * x1 * x1) * 0.3989422804014327
+    return h, cdf + x1 * pdf
+
+
+def ffn_explicit(x, w1, b1, w2, b2, dout, dtype, act="gelu", gelu_bwd="exact"):
+    """One expert on its rows ``x [n, M]`` with upstream gradient ``dout [n, M]`` (fp32 tensors
+    holding dtype-representable values).  Returns out, dx and the four parameter gradients,
+    following MOLE/cpp/core.cpp:350-353 (forward) and :388-412 (backward)."""
+    rd = (lambda t: t) if dtype == torch.float32 else (lambda t: t.to(dtype).float())
+    x1 = rd(x @ w1.t() + b1)
+    h_full, dact = _act_and_grad(x1, act, gelu_bwd)
+    h = rd(h_full)
+    out = rd(h @ w2 + b2)
+    gw2 = rd(h.t() @ dout)
+    dx1 = rd((dout @ w2.t()) * dact)
+    gb2 = rd(dout.sum(0))
+    gw1 = rd(dx1.t() @ x)
+    gb1 = rd(dx1.sum(0))
+    dx = rd(dx1 @ w1)
+    return dict(out=out, dx=dx, gw1=gw1, gb1=gb1, gw2=gw2, gb2=gb2)
+
+
+def layer_explicit(x, gy, wg, w1, b1, w2, b2, k, capacity_factor, dtype,
+                   scores=None, logit_bias=None, normalize_gate=False, l_aux_weight=0.0,
+                   act="gelu", gelu_bwd="exact"):
+    """Whole layer forward + backward with storage dtype ``dtype``.  All inputs are fp32 tensors
+    holding dtype-representable values.  ``scores`` (optional) supplies the scores the routing
+    *decisions* are taken from (a GPU run's own scores, so that rounding-level ties do not
+    flip choices); gate values and their gradients always come from this function's scores."""
+    rd = (lambda t: t) if dtype == torch.float32 else (lambda t: t.to(dtype).float())
+    T, M = x.shape
+    E = w1.shape[0]
+    xg = x.clone().requires_grad_(True)
+    wgg = wg.clone().requires_grad_(True)
+    own = gate_scores(xg, wgg, logit_bias)
+    r = route(own.detach() if scores is None else scores, k, capacity_factor, normalize_gate)
+    # differentiable gates / l_aux from this function's own scores on the decided routing
+    g = torch.gather(own, 1, r.idx.long())
+    if normalize_gate:
+        g = g / g.sum(dim=1, keepdim=True).clamp_min(1e-9)
+    g = g * r.kept.to(g.dtype)
+    me = own.mean(dim=0)
+    ce = F.one_hot(r.idx[:, 0].long(), E).to(own.dtype).mean(dim=0)
+    l_aux = E * torch.sum(me * ce)
+    C = r.capacity
+    gates = g.detach()
+    disp = encode(x, r, E)                                        # exact copies
+    pair_t = torch.arange(T).view(T, 1).expand(T, k)
+    out = torch.zeros(E, C, M)
+    ddisp = torch.zeros(E, C, M)
+    drows = torch.zeros(E, C, M)
+    grads = dict(gw1=torch.zeros_like(w1), gb1=torch.zeros_like(b1),
+                 gw2=torch.zeros_like(w2), gb2=torch.zeros_like(b2))
+    # combine backward needs the expert outputs, which need the forward of every expert first
+    for e in range(E):
+        n = int(r.counts[e])
+        res = ffn_explicit(disp[e, :n], w1[e], b1[e], w2[e], b2[e], torch.zeros(n, M), dtype, act,
+                           gelu_bwd)
+        out[e, :n] = res["out"]
+    rr = Routing(r.idx, r.slot, r.kept, gates, r.counts, r.offsets, r.perm, C, l_aux.detach())
+    y = rd(decode(out, rr))
+    # backward of combine: drows = g * dy, dgates = <dy, out row>
+    flat = (r.idx.long() * C + r.slot.long()).clamp(max=E * C - 1)
+    rows_of_pair = out.reshape(E * C, M)[flat.view(-1)].view(T, k, M)
+    dgates = (rows_of_pair * gy.unsqueeze(1)).sum(-1) * r.kept
+    kept = r.kept
+    drows.view(E * C, M)[flat[kept]] = rd(gates[kept].unsqueeze(-1) * gy[pair_t[kept]])
+    for e in range(E):
+        n = int(r.counts[e])
+        res = ffn_explicit(disp[e, :n], w1[e], b1[e], w2[e], b2[e], drows[e, :n], dtype, act,
+                           gelu_bwd)
+        ddisp[e, :n] = res["dx"]
+        for name in grads:
+            grads[name][e] = res[name]
+    dx_disp = torch.zeros(T, M)
+    dx_disp.index_add_(0, pair_t[kept], ddisp.view(E * C, M)[flat[kept]])
+    dx_disp = rd(dx_disp)
+    ((g * dgates).sum() + l_aux_weight * l_aux).backward()
+    dx = rd(dx_disp + rd(xg.grad))
+    return dict(y=y, dx=dx, dwg=rd(wgg.grad), routing=rr, scores=own.detach(), dgates=dgates,
+                l_aux=l_aux.detach(), **grads)

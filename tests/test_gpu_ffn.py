@@ -36,12 +36,13 @@ class Case:
         return torch.cat([t[w, l, :int(self.counts[w, l])] for w in range(self.n_src)], 0)
 
     def oracle(self, l):
-        """Forward and backward of local expert l on its valid rows, fp32 math."""
-        x = self.expert_rows(self.x, l).float().requires_grad_(True)
-        ws = [t[l:l + 1].float().clone().requires_grad_(True) for t in (self.w1, self.b1, self.w2, self.b2)]
-        out = O.expert_ffn(x.unsqueeze(0), *ws, act=self.act)
-        out.backward(self.expert_rows(self.dout, l).float().unsqueeze(0))
-        return out.detach()[0], x.grad, [w.grad[0] for w in ws]
+        """Forward and backward of local expert l on its valid rows: fp32 arithmetic, stored
+        tensors rounded to the case's dtype (identity for fp32)."""
+        x = self.expert_rows(self.x, l).float()
+        dout = self.expert_rows(self.dout, l).float()
+        r = O.ffn_explicit(x, self.w1[l].float(), self.b1[l].float(), self.w2[l].float(),
+                           self.b2[l].float(), dout, self.dtype, act=self.act)
+        return r["out"], r["dx"], [r["gw1"], r["gb1"], r["gw2"], r["gb2"]]
 
 
 def run_gpu(case, e_begin=0, e_end=None, backend=0, accumulate=False, slots=None, grads=None):

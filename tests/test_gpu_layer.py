@@ -32,41 +32,28 @@ def run_module(m, inp, cf, dtype, l_aux_weight=0.0):
     return x, y
 
 
-def run_oracle(inp, k, cf, dtype, scores=None, l_aux_weight=0.0):
-    rd = lambda t: t.to(dtype).float()      # the oracle sees the values the GPU sees
-    x = rd(inp["x"]).requires_grad_(True)
-    ws = [rd(inp[n]).requires_grad_(True) for n in ("wg", "w1", "b1", "w2", "b2")]
-    if scores is None:
-        out = O.moe_layer(x, *ws, k=k, capacity_factor=cf)
-    else:
-        # routing decisions from the GPU's scores (rounding-level ties), gate values and their
-        # gradient from the oracle's own
-        own = O.gate_scores(x, ws[0])
-        r = O.route(scores, k, cf)
-        g = torch.gather(own, 1, r.idx.long()) * r.kept
-        me, ce = own.mean(0), torch.nn.functional.one_hot(r.idx[:, 0].long(), own.shape[1]).float().mean(0)
-        r = O.Routing(r.idx, r.slot, r.kept, g, r.counts, r.offsets, r.perm, r.capacity,
-                      own.shape[1] * (me * ce).sum())
-        E = ws[1].shape[0]
-        y = O.decode(O.expert_ffn(O.encode(x, r, E), *ws[1:]), r)
-        out = O.LayerOut(y, r, own)
-    ((out.y * inp["gy"]).sum() + l_aux_weight * out.routing.l_aux).backward()
-    return x, ws, out
+def run_oracle(inp, k, cf, dtype, scores=None, l_aux_weight=0.0, logit_bias=None):
+    """The oracle's explicit forward + backward on the values the GPU sees, with every stored
+    tensor rounded to ``dtype``; routing decisions from the GPU's scores when given."""
+    rd = lambda t: t.to(dtype).float()
+    return O.layer_explicit(rd(inp["x"]), rd(inp["gy"]), rd(inp["wg"]), rd(inp["w1"]), rd(inp["b1"]),
+                            rd(inp["w2"]), rd(inp["b2"]), k, cf, dtype, scores=scores,
+                            logit_bias=logit_bias, l_aux_weight=l_aux_weight)
 
 
-def compare(m, x, y, ox, ows, oout, dtype, E):
+def compare(m, x, y, ref, dtype):
     plan = m.last_plan
-    r = oout.routing
+    r = ref["routing"]
     for name in ("idx", "slot", "counts", "offsets", "perm"):
         assert torch.equal(getattr(plan, name).cpu(), getattr(r, name)), name
-    assert_close(y, oout.y, dtype, "y")
-    assert_close(x.grad, ox.grad, dtype, "dx")
-    assert_close(m.gate[0].linear.weight.grad, ows[0].grad, dtype, "dWg", scale=4.0)
+    assert_close(y, ref["y"], dtype, "y")
+    assert_close(x.grad, ref["dx"], dtype, "dx")
+    assert_close(m.gate[0].linear.weight.grad, ref["dwg"], dtype, "dWg", scale=4.0)
     got = [m.FC1_W_GPU.grad_tensors, m.FC1_B_GPU.grad_tensors, m.FC2_W_GPU.grad_tensors,
            m.FC2_B_GPU.grad_tensors]
-    for name, g, w in zip(("gW1", "gb1", "gW2", "gb2"), got, ows[1:]):
-        assert_close(g, w.grad, dtype, name, scale=4.0 if dtype == torch.float32 else 1.0)
-    torch.testing.assert_close(m.l_aux.detach().cpu(), r.l_aux.detach(), rtol=1e-4, atol=1e-6)
+    for name, g in zip(("gw1", "gb1", "gw2", "gb2"), got):
+        assert_close(g, ref[name], dtype, name, scale=4.0 if dtype == torch.float32 else 1.0)
+    torch.testing.assert_close(m.l_aux.detach().cpu(), ref["l_aux"], rtol=1e-4, atol=1e-6)
 
 
 def test_layer_fp32_config1_matches_oracle_and_golden():
@@ -75,8 +62,8 @@ def test_layer_fp32_config1_matches_oracle_and_golden():
     inp = O.make_inputs(cfg["T"], cfg["M"], cfg["E"], cfg["F"], cfg["seed"])
     m = build_module(inp, cfg["E"], cfg["M"], cfg["F"], cfg["k"], torch.float32)
     x, y = run_module(m, inp, cfg["cf"], torch.float32, l_aux_weight=0.01)
-    ox, ows, oout = run_oracle(inp, cfg["k"], cfg["cf"], torch.float32, l_aux_weight=0.01)
-    compare(m, x, y, ox, ows, oout, torch.float32, cfg["E"])
+    ref = run_oracle(inp, cfg["k"], cfg["cf"], torch.float32, l_aux_weight=0.01)
+    compare(m, x, y, ref, torch.float32)
     g = np.load(GOLDEN / "c1_routing.npz")
     assert np.array_equal(m.last_plan.idx.cpu().numpy(), g["idx"].astype(np.int32))
     assert np.array_equal(m.last_plan.slot.cpu().numpy(), g["slot"].astype(np.int32))
@@ -110,8 +97,8 @@ def test_layer_bf16_matches_oracle(backend, cf):
     inp["b2"] = torch.randn(E, M, generator=torch.Generator().manual_seed(2)) * 0.05
     m = build_module(inp, E, M, F, k, torch.bfloat16, ffn_backend=backend)
     x, y = run_module(m, inp, cf, torch.bfloat16)
-    ox, ows, oout = run_oracle(inp, k, cf, torch.bfloat16, scores=m.last_plan.scores.cpu())
-    compare(m, x, y, ox, ows, oout, torch.bfloat16, E)
+    ref = run_oracle(inp, k, cf, torch.bfloat16, scores=m.last_plan.scores.cpu())
+    compare(m, x, y, ref, torch.bfloat16)
 
 
 def test_layer_bf16_skewed_routing():
@@ -123,14 +110,9 @@ def test_layer_bf16_skewed_routing():
     x, y = run_module(m, inp, 1.25, torch.bfloat16)
     counts = m.last_plan.counts.cpu()
     assert counts.max() == m.last_plan.C and counts.min() < 64
-    rd = lambda t: t.bfloat16().float()
-    xo = rd(inp["x"]).requires_grad_(True)
-    ws = [rd(inp[n]).requires_grad_(True) for n in ("wg", "w1", "b1", "w2", "b2")]
-    r = O.route(m.last_plan.scores.cpu(), k, 1.25)
-    for name in ("idx", "slot", "counts", "perm"):
-        assert torch.equal(getattr(m.last_plan, name).cpu(), getattr(r, name)), name
-    yo = O.decode(O.expert_ffn(O.encode(xo, r, E), *ws[1:]), r)
-    assert_close(y, yo, torch.bfloat16, "y")
+    ref = run_oracle(inp, k, 1.25, torch.bfloat16, scores=m.last_plan.scores.cpu(),
+                     logit_bias=inp["logit_bias"] * 4)
+    compare(m, x, y, ref, torch.bfloat16)
 
 
 def test_offloaded_experts_match_resident():
