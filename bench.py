@@ -152,8 +152,12 @@ def init_weights(m, cfg, rank, L, dtype, device):
             kinds[1].fetch_single(l).zero_()
             kinds[3].fetch_single(l).zero_()
         if cfg.get("zipf"):
+            # Gumbel-max construction: with logit noise of scale beta, P(expert is the top choice) is
+            # proportional to rank^-s when the bias is -s * beta * ln(rank).  The gate's logits
+            # are Gaussian with std 0.02 * sqrt(M); beta is the Gumbel scale of equal variance.
             ranks = torch.randperm(cfg["E"], generator=torch.Generator().manual_seed(cfg["seed"] + 99)) + 1
-            m.gate[0].logit_bias = (-cfg["zipf"] * torch.log(ranks.float())).to(device)
+            beta = 0.02 * (cfg["M"] ** 0.5) * (6 ** 0.5) / 3.141592653589793
+            m.gate[0].logit_bias = (-cfg["zipf"] * beta * torch.log(ranks.float())).to(device)
 
 
 def run_ours(args):

@@ -199,37 +199,46 @@ simt_wgrad_kernel(const __grid_constant__ WgradArgs a) {
     }
 }
 
-// Block: 32 column groups of 4 x 8 row lanes; one expert, 128 columns.
+// Block: 32 column groups of one 16-byte vector x 8 row lanes; one expert, 32 vectors of
+// columns.  Every thread keeps four 16-byte loads in flight.
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __grid_constant__ ColsumArgs a) {
-  __shared__ float red[8][132];
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[8][32 * V + 4];
   const int el = blockIdx.y;
   const int t0 = a.sched.expert_tile_start[el], t1 = a.sched.expert_tile_start[el + 1];
   const int slot = a.gslot.s[a.e_begin + el];
   const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
-  const int col = blockIdx.x * 128 + cg * 4;
+  const int col = (blockIdx.x * 32 + cg) * V;
   const T* A = static_cast<const T*>(a.A);
-  float s[4] = {0.f, 0.f, 0.f, 0.f};
+  float s[V];
+#pragma unroll
+  for (int c = 0; c < V; ++c) s[c] = 0.f;
   if (col < a.N) {
     for (int t = t0; t < t1; ++t) {
-      const int64_t row0 = a.sched.tile_row0[t];
-      for (int r = rl; r < kTileRows; r += 8) {
-        const T* p = A + (row0 + r) * a.N + col;
+      const T* base = A + ((int64_t)a.sched.tile_row0[t] + rl) * a.N + col;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) s[c] += Elem<T>::to_f(p[c]);
+      for (int r0 = 0; r0 < kTileRows; r0 += 32) {          // rows rl + {0, 8, 16, 24} + r0
+        float v[4][V];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) Vec16<T>::load(base + (int64_t)(r0 + 8 * u) * a.N, v[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int c = 0; c < V; ++c) s[c] += v[u][c];
       }
     }
   }
 #pragma unroll
-  for (int c = 0; c < 4; ++c) red[rl][cg * 4 + c] = s[c];
+  for (int c = 0; c < V; ++c) red[rl][cg * V + c] = s[c];
   __syncthreads();
-  if (threadIdx.x < 128) {
-    const int n = blockIdx.x * 128 + threadIdx.x;
+  for (int i = threadIdx.x; i < 32 * V; i += 256) {
+    const int n = blockIdx.x * 32 * V + i;
     if (n < a.N) {
       float v = 0.f;
 #pragma unroll
-      for (int r = 0; r < 8; ++r) v += red[r][threadIdx.x];
+      for (int r = 0; r < 8; ++r) v += red[r][i];
       T* out = static_cast<T*>(a.out) + (int64_t)slot * a.N + n;
       if (a.accumulate) v += Elem<T>::to_f(*out);
       *out = Elem<T>::from_f(v);
@@ -258,9 +267,10 @@ int simt_wgrad(int dtype, const WgradArgs& a, cudaStream_t st) {
 }
 
 int colsum(int dtype, const ColsumArgs& a, cudaStream_t st) {
-  MOLE_REQUIRE(a.N % 4 == 0, "column sums need N %% 4 == 0");
+  const int vec = dtype == MOLE_F32 ? 4 : 8;
+  MOLE_REQUIRE(a.N % vec == 0, "column sums need 16-byte rows");
   if (a.n_experts <= 0) return MOLE_OK;
-  dim3 grid((a.N + 127) / 128, a.n_experts);
+  dim3 grid((a.N + 32 * vec - 1) / (32 * vec), a.n_experts);
   if (dtype == MOLE_F32) colsum_kernel<float><<<grid, 256, 0, st>>>(a);
   else colsum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
   MOLE_LAUNCH_OK();

@@ -143,29 +143,74 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// 32 bf16 = 64 bytes per thread, moved as two 32-byte vectors so that every request covers a
+// whole 32-byte sector
+__device__ __forceinline__ void ld_v8(const void* p, uint32_t (&w)[8]) {
+  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]),
+                 "=r"(w[6]), "=r"(w[7]) : "l"(p));
+}
+__device__ __forceinline__ void st_v8(void* p, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
+                 "r"(w[6]), "r"(w[7]) : "memory");
+}
 __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* p, float (&v)[32]) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint4 t = *reinterpret_cast<const uint4*>(p + 8 * i);
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+  for (int i = 0; i < 2; ++i) {
+    uint32_t w[8];
+    ld_v8(p + 16 * i, w);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
-      v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    for (int j = 0; j < 8; ++j) {
+      v[16 * i + 2 * j] = __uint_as_float(w[j] << 16);
+      v[16 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
     }
   }
 }
 __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* p, const float (&v)[32]) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t w[4];
+  for (int i = 0; i < 2; ++i) {
+    uint32_t w[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __nv_bfloat162 b = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+    for (int j = 0; j < 8; ++j) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(v[16 * i + 2 * j], v[16 * i + 2 * j + 1]);
       w[j] = *reinterpret_cast<uint32_t*>(&b);
     }
-    *reinterpret_cast<uint4*>(p + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+    st_v8(p + 16 * i, w);
   }
+}
+
+// Exact-GELU pieces for the bf16 epilogues.  Phi(x) = 0.5 (1 + erf(x / sqrt 2)) through the
+// rational-exponential form of erfc (Abramowitz & Stegun 7.1.26, |error| < 1.5e-7, far below a
+// bf16 ulp): with z = |x| / sqrt 2 and t = 1 / (1 + p z),
+//   erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-z^2).
+// exp(-z^2) = exp(-x^2 / 2) is also the Gaussian density's exponential, so value and derivative
+// share one ex2 and one rcp.  The fp32 layer keeps erff (CUDA-core path).
+struct GeluParts { float cdf, e; };     // Phi(x) and exp(-x^2 / 2)
+__device__ __forceinline__ GeluParts gelu_parts(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.0f, fmaf(0.3275911f * 0.70710678f, ax, 1.0f));
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * x * -0.72134752f));
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(t, poly, 1.421413741f);
+  poly = fmaf(t, poly, -0.284496736f);
+  poly = fmaf(t, poly, 0.254829592f);
+  const float half_erfc = 0.5f * t * poly * e;          // 0.5 erfc(|x| / sqrt 2)
+  GeluParts g;
+  g.cdf = x >= 0.f ? 1.0f - half_erfc : half_erfc;
+  g.e = e;
+  return g;
+}
+__device__ __forceinline__ float fast_act_fwd(float x, int act) {
+  if (act == MOLE_ACT_RELU) return fmaxf(x, 0.f);
+  return x * gelu_parts(x).cdf;
+}
+__device__ __forceinline__ float fast_act_grad(float x, int act, int gelu_bwd) {
+  if (act == MOLE_ACT_RELU) return x > 0.f ? 1.f : 0.f;
+  if (gelu_bwd == MOLE_GELU_BWD_TANH) return gelu_tanh_grad(x);
+  const GeluParts g = gelu_parts(x);
+  return fmaf(x * 0.39894228f, g.e, g.cdf);
 }
 
 struct TcParams {
@@ -399,7 +444,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // the saved pre-activation is bf16: the activation is taken of the rounded value so
             // that backward's act'(x1) and forward's act(x1) see the same x1
             v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
-            h[i] = act_fwd(v[i], p.act);
+            h[i] = fast_act_fwd(v[i], p.act);
           }
           store_bf16x32(p.out0 + obase + c0, v);
           store_bf16x32(p.out1 + obase + c0, h);
@@ -415,7 +460,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           float x1[32];
           load_bf16x32(p.aux + obase + c0, x1);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= act_grad(x1[i], p.act, p.gelu_bwd);
+          for (int i = 0; i < 32; ++i) v[i] *= fast_act_grad(x1[i], p.act, p.gelu_bwd);
           store_bf16x32(p.out0 + obase + c0, v);
         } else {
           store_bf16x32(p.out0 + obase + c0, v);

@@ -115,15 +115,16 @@ __device__ void softmax_topk_block(float* ls, int* hist_s, int64_t tok0, int64_t
   }
   __syncthreads();
   const int blk = blockIdx.x;
+  // expert-major layouts: the scan kernel reads one expert's (choice, block) sequence contiguously
   for (int i = tid; i < k * E; i += kGateThreads) {
     const int c = i / E, e = i - c * E;
-    hist[((int64_t)c * nblk + blk) * E + e] = hist_s[i];
+    hist[((int64_t)e * k + c) * nblk + blk] = hist_s[i];
   }
   const int nvalid = (int)min((int64_t)kGateTok, T - tok0);
   for (int e = tid; e < E; e += kGateThreads) {
     float s = 0.f;
     for (int tl = 0; tl < nvalid; ++tl) s += ls[tl * ldl + e];
-    me_part[(int64_t)blk * E + e] = s;
+    me_part[(int64_t)e * nblk + blk] = s;
   }
 }
 
@@ -195,6 +196,119 @@ gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float*
                      me_part, nblk);
 }
 
+// ---- bf16 gate on the warp-level tensor-core path ------------------------------------------
+// The gate product is [T, M] x [M, E] with E <= 256: far too small for a tcgen05 tile pipeline to
+// pay off, but on CUDA cores it is FMA-bound at ~3 % of the HBM rate it should run at.  Warp-level
+// mma.sync (m16n8k16, bf16 in, fp32 accumulate in the hardware's fixed order) brings it to the
+// memory roofline: the kernel streams x once through a two-stage cp.async ring.
+// Block: 8 warps, 64 tokens; warp w owns tokens 16 * (w & 3) .. +15 and half of the experts.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+               ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(const void* p, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kMmaKC = 64;            // K elements per stage
+constexpr int kMmaLds = kMmaKC + 8;   // padded row (144 bytes): conflict-free ldmatrix
+
+template <int NT>                     // expert tiles of 8: experts padded to NT * 8 >= 32
+__global__ void __launch_bounds__(kGateThreads)
+gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg,
+                     const float* __restrict__ bias, int64_t Ttok, int M, int E, int k,
+                     int normalize, float* __restrict__ scores, int32_t* __restrict__ idx,
+                     float* __restrict__ gates, int32_t* __restrict__ hist,
+                     float* __restrict__ me_part, int nblk) {
+  extern __shared__ float smem[];
+  constexpr int EP = NT * 8, NTW = NT / 2;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);          // [2][64][72]
+  __nv_bfloat16* wsm = xs + 2 * kGateTok * kMmaLds;                    // [2][EP][72]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int mt = warp & 3, nh = warp >> 2;
+  const int64_t tok0 = (int64_t)blockIdx.x * kGateTok;
+
+  auto load_chunk = [&](int c, int st) {
+    for (int i = tid; i < kGateTok * 8; i += kGateThreads) {
+      const int r = i >> 3, v = i & 7;
+      const int64_t t = tok0 + r;
+      const bool ok = t < Ttok;
+      cp_async16(xs + (st * kGateTok + r) * kMmaLds + v * 8,
+                 x + (ok ? t : 0) * M + c * kMmaKC + v * 8, ok ? 16 : 0);
+    }
+    for (int i = tid; i < EP * 8; i += kGateThreads) {
+      const int r = i >> 3, v = i & 7;
+      const bool ok = r < E;
+      cp_async16(wsm + (st * EP + r) * kMmaLds + v * 8,
+                 wg + (int64_t)(ok ? r : 0) * M + c * kMmaKC + v * 8, ok ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float acc[NTW][4];
+#pragma unroll
+  for (int i = 0; i < NTW; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  const int nchunks = M / kMmaKC;
+  load_chunk(0, 0);
+  for (int c = 0; c < nchunks; ++c) {
+    const int st = c & 1;
+    if (c + 1 < nchunks) {
+      load_chunk(c + 1, st ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __nv_bfloat16* xa = xs + st * kGateTok * kMmaLds;
+    const __nv_bfloat16* wb = wsm + st * EP * kMmaLds;
+#pragma unroll
+    for (int ks = 0; ks < kMmaKC / 16; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(xa + (mt * 16 + (lane & 15)) * kMmaLds + ks * 16 + (lane >> 4) * 8, a);
+#pragma unroll
+      for (int p = 0; p < NTW / 2; ++p) {
+        const int n0 = (nh * NTW + 2 * p) * 8;
+        uint32_t b[4];
+        ldmatrix_x4(wb + (n0 + (lane & 7) + ((lane >> 4) << 3)) * kMmaLds + ks * 16 +
+                        ((lane >> 3) & 1) * 8, b);
+        mma_bf16_16816(acc[2 * p], a, b[0], b[1]);
+        mma_bf16_16816(acc[2 * p + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  // logits tile to shared memory (operand stages are dead after the last barrier)
+  float* ls = smem;
+  const int ldl = E + 1;
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int i = 0; i < NTW; ++i) {
+    const int e0 = (nh * NTW + i) * 8 + 2 * q;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = e0 + (j & 1), row = mt * 16 + g + (j >> 1) * 8;
+      if (e < E) ls[row * ldl + e] = acc[i][j] + (bias ? bias[e] : 0.f);
+    }
+  }
+  int* hist_s = reinterpret_cast<int*>(smem + kGateTok * ldl);
+  __syncthreads();
+  softmax_topk_block(ls, hist_s, tok0, Ttok, E, k, normalize, true, scores, idx, gates, hist,
+                     me_part, nblk);
+}
+
 __global__ void __launch_bounds__(kGateThreads)
 topk_from_scores_kernel(const float* __restrict__ scores, int64_t Ttok, int E, int k,
                         int normalize, int32_t* __restrict__ idx, float* __restrict__ gates,
@@ -214,37 +328,49 @@ topk_from_scores_kernel(const float* __restrict__ scores, int64_t Ttok, int E, i
                      me_part, nblk);
 }
 
-// One block.  hist [k][nblk][E] is turned in place into the slot base of every
-// (choice, block, expert): all earlier choices of all tokens, then earlier blocks.
-__global__ void __launch_bounds__(kMaxExperts)
+// One block of 32 warps.  hist [E][k][nblk] is turned in place into the slot base of every
+// (expert, choice, block): all earlier choices of all tokens, then earlier blocks.  A warp owns
+// an expert at a time and scans its k * nblk sequence 32 values per step.
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads)
 route_scan_kernel(int32_t* __restrict__ hist, const float* __restrict__ me_part, int64_t T,
                   int E, int k, int C, int nblk, int32_t* __restrict__ counts,
                   int32_t* __restrict__ offsets, int32_t* __restrict__ first_hist,
                   float* __restrict__ l_aux) {
   __shared__ float prod[kMaxExperts];
   __shared__ int cnt[kMaxExperts];
-  const int e = threadIdx.x;
-  if (e < E) {
-    int running = 0;
-    int first = 0;
-    for (int c = 0; c < k; ++c) {
-      int32_t* h = hist + (int64_t)c * nblk * E + e;
-#pragma unroll 8
-      for (int b = 0; b < nblk; ++b) {
-        const int v = h[(int64_t)b * E];
-        h[(int64_t)b * E] = running;
-        running += v;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = k * nblk;
+  for (int e = warp; e < E; e += kScanThreads / 32) {
+    int32_t* h = hist + (int64_t)e * n;
+    int running = 0, first = 0;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+      const int i = i0 + lane;
+      const int v = i < n ? h[i] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
       }
-      if (c == 0) first = running;
+      const int excl = running + incl - v;
+      if (i < n) h[i] = excl;
+      if (i == nblk) first = excl;              // everything of choice 0
+      running += __shfl_sync(0xffffffffu, incl, 31);
     }
+    first = __reduce_max_sync(0xffffffffu, first);
+    if (k == 1) first = running;
+    // mean score of the expert: lane-strided partial sums, then a fixed shuffle tree
     float me = 0.f;
-#pragma unroll 8
-    for (int b = 0; b < nblk; ++b) me += me_part[(int64_t)b * E + e];
-    const float fT = (float)T;
-    prod[e] = (me / fT) * ((float)first / fT);
-    cnt[e] = min(running, C);
-    counts[e] = cnt[e];
-    first_hist[e] = first;
+    for (int b = lane; b < nblk; b += 32) me += me_part[(int64_t)e * nblk + b];
+    me = warp_sum(me);
+    if (lane == 0) {
+      const float fT = (float)T;
+      prod[e] = (me / fT) * ((float)first / fT);
+      cnt[e] = min(running, C);
+      counts[e] = cnt[e];
+      first_hist[e] = first;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -277,7 +403,7 @@ route_slot_kernel(const int32_t* __restrict__ idx, const int32_t* __restrict__ b
     if (warp == 0 && rank == 0 && e >= 0) cnt0[e] = __popc(mask);
     __syncthreads();
     if (t < T) {
-      const int s = base[((int64_t)c * nblk + blockIdx.x) * E + e] + (warp == 1 ? cnt0[e] : 0) + rank;
+      const int s = base[((int64_t)e * k + c) * nblk + blockIdx.x] + (warp == 1 ? cnt0[e] : 0) + rank;
       slot[t * k + c] = s;
       if (s < C) {
         perm[offsets[e] + s] = (int32_t)(t * k + c);
@@ -421,7 +547,7 @@ static int route_tail(RouteWs w, int64_t T, int E, int k, int C, int32_t* idx, i
                       int32_t* first_hist, float* l_aux, cudaStream_t st) {
   const int nb = nblocks(T);
   MOLE_CUDA_OK(cudaMemsetAsync(perm, 0xff, (size_t)T * k * 4, st));
-  route_scan_kernel<<<1, kMaxExperts, 0, st>>>(w.hist, w.me_part, T, E, k, C, nb, counts, offsets,
+  route_scan_kernel<<<1, kScanThreads, 0, st>>>(w.hist, w.me_part, T, E, k, C, nb, counts, offsets,
                                                first_hist, l_aux);
   MOLE_LAUNCH_OK();
   route_slot_kernel<<<nb, kGateTok, 0, st>>>(idx, w.hist, offsets, T, E, k, C, nb, slot, gates,
@@ -445,6 +571,32 @@ static int launch_gate(const void* x, const void* wg, const float* bias, int64_t
                                        w.me_part, nb);
   MOLE_LAUNCH_OK();
   return MOLE_OK;
+}
+
+template <int NT>
+static int launch_gate_mma(const void* x, const void* wg, const float* bias, int64_t Ttok, int M,
+                           int E, int k, int normalize, float* scores, int32_t* idx, float* gates,
+                           RouteWs w, cudaStream_t st) {
+  const int nb = nblocks(Ttok);
+  const size_t tiles = (size_t)2 * (kGateTok + NT * 8) * kMmaLds * 2;
+  const size_t tail = (size_t)kGateTok * (E + 1) * 4 + (size_t)k * E * 4;
+  const size_t smem = tiles > tail ? tiles : tail;
+  auto kern = gate_topk_mma_kernel<NT>;
+  MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<nb, kGateThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                       static_cast<const __nv_bfloat16*>(wg), bias, Ttok, M, E, k,
+                                       normalize, scores, idx, gates, w.hist, w.me_part, nb);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+static int dispatch_gate_mma(int E, const void* x, const void* wg, const float* bias, int64_t Ttok,
+                             int M, int k, int normalize, float* scores, int32_t* idx, float* gates,
+                             RouteWs w, cudaStream_t st) {
+  if (E <= 32) return launch_gate_mma<4>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+  if (E <= 64) return launch_gate_mma<8>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+  if (E <= 128) return launch_gate_mma<16>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
+  return launch_gate_mma<32>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
 }
 
 template <typename T>
@@ -488,7 +640,10 @@ extern "C" int mole_gate_route_fwd(const void* x, const void* wg, const float* l
   int rc;
   if (dtype == MOLE_F32)
     rc = dispatch_gate<float>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
-  else if (dtype == MOLE_BF16)
+  else if (dtype == MOLE_BF16 && M % kMmaKC == 0 &&
+           ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg)) & 15) == 0)
+    rc = dispatch_gate_mma(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else if (dtype == MOLE_BF16)     // odd M or unaligned rows: CUDA-core gate
     rc = dispatch_gate<__nv_bfloat16>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
   else
     return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);

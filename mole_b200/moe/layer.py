@@ -240,7 +240,10 @@ class MOLEModule(torch.nn.Module):
         plan = holder["plan"]
         self.l_aux = l_aux
         self.last_plan = plan
-        dispatched_input = Dispatch.apply(resized_input, plan)
+        # when x needs a gradient the gate's backward will run after the dispatch's and can fuse
+        # the two contributions to dx
+        holder["gate_needs_x_grad"] = bool(resized_input.requires_grad and torch.is_grad_enabled())
+        dispatched_input = Dispatch.apply(resized_input, plan, holder)
 
         self._route_counts = plan.counts
         experts_output = BatchFusedFWD.apply(dispatched_input, self, self.dummy_param, time_it, prefetch)
