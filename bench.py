@@ -222,8 +222,10 @@ def run_ours(args):
         barrier()
         n0 = launches()
         ev0.record()
+        h0 = time.perf_counter()
         for _ in range(args.steps):
             step()
+        host_ms = (time.perf_counter() - h0) * 1e3 / args.steps     # enqueue time, no sync inside
         ev1.record()
         barrier()
         n1 = launches()
@@ -281,6 +283,7 @@ def run_ours(args):
                    "l2": "per-step working set (weights, gradients, activations) is >10 GB, far above "
                          "the 126 MB L2, so no flush is needed between iterations"},
         "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": n1 - n0,
+        "host_enqueue_ms_per_step": host_ms,
     }
     plan = m.last_plan
     pairs = int(plan.counts.sum().item())

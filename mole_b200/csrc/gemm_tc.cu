@@ -503,9 +503,47 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// bf16 tensor, innermost dimension contiguous, 128-byte swizzle, box inner extent 64 elements
+// Encoded tensor maps are cached by (base, extents, box): a training loop presents the same few
+// buffers every step and the driver call costs microseconds on the launch path.
+struct MapKey {
+  uintptr_t base;
+  uint64_t d[3];
+  uint32_t b[3];
+  int rank;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rank == o.rank && d[0] == o.d[0] && d[1] == o.d[1] && d[2] == o.d[2] &&
+           b[0] == o.b[0] && b[1] == o.b[1] && b[2] == o.b[2];
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
+    for (int i = 0; i < 3; ++i) h = (h ^ (k.d[i] + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2))) * 31 + k.b[i];
+    return (size_t)(h ^ (uint64_t)k.rank);
+  }
+};
+static int encode_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                      const uint32_t* box);
 static int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
                     const uint32_t* box) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{};
+  key.base = reinterpret_cast<uintptr_t>(base);
+  key.rank = rank;
+  for (int i = 0; i < rank; ++i) { key.d[i] = dims[i]; key.b[i] = box[i]; }
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *m = it->second; return MOLE_OK; }
+  if (int rc = encode_map(m, base, rank, dims, box)) return rc;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *m);
+  return MOLE_OK;
+}
+
+// bf16 tensor, innermost dimension contiguous, 128-byte swizzle, box inner extent 64 elements
+static int encode_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                      const uint32_t* box) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(MOLE_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
   cuuint64_t gdim[3], gstride[2];

@@ -582,7 +582,11 @@ static int launch_gate_mma(const void* x, const void* wg, const float* bias, int
   const size_t tail = (size_t)kGateTok * (E + 1) * 4 + (size_t)k * E * 4;
   const size_t smem = tiles > tail ? tiles : tail;
   auto kern = gate_topk_mma_kernel<NT>;
-  MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  static size_t configured = 0;             // the attribute only ever needs to grow
+  if (smem > configured) {
+    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
   kern<<<nb, kGateThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
                                        static_cast<const __nv_bfloat16*>(wg), bias, Ttok, M, E, k,
                                        normalize, scores, idx, gates, w.hist, w.me_part, nb);
