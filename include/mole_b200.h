@@ -157,9 +157,10 @@ typedef struct {
   int32_t n_slots;        /* leading extent of the weight arrays */
   int32_t n_grad_slots;   /* leading extent of the gradient arrays (0: same as n_slots) */
   int32_t accumulate;     /* backward: weight grads += instead of = (core.cpp:457-514) */
-  int32_t backend;        /* 0: tensor cores for bf16, CUDA cores for fp32 (the fp32 layer needs
-                             fp32-exact products); 1: CUDA-core kernels also for bf16, used to
-                             bisect numerics */
+  int32_t backend;        /* 0: tensor cores for bf16 (CTA pairs, cta_group::2, where the shape
+                             allows), CUDA cores for fp32 (the fp32 layer needs fp32-exact
+                             products); 1: CUDA-core kernels also for bf16, used to bisect
+                             numerics; 2: tensor cores with the one-CTA kernel only */
 } mole_ffn_desc;
 
 /* scratch the FFN needs per call (tile schedule); bytes depends only on L, n_src, Cs */

@@ -127,10 +127,12 @@ __device__ __forceinline__ float act_grad(float x, int act, int gelu_bwd) {
 //   tile_row0[i]   first row of the i-th 128-row tile that holds at least one valid row
 //   tile_expert[i] local expert the tile belongs to; tiles are sorted by expert
 //   expert_tile_start[l - e_begin] .. [+1]  tile index range of expert l
+//   expert_pair_start  the same ranges counted in pairs of tiles (odd counts rounded up)
 //   n_tiles        total
 struct Schedule {
   int32_t* n_tiles;            // [1]
   int32_t* expert_tile_start;  // [L + 1]
+  int32_t* expert_pair_start;  // [L + 1]  prefix of ceil(tiles / 2): work units of the 2-CTA GEMM
   int32_t* tile_row0;          // [max_tiles]
   int32_t* tile_expert;        // [max_tiles]
   int32_t max_tiles;

@@ -41,6 +41,7 @@ static int fill_slots(SlotMap& m, const mole_ffn_desc* d, const int32_t* host_ma
 }
 
 static bool use_tc(const mole_ffn_desc* d) { return d->dtype == MOLE_BF16 && d->backend != 1; }
+static int single_cta(const mole_ffn_desc* d) { return d->backend == 2; }
 
 static int row_gemm(const mole_ffn_desc* d, const RowGemmArgs& a, cudaStream_t st) {
   return use_tc(d) ? tc_row_gemm(a, st) : simt_row_gemm(d->dtype, a, st);
@@ -83,6 +84,7 @@ extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
   a.gelu_bwd = d->gelu_bwd;
   a.e_begin = d->e_begin;
   a.n_experts = d->e_end - d->e_begin;
+  a.single_cta = single_cta(d);
   // FC1: [rows, M] x W1_e^T ([F, M] read as [N=F][K=M])
   a.A = x; a.W = w1; a.w_nk = 1; a.N = d->F; a.K = d->M; a.bias = b1; a.aux = nullptr;
   a.out0 = x1; a.out1 = h; a.epi = EPI_FC1;
@@ -118,7 +120,7 @@ extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
   WgradArgs g{};
   g.sched = s; g.gslot = gslot; g.n_slots = n_grad_slots; g.total_rows = total_rows;
   g.accumulate = d->accumulate; g.e_begin = d->e_begin; g.n_experts = n_experts;
-  g.P = d->F; g.Q = d->M;
+  g.P = d->F; g.Q = d->M; g.single_cta = single_cta(d);
   ColsumArgs c{};
   c.sched = s; c.gslot = gslot; c.accumulate = d->accumulate; c.e_begin = d->e_begin;
   c.n_experts = n_experts;
@@ -130,7 +132,7 @@ extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
   RowGemmArgs a{};
   a.sched = s; a.wslot = wslot; a.w_expert_stride = (int64_t)d->F * d->M; a.n_slots = d->n_slots;
   a.total_rows = total_rows; a.act = d->act; a.gelu_bwd = d->gelu_bwd;
-  a.e_begin = d->e_begin; a.n_experts = n_experts;
+  a.e_begin = d->e_begin; a.n_experts = n_experts; a.single_cta = single_cta(d);
   a.A = dout; a.W = w2; a.w_nk = 1; a.N = d->F; a.K = d->M; a.bias = nullptr; a.aux = x1;
   a.out0 = dx1; a.out1 = nullptr; a.epi = EPI_DACT;
   if (int rc = row_gemm(d, a, st)) return rc;

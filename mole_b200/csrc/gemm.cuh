@@ -29,6 +29,7 @@ struct RowGemmArgs {
   int64_t total_rows;   // extent of the row buffers
   int epi, act, gelu_bwd;
   int e_begin, n_experts;   // experts covered by the schedule
+  int single_cta;           // tensor cores: keep to the one-CTA kernel (A/B comparisons)
   Schedule sched;
   SlotMap wslot;
 };
@@ -43,6 +44,7 @@ struct WgradArgs {
   int64_t total_rows;
   int accumulate;
   int e_begin, n_experts;
+  int single_cta;
   Schedule sched;
   SlotMap gslot;
 };

@@ -11,7 +11,7 @@ namespace mole {
 // ---- schedule -----------------------------------------------------------------------
 int64_t schedule_bytes(int L, int n_src, int Cs) {
   const int64_t max_tiles = (int64_t)L * n_src * (Cs / kTileRows);
-  return (1 + (L + 1) + 2 * max_tiles + 16) * 4;
+  return (1 + 2 * (L + 1) + 2 * max_tiles + 16) * 4;
 }
 Schedule carve_schedule(void* ws, int L, int n_src, int Cs) {
   Schedule s;
@@ -19,7 +19,8 @@ Schedule carve_schedule(void* ws, int L, int n_src, int Cs) {
   s.max_tiles = L * n_src * (Cs / kTileRows);
   s.n_tiles = p;
   s.expert_tile_start = p + 4;
-  s.tile_row0 = s.expert_tile_start + (L + 1) + 3;
+  s.expert_pair_start = s.expert_tile_start + (L + 1);
+  s.tile_row0 = s.expert_pair_start + (L + 1) + 3;
   s.tile_expert = s.tile_row0 + s.max_tiles;
   return s;
 }
@@ -58,6 +59,16 @@ schedule_kernel(const int32_t* __restrict__ counts, int L, int n_src, int Cs, in
       s.tile_expert[t + i] = l;
     }
     t += nt;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const int ne = e_end - e_begin;
+    int run = 0;
+    for (int i = 0; i < ne; ++i) {
+      s.expert_pair_start[i] = run;
+      run += (s.expert_tile_start[i + 1] - s.expert_tile_start[i] + 1) / 2;
+    }
+    s.expert_pair_start[ne] = run;
   }
 }
 

@@ -219,6 +219,7 @@ struct TcParams {
   const int32_t* expert_tile_start;
   const int32_t* tile_row0;
   const int32_t* tile_expert;
+  const int32_t* expert_pair_start;   // 2-CTA kernel: prefix of ceil(tiles / 2) per expert
   int n_experts, e_begin;
   int N, K;                 // rows mode: output columns / reduction.  wgrad: Q / unused
   int P;                    // wgrad: output rows per expert
@@ -272,6 +273,66 @@ __device__ __forceinline__ WorkItem decode_item(const TcParams& p, int item) {
     w.t1 = p.expert_tile_start[w.el + 1];
   }
   return w;
+}
+
+// Epilogue of one thread's accumulator row: columns [c_begin, c_end) of the tile in steps of 32,
+// TMEM -> registers -> fused epilogue -> global memory (64 contiguous bytes per step and output).
+template <int MODE>
+__device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t taddr, bool empty,
+                                                 int64_t obase, const __nv_bfloat16* bias,
+                                                 int c_begin, int c_end) {
+#pragma unroll 1
+  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+    float v[32];
+    if (!empty) {
+      uint32_t r[32];
+      tmem_ld32(taddr + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = 0.f;
+    }
+    if (MODE == TC_WGRAD) {
+      if (p.accumulate) {
+        float old[32];
+        load_bf16x32(p.out0 + obase + c0, old);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += old[i];
+      }
+      store_bf16x32(p.out0 + obase + c0, v);
+    } else if (p.epi == EPI_FC1) {
+      float b[32], h[32];
+      if (bias) load_bf16x32(bias + c0, b);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        v[i] += bias ? b[i] : 0.f;
+        // the saved pre-activation is bf16: the activation is taken of the rounded value so
+        // that backward's act'(x1) and forward's act(x1) see the same x1
+        v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+        h[i] = fast_act_fwd(v[i], p.act);
+      }
+      store_bf16x32(p.out0 + obase + c0, v);
+      store_bf16x32(p.out1 + obase + c0, h);
+    } else if (p.epi == EPI_BIAS) {
+      float b[32];
+      if (bias) {
+        load_bf16x32(bias + c0, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += b[i];
+      }
+      store_bf16x32(p.out0 + obase + c0, v);
+    } else if (p.epi == EPI_DACT) {
+      float x1[32];
+      load_bf16x32(p.aux + obase + c0, x1);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= fast_act_grad(x1[i], p.act, p.gelu_bwd);
+      store_bf16x32(p.out0 + obase + c0, v);
+    } else {
+      store_bf16x32(p.out0 + obase + c0, v);
+    }
+  }
 }
 
 template <int MODE, bool B_KMAJOR, int BN, int STAGES>
@@ -414,58 +475,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       else obase = ((int64_t)slot * p.P + w.row0 + lrow) * p.N + w.n0;
       const __nv_bfloat16* bias =
           (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
-#pragma unroll 1
-      for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
-        float v[32];
-        if (!empty) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-        }
-        if (MODE == TC_WGRAD) {
-          if (p.accumulate) {
-            float old[32];
-            load_bf16x32(p.out0 + obase + c0, old);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += old[i];
-          }
-          store_bf16x32(p.out0 + obase + c0, v);
-        } else if (p.epi == EPI_FC1) {
-          float b[32], h[32];
-          if (bias) load_bf16x32(bias + c0, b);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            v[i] += bias ? b[i] : 0.f;
-            // the saved pre-activation is bf16: the activation is taken of the rounded value so
-            // that backward's act'(x1) and forward's act(x1) see the same x1
-            v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
-            h[i] = fast_act_fwd(v[i], p.act);
-          }
-          store_bf16x32(p.out0 + obase + c0, v);
-          store_bf16x32(p.out1 + obase + c0, h);
-        } else if (p.epi == EPI_BIAS) {
-          float b[32];
-          if (bias) {
-            load_bf16x32(bias + c0, b);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += b[i];
-          }
-          store_bf16x32(p.out0 + obase + c0, v);
-        } else if (p.epi == EPI_DACT) {
-          float x1[32];
-          load_bf16x32(p.aux + obase + c0, x1);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= fast_act_grad(x1[i], p.act, p.gelu_bwd);
-          store_bf16x32(p.out0 + obase + c0, v);
-        } else {
-          store_bf16x32(p.out0 + obase + c0, v);
-        }
-      }
+      epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, obase,
+                             bias, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -480,6 +491,278 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols) : "memory");
+  }
+}
+
+// =========================================================================================
+// cta_group::2 variant: a pair of CTAs on two SMs (a cluster of 2) computes a 256 x 256 tile.
+// Each CTA stages its own 128 rows of A and one 128-column half of B; one tcgen05.mma issued by
+// the even CTA reads A and both halves of B from both CTAs' shared memory and writes 128 lanes
+// x 256 columns of accumulator into each CTA's TMEM.  Per unit of work the operand bytes read
+// through L2 drop from 48 KB to 32 KB per 128 x 256 x 64 block-product -- the grouped GEMMs with
+// few rows per expert are bound by L2 throughput, not by HBM or the tensor pipe.
+//
+//   rows mode   the pair takes two consecutive row tiles of one expert (the odd CTA idles its A
+//               loads and its epilogue when the expert has an odd number of tiles)
+//   wgrad mode  the pair takes a 256 x 256 block of the expert's [F, M] gradient
+//
+// Barriers: TMA loads of both CTAs complete on the even CTA's "full" barrier (.cta_group::2
+// form, no multicast); stage release and accumulator-ready are tcgen05.commit arrivals multicast
+// to both CTAs' barriers; the odd CTA's epilogue releases the accumulator with a remote arrive.
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared::cluster address
+constexpr int kBN2 = 256;
+constexpr uint32_t kBHalfBytes = (kBN2 / 2) * kBK * 2;
+constexpr uint32_t kStage2Bytes = kABytes + kBHalfBytes;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma2_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                             int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                             int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit2(uint32_t bar) {   // arrives in both CTAs of the pair
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma2_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+struct PairItem {
+  int valid;
+  int el;
+  int n0;          // first output column of the pair's 256-wide block
+  int row0[2];     // rows mode: first row of each CTA's tile, -1 = none.  wgrad: p0 of each CTA
+  int t0, t1;      // wgrad: tile range of the expert
+};
+
+template <int MODE>
+__device__ __forceinline__ PairItem decode_pair(const TcParams& p, int item) {
+  PairItem w;
+  w.valid = 0;
+  if (MODE == TC_ROWS) {
+    const int nb = p.N / kBN2;
+    const int total = p.expert_pair_start[p.n_experts] * nb;
+    if (item >= total) return w;
+    int lo = 0, hi = p.n_experts;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.expert_pair_start[mid] * nb <= item) lo = mid; else hi = mid;
+    }
+    const int ps = p.expert_pair_start[lo], np = p.expert_pair_start[lo + 1] - ps;
+    const int local = item - ps * nb;
+    const int pair = local % np;
+    const int ts = p.expert_tile_start[lo], te = p.expert_tile_start[lo + 1];
+    w.valid = 1;
+    w.el = lo;
+    w.n0 = (local / np) * kBN2;
+    w.row0[0] = p.tile_row0[ts + 2 * pair];
+    w.row0[1] = ts + 2 * pair + 1 < te ? p.tile_row0[ts + 2 * pair + 1] : -1;
+    w.t0 = w.t1 = 0;
+  } else {
+    const int pb = p.P / 256, qb = p.N / kBN2;
+    if (item >= p.n_experts * pb * qb) return w;
+    w.valid = 1;
+    w.el = item / (pb * qb);
+    const int r = item - w.el * pb * qb;
+    w.row0[0] = (r / qb) * 256;
+    w.row0[1] = w.row0[0] + 128;
+    w.n0 = (r % qb) * kBN2;
+    w.t0 = p.expert_tile_start[w.el];
+    w.t1 = p.expert_tile_start[w.el + 1];
+  }
+  return w;
+}
+
+template <int MODE, bool B_KMAJOR, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const __grid_constant__ TcParams p) {
+  constexpr uint32_t kTmemCols = 2 * kBN2;
+  constexpr bool A_MN = (MODE == TC_WGRAD);
+  constexpr bool B_MN = (MODE == TC_WGRAD) || !B_KMAJOR;
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                              ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(kBN2 >> 3) << 17) |
+                              ((uint32_t)(256 >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+  const uint32_t smem_base = smem_u32(smem);
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);               // the even CTA's arrive.expect_tx
+      mbar_init(empty0 + 8 * s, 1);              // one multicast commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 2 * kEpiWarps); // epilogue warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  cluster_sync_all();                            // peer barriers initialised, TMEM address published
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int item = cluster_id;; item += n_clusters) {
+        const PairItem w = decode_pair<MODE>(p, item);
+        if (!w.valid) break;
+        const int slot = p.slot.s[p.e_begin + w.el];
+        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
+        const bool have_a = w.row0[rank] >= 0;
+        const uint32_t tx = MODE == TC_ROWS
+                                ? kABytes * (w.row0[1] >= 0 ? 2u : 1u) + 2u * kBHalfBytes
+                                : 2u * kStage2Bytes;
+        const int nh = w.n0 + 128 * (int)rank;         // this CTA's half of the B columns
+        for (int kb = 0; kb < nkb; ++kb) {
+          mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11);
+          const uint32_t bar = (full0 + 8 * stage) & kPeerMask;     // the even CTA's barrier
+          const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
+          if (leader) mbar_expect_tx(full0 + 8 * stage, tx);
+          if (MODE == TC_ROWS) {
+            if (have_a) tma2_load_2d(sa, &tmap_a, bar, kb * kBK, w.row0[rank]);
+            if (B_KMAJOR) {
+              tma2_load_3d(sb, &tmap_b, bar, kb * kBK, nh, slot);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                tma2_load_3d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, kb * kBK, slot);
+            }
+          } else {
+            const int row = p.tile_row0[w.t0 + (kb >> 1)] + (kb & 1) * kBK;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              tma2_load_2d(sa + i * 8192, &tmap_a, bar, w.row0[rank] + 64 * i, row);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              tma2_load_2d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, row);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (even CTA only) -----------------------
+    if (lane == 0 && leader) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int item = cluster_id;; item += n_clusters) {
+        const PairItem w = decode_pair<MODE>(p, item);
+        if (!w.valid) break;
+        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
+        if (nkb == 0) continue;
+        mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12);
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN2;
+        for (int kb = 0; kb < nkb; ++kb) {
+          mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 13);
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
+            const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
+                                     : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
+            const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
+                                     : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
+            tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          tcgen05_commit2(empty0 + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        tcgen05_commit2(tfull0 + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs) -----------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int chalf = ew >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int item = cluster_id;; item += n_clusters) {
+      const PairItem w = decode_pair<MODE>(p, item);
+      if (!w.valid) break;
+      const int slot = p.slot.s[p.e_begin + w.el];
+      const bool empty = MODE == TC_WGRAD && w.t1 == w.t0;
+      if (!empty) {
+        mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14);
+        tcgen05_fence_after();
+      }
+      const int lrow = quarter * 32 + lane;
+      const int r0 = w.row0[rank];
+      if (r0 >= 0) {
+        int64_t obase;
+        if (MODE == TC_ROWS) obase = (int64_t)(r0 + lrow) * p.N + w.n0;
+        else obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
+        const __nv_bfloat16* bias =
+            (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
+        epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty,
+                               obase, bias, chalf * (kBN2 / 2), (chalf + 1) * (kBN2 / 2));
+      }
+      if (!empty) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster((tempty0 + 8 * acc) & kPeerMask);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  cluster_sync_all();          // nobody leaves while the peer may still touch its smem or barriers
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(kTmemCols) : "memory");
   }
 }
@@ -598,17 +881,54 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   return MOLE_OK;
 }
 
+// Launch of the cta_group::2 kernel: grid = 2 x min(work units, clusters that can be resident).
+template <int MODE, bool B_KMAJOR>
+static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_items,
+                      cudaStream_t st) {
+  constexpr int STAGES = 6;
+  constexpr size_t smem = (size_t)STAGES * kStage2Bytes + 1024;
+  auto kern = tc2_gemm_kernel<MODE, B_KMAJOR, STAGES>;
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    max_clusters = n;
+  }
+  int clusters = max_clusters < max_items ? max_clusters : max_items;
+  if (clusters <= 0) return MOLE_OK;
+  if (profile_enabled()) profile_begin(st, p.epi);
+  kern<<<2 * clusters, kThreads, smem, st>>>(ma, mb, p);
+  if (profile_enabled()) profile_end(st);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
 static void fill_sched(TcParams& p, const Schedule& s) {
   p.n_tiles = s.n_tiles;
   p.expert_tile_start = s.expert_tile_start;
   p.tile_row0 = s.tile_row0;
   p.tile_expert = s.tile_expert;
+  p.expert_pair_start = s.expert_pair_start;
 }
 
 int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   MOLE_REQUIRE(a.N % 128 == 0 && a.K % kBK == 0, "tensor-core GEMM needs N %% 128 == 0 and K %% 64 == 0 (N=%d K=%d)", a.N, a.K);
   MOLE_REQUIRE(a.total_rows % kTileRows == 0, "row buffers must hold whole 128-row tiles");
   const int BN = a.N % 256 == 0 ? 256 : 128;
+  const bool pair = BN == 256 && !a.single_cta;
   CUtensorMap ma, mb;
   {
     const uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.total_rows};
@@ -622,7 +942,7 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
     const uint64_t outer = a.w_nk ? (uint64_t)a.N : (uint64_t)a.K;
     MOLE_REQUIRE((int64_t)(inner * outer) == a.w_expert_stride, "weight stride mismatch");
     const uint64_t dims[3] = {inner, outer, (uint64_t)a.n_slots};
-    const uint32_t box_k[3] = {kBK, (uint32_t)BN, 1};
+    const uint32_t box_k[3] = {kBK, (uint32_t)(pair ? 128 : BN), 1};   // a pair loads half each
     const uint32_t box_n[3] = {64, kBK, 1};
     if (int rc = make_map(&mb, a.W, 3, dims, a.w_nk ? box_k : box_n)) return rc;
   }
@@ -644,6 +964,12 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   p.fault = device_fault_word();
   p.slot = a.wslot;
   const int max_items = a.sched.max_tiles * (a.N / BN);
+  for (const void* q : {a.bias, a.aux, (const void*)a.out0, (const void*)a.out1})
+    MOLE_REQUIRE((reinterpret_cast<uintptr_t>(q) & 31) == 0, "epilogue operand %p not 32-byte aligned", q);
+  if (pair) {
+    return a.w_nk ? launch_tc2<TC_ROWS, true>(ma, mb, p, max_items, st)
+                  : launch_tc2<TC_ROWS, false>(ma, mb, p, max_items, st);
+  }
   if (a.w_nk) {
     return BN == 256 ? launch_tc<TC_ROWS, true, 256>(ma, mb, p, max_items, st)
                      : launch_tc<TC_ROWS, true, 128>(ma, mb, p, max_items, st);
@@ -679,6 +1005,9 @@ int tc_wgrad(const WgradArgs& a, cudaStream_t st) {
   p.out0 = static_cast<__nv_bfloat16*>(a.out);
   p.fault = device_fault_word();
   p.slot = a.gslot;
+  MOLE_REQUIRE((reinterpret_cast<uintptr_t>(a.out) & 31) == 0, "gradient base not 32-byte aligned");
+  if (BN == 256 && a.P % 256 == 0 && !a.single_cta)
+    return launch_tc2<TC_WGRAD, true>(ma, mb, p, a.n_experts * (a.P / 256) * (a.Q / 256), st);
   const int max_items = a.n_experts * (a.P / kBM) * (a.Q / BN);
   return BN == 256 ? launch_tc<TC_WGRAD, true, 256>(ma, mb, p, max_items, st)
                    : launch_tc<TC_WGRAD, true, 128>(ma, mb, p, max_items, st);

@@ -115,7 +115,7 @@ def test_ffn_fp32_two_sources_and_relu():
     check(case, out, dx, grads, range(4), wscale=4.0)
 
 
-@pytest.mark.parametrize("backend", [1, 0], ids=["cuda_cores", "tcgen05"])
+@pytest.mark.parametrize("backend", [1, 2, 0], ids=["cuda_cores", "tcgen05_one_cta", "tcgen05_cta_pair"])
 def test_ffn_bf16(backend):
     case = Case(M=256, F=512, L=8, n_src=1, Cs=256, counts=RAGGED, dtype=torch.bfloat16, seed=1)
     out, dx, grads = run_gpu(case, backend=backend)
@@ -164,6 +164,7 @@ def test_ffn_bf16_full_size_spot_check():
     case = Case(M, F, L, 1, Cs, counts, torch.bfloat16, seed=6)
     out, dx, grads = run_gpu(case)
     out2, dx2, grads2 = run_gpu(case, backend=1)
+    out3, dx3, grads3 = run_gpu(case, backend=2)
     valid = torch.zeros(1, L, Cs, dtype=torch.bool)
     for l in range(L):
         valid[0, l, :counts[l]] = True
@@ -171,6 +172,10 @@ def test_ffn_bf16_full_size_spot_check():
     assert rel_fro(dx[valid], dx2[valid]) < 4e-3
     for a, b in zip(grads, grads2):
         assert rel_fro(a, b) < 4e-3
+    # the CTA-pair kernel and the one-CTA kernel accumulate in the same order: identical bits
+    assert torch.equal(out[valid], out3[valid]) and torch.equal(dx[valid], dx3[valid])
+    for a, b in zip(grads, grads3):
+        assert torch.equal(a, b)
     for l in (0, 10, 37):
         o_ref, dx_ref, g_ref = case.oracle(l)
         assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
