@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per rank (debugging)")
+    ap.add_argument("--ffn-backend", type=int, default=0,
+                    help="0 default (CTA pairs), 1 CUDA cores, 2 one-CTA tcgen05 (for comparisons)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-report", action="store_true")
     return ap.parse_args()
@@ -183,9 +185,11 @@ def run_ours(args):
     MOLEDist(local_rank=local)
     dist_info = {"local_rank": local, "world_size": world, "rank": rank}
     if cfg.get("offload"):
-        m = MOLEModule(E, 0, M, F, cfg["pool"], k, 8, dist_info, "gelu", 1, False, True, dtype=dtype)
+        m = MOLEModule(E, 0, M, F, cfg["pool"], k, 8, dist_info, "gelu", 1, False, True, dtype=dtype,
+                       ffn_backend=args.ffn_backend)
     else:
-        m = MOLEModule(0, E, M, F, -1, k, max(L, 1), dist_info, "gelu", 1, False, False, dtype=dtype)
+        m = MOLEModule(0, E, M, F, -1, k, max(L, 1), dist_info, "gelu", 1, False, False, dtype=dtype,
+                       ffn_backend=args.ffn_backend)
     init_weights(m, cfg, rank, L, dtype, device)
 
     gt = torch.Generator(device=device).manual_seed(7_000_001 + rank)
@@ -388,6 +392,10 @@ def hbm_kernel_report(m, x, gy, cf, pk):
     add("combine_fwd", lambda: ops.combine(rows, plan, plan.gates), (P + T) * M * es)
     add("combine_bwd", lambda: ops.combine_bwd(gy, rows, plan, plan.gates), 3 * P * M * es + P * 4)
     add("dispatch_bwd", lambda: ops.dispatch_bwd(rows, plan, M, x.dtype, x.device), (P + T) * M * es)
+    fill = torch.empty(1 << 30, dtype=torch.uint8, device=x.device)
+    add("memset_1GiB (write-only reference)", lambda: fill.zero_(), fill.numel())
+    src = torch.empty(1 << 30, dtype=torch.uint8, device=x.device)
+    add("copy_1GiB (read+write reference)", lambda: fill.copy_(src), 2 * fill.numel())
     rep["peak_gbs"] = pk["hbm"]
     rep["note"] = "L2 flushed (256 MiB memset) before every timed launch"
     return rep

@@ -160,7 +160,9 @@ typedef struct {
   int32_t backend;        /* 0: tensor cores for bf16 (CTA pairs, cta_group::2, where the shape
                              allows), CUDA cores for fp32 (the fp32 layer needs fp32-exact
                              products); 1: CUDA-core kernels also for bf16, used to bisect
-                             numerics; 2: tensor cores with the one-CTA kernel only */
+                             numerics; 2: tensor cores with the one-CTA kernel only; 3: tensor cores
+                             with CTA pairs wherever the shape allows (0 picks between 2 and 3 by
+                             the number of row tiles an expert can have) */
 } mole_ffn_desc;
 
 /* scratch the FFN needs per call (tile schedule); bytes depends only on L, n_src, Cs */

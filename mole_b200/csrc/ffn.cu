@@ -41,7 +41,15 @@ static int fill_slots(SlotMap& m, const mole_ffn_desc* d, const int32_t* host_ma
 }
 
 static bool use_tc(const mole_ffn_desc* d) { return d->dtype == MOLE_BF16 && d->backend != 1; }
-static int single_cta(const mole_ffn_desc* d) { return d->backend == 2; }
+// CTA pairs (cta_group::2) pay off when an expert has many row tiles: the pair halves the
+// weight bytes read through L2 per product, but an odd tile count idles half a pair.  With few
+// tiles per expert the GEMMs are bound by HBM (weights are read once whatever the tile shape)
+// and the one-CTA kernel's finer granularity wins; measured crossover is around a dozen tiles.
+static int single_cta(const mole_ffn_desc* d) {
+  if (d->backend == 2) return 1;
+  if (d->backend == 3) return 0;
+  return d->n_src * (d->Cs / kTileRows) < 12;
+}
 
 static int row_gemm(const mole_ffn_desc* d, const RowGemmArgs& a, cudaStream_t st) {
   return use_tc(d) ? tc_row_gemm(a, st) : simt_row_gemm(d->dtype, a, st);

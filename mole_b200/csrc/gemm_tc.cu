@@ -277,10 +277,29 @@ __device__ __forceinline__ WorkItem decode_item(const TcParams& p, int item) {
 
 // Epilogue of one thread's accumulator row: columns [c_begin, c_end) of the tile in steps of 32,
 // TMEM -> registers -> fused epilogue -> global memory (64 contiguous bytes per step and output).
-template <int MODE>
-__device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t taddr, bool empty,
-                                                 int64_t obase, const __nv_bfloat16* bias,
-                                                 int c_begin, int c_end) {
+// Epilogue kind, activation and GELU-derivative flavour are compile-time here (the run-time
+// switch sits outside the column loop): the FC1 and dX2 epilogues are issue-bound, every
+// per-element branch shows up in the GEMM's time.
+template <int ACT>
+__device__ __forceinline__ float act_fwd_t(float x) {
+  if (ACT == MOLE_ACT_RELU) return fmaxf(x, 0.f);
+  return x * gelu_parts(x).cdf;
+}
+template <int ACT, int GBWD>
+__device__ __forceinline__ float act_grad_t(float x) {
+  if (ACT == MOLE_ACT_RELU) return x > 0.f ? 1.f : 0.f;
+  if (GBWD == MOLE_GELU_BWD_TANH) return gelu_tanh_grad(x);
+  const GeluParts g = gelu_parts(x);
+  return fmaf(x * 0.39894228f, g.e, g.cdf);
+}
+__device__ __forceinline__ float bf16_round(float v) {
+  return __uint_as_float((__float_as_uint(v) + 0x7fffu + ((__float_as_uint(v) >> 16) & 1u)) & 0xffff0000u);
+}
+
+template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM>
+__device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
+                                              int64_t obase, const __nv_bfloat16* bias,
+                                              int c_begin, int c_end) {
 #pragma unroll 1
   for (int c0 = c_begin; c0 < c_end; c0 += 32) {
     float v[32];
@@ -294,45 +313,79 @@ __device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t tad
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = 0.f;
     }
-    if (MODE == TC_WGRAD) {
-      if (p.accumulate) {
+    if (EPI == EPI_WGRAD) {
+      if (ACCUM) {
         float old[32];
         load_bf16x32(p.out0 + obase + c0, old);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] += old[i];
       }
       store_bf16x32(p.out0 + obase + c0, v);
-    } else if (p.epi == EPI_FC1) {
-      float b[32], h[32];
-      if (bias) load_bf16x32(bias + c0, b);
+    } else if (EPI == EPI_FC1) {
+      float h[32];
+      if (HAS_BIAS) {
+        float b[32];
+        load_bf16x32(bias + c0, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += b[i];
+      }
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        v[i] += bias ? b[i] : 0.f;
         // the saved pre-activation is bf16: the activation is taken of the rounded value so
         // that backward's act'(x1) and forward's act(x1) see the same x1
-        v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
-        h[i] = fast_act_fwd(v[i], p.act);
+        v[i] = bf16_round(v[i]);
+        h[i] = act_fwd_t<ACT>(v[i]);
       }
       store_bf16x32(p.out0 + obase + c0, v);
       store_bf16x32(p.out1 + obase + c0, h);
-    } else if (p.epi == EPI_BIAS) {
-      float b[32];
-      if (bias) {
+    } else if (EPI == EPI_BIAS) {
+      if (HAS_BIAS) {
+        float b[32];
         load_bf16x32(bias + c0, b);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] += b[i];
       }
       store_bf16x32(p.out0 + obase + c0, v);
-    } else if (p.epi == EPI_DACT) {
+    } else if (EPI == EPI_DACT) {
       float x1[32];
       load_bf16x32(p.aux + obase + c0, x1);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] *= fast_act_grad(x1[i], p.act, p.gelu_bwd);
+      for (int i = 0; i < 32; ++i) v[i] *= act_grad_t<ACT, GBWD>(x1[i]);
       store_bf16x32(p.out0 + obase + c0, v);
     } else {
       store_bf16x32(p.out0 + obase + c0, v);
     }
   }
+}
+
+template <int MODE>
+__device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t taddr, bool empty,
+                                                 int64_t obase, const __nv_bfloat16* bias,
+                                                 int c_begin, int c_end) {
+#define MOLE_EPI(E, A, G, B, C) \
+  epilogue_loop<E, A, G, B, C>(p, taddr, empty, obase, bias, c_begin, c_end)
+  if (MODE == TC_WGRAD) {
+    if (p.accumulate) MOLE_EPI(EPI_WGRAD, 0, 0, false, true);
+    else MOLE_EPI(EPI_WGRAD, 0, 0, false, false);
+  } else if (p.epi == EPI_FC1) {
+    if (p.act == MOLE_ACT_GELU) {
+      if (bias) MOLE_EPI(EPI_FC1, MOLE_ACT_GELU, 0, true, false);
+      else MOLE_EPI(EPI_FC1, MOLE_ACT_GELU, 0, false, false);
+    } else {
+      if (bias) MOLE_EPI(EPI_FC1, MOLE_ACT_RELU, 0, true, false);
+      else MOLE_EPI(EPI_FC1, MOLE_ACT_RELU, 0, false, false);
+    }
+  } else if (p.epi == EPI_BIAS) {
+    if (bias) MOLE_EPI(EPI_BIAS, 0, 0, true, false);
+    else MOLE_EPI(EPI_BIAS, 0, 0, false, false);
+  } else if (p.epi == EPI_DACT) {
+    if (p.act == MOLE_ACT_RELU) MOLE_EPI(EPI_DACT, MOLE_ACT_RELU, 0, false, false);
+    else if (p.gelu_bwd == MOLE_GELU_BWD_TANH) MOLE_EPI(EPI_DACT, MOLE_ACT_GELU, MOLE_GELU_BWD_TANH, false, false);
+    else MOLE_EPI(EPI_DACT, MOLE_ACT_GELU, MOLE_GELU_BWD_EXACT, false, false);
+  } else {
+    MOLE_EPI(EPI_STORE, 0, 0, false, false);
+  }
+#undef MOLE_EPI
 }
 
 template <int MODE, bool B_KMAJOR, int BN, int STAGES>

@@ -115,7 +115,7 @@ def test_ffn_fp32_two_sources_and_relu():
     check(case, out, dx, grads, range(4), wscale=4.0)
 
 
-@pytest.mark.parametrize("backend", [1, 2, 0], ids=["cuda_cores", "tcgen05_one_cta", "tcgen05_cta_pair"])
+@pytest.mark.parametrize("backend", [1, 2, 3], ids=["cuda_cores", "tcgen05_one_cta", "tcgen05_cta_pair"])
 def test_ffn_bf16(backend):
     case = Case(M=256, F=512, L=8, n_src=1, Cs=256, counts=RAGGED, dtype=torch.bfloat16, seed=1)
     out, dx, grads = run_gpu(case, backend=backend)
@@ -165,6 +165,7 @@ def test_ffn_bf16_full_size_spot_check():
     out, dx, grads = run_gpu(case)
     out2, dx2, grads2 = run_gpu(case, backend=1)
     out3, dx3, grads3 = run_gpu(case, backend=2)
+    out, dx, grads = run_gpu(case, backend=3)
     valid = torch.zeros(1, L, Cs, dtype=torch.bool)
     for l in range(L):
         valid[0, l, :counts[l]] = True

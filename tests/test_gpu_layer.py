@@ -87,7 +87,7 @@ def test_layer_fp32_golden_small_with_drops():
     assert_close(m.gate[0].linear.weight.grad, torch.from_numpy(g["dwg"]), torch.float32, "dWg", scale=4.0)
 
 
-@pytest.mark.parametrize("backend", [1, 2, 0], ids=["cuda_cores", "tcgen05_one_cta", "tcgen05_cta_pair"])
+@pytest.mark.parametrize("backend", [1, 2, 3], ids=["cuda_cores", "tcgen05_one_cta", "tcgen05_cta_pair"])
 @pytest.mark.parametrize("cf", [1.25, 0.5])
 def test_layer_bf16_matches_oracle(backend, cf):
     T, M, E, F, k = 2048, 256, 16, 512, 2
