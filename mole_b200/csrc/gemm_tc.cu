@@ -296,87 +296,143 @@ __device__ __forceinline__ float bf16_round(float v) {
   return __uint_as_float((__float_as_uint(v) + 0x7fffu + ((__float_as_uint(v) >> 16) & 1u)) & 0xffff0000u);
 }
 
+// 64 bytes of bf16 as packed words (two 32-byte vectors), and their conversion
+__device__ __forceinline__ void ld_packed32(const __nv_bfloat16* p, uint32_t (&w)[16]) {
+  uint32_t a[8], b[8];
+  ld_v8(p, a);
+  ld_v8(p + 16, b);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { w[i] = a[i]; w[8 + i] = b[i]; }
+}
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&b);
+}
+__device__ __forceinline__ void st_packed32(__nv_bfloat16* p, const uint32_t (&w)[16]) {
+  uint32_t a[8], b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { a[i] = w[i]; b[i] = w[8 + i]; }
+  st_v8(p, a);
+  st_v8(p + 16, b);
+}
+
+// Global operands of the epilogue (pre-activation for dX2, old gradient for "+=") are fetched
+// two 32-column steps ahead, the first two before the accumulator is even ready: under the
+// TMA traffic of the main loop a global load takes microseconds, and a load-use chain per step
+// made the FC1 / dX2 epilogues several times longer than their arithmetic.  The bias slice of
+// the tile sits in a per-warp shared-memory strip, filled at the same early point.
 template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM>
 __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
-                                              int64_t obase, const __nv_bfloat16* bias,
-                                              int c_begin, int c_end) {
+                                              int64_t obase, const float* bias_s,
+                                              int c_begin, int c_end, uint32_t (&pre0)[16],
+                                              uint32_t (&pre1)[16]) {
+  constexpr bool kPrefetch = EPI == EPI_DACT || (EPI == EPI_WGRAD && ACCUM);
+  const __nv_bfloat16* src = EPI == EPI_DACT ? p.aux : p.out0;
 #pragma unroll 1
-  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-    float v[32];
-    if (!empty) {
-      uint32_t r[32];
-      tmem_ld32(taddr + c0, r);
-      tmem_ld_wait();
+  for (int c0 = c_begin; c0 < c_end; c0 += 64) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-    } else {
+    for (int half = 0; half < 2; ++half) {
+      const int c = c0 + 32 * half;
+      uint32_t (&cur)[16] = half == 0 ? pre0 : pre1;
+      float v[32];
+      if (!empty) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c, r);
+        tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      uint32_t o[16];
+      if (EPI == EPI_WGRAD) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float lo = v[2 * i], hi = v[2 * i + 1];
+          if (ACCUM) { lo += bf16_lo(cur[i]); hi += bf16_hi(cur[i]); }
+          o[i] = pack_bf16(lo, hi);
+        }
+        st_packed32(p.out0 + obase + c, o);
+      } else if (EPI == EPI_FC1) {
+        uint32_t h[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float lo = v[2 * i], hi = v[2 * i + 1];
+          if (HAS_BIAS) { lo += bias_s[c - c_begin + 2 * i]; hi += bias_s[c - c_begin + 2 * i + 1]; }
+          // the saved pre-activation is bf16: the activation is taken of the rounded value so
+          // that backward's act'(x1) and forward's act(x1) see the same x1
+          o[i] = pack_bf16(lo, hi);
+          h[i] = pack_bf16(act_fwd_t<ACT>(bf16_lo(o[i])), act_fwd_t<ACT>(bf16_hi(o[i])));
+        }
+        st_packed32(p.out0 + obase + c, o);
+        st_packed32(p.out1 + obase + c, h);
+      } else if (EPI == EPI_BIAS) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float lo = v[2 * i], hi = v[2 * i + 1];
+          if (HAS_BIAS) { lo += bias_s[c - c_begin + 2 * i]; hi += bias_s[c - c_begin + 2 * i + 1]; }
+          o[i] = pack_bf16(lo, hi);
+        }
+        st_packed32(p.out0 + obase + c, o);
+      } else if (EPI == EPI_DACT) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          o[i] = pack_bf16(v[2 * i] * act_grad_t<ACT, GBWD>(bf16_lo(cur[i])),
+                           v[2 * i + 1] * act_grad_t<ACT, GBWD>(bf16_hi(cur[i])));
+        st_packed32(p.out0 + obase + c, o);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+        st_packed32(p.out0 + obase + c, o);
+      }
+      if (kPrefetch && c + 64 < c_end) ld_packed32(src + obase + c + 64, cur);   // two steps ahead
     }
-    if (EPI == EPI_WGRAD) {
-      if (ACCUM) {
-        float old[32];
-        load_bf16x32(p.out0 + obase + c0, old);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] += old[i];
-      }
-      store_bf16x32(p.out0 + obase + c0, v);
-    } else if (EPI == EPI_FC1) {
-      float h[32];
-      if (HAS_BIAS) {
-        float b[32];
-        load_bf16x32(bias + c0, b);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] += b[i];
-      }
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        // the saved pre-activation is bf16: the activation is taken of the rounded value so
-        // that backward's act'(x1) and forward's act(x1) see the same x1
-        v[i] = bf16_round(v[i]);
-        h[i] = act_fwd_t<ACT>(v[i]);
-      }
-      store_bf16x32(p.out0 + obase + c0, v);
-      store_bf16x32(p.out1 + obase + c0, h);
-    } else if (EPI == EPI_BIAS) {
-      if (HAS_BIAS) {
-        float b[32];
-        load_bf16x32(bias + c0, b);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] += b[i];
-      }
-      store_bf16x32(p.out0 + obase + c0, v);
-    } else if (EPI == EPI_DACT) {
-      float x1[32];
-      load_bf16x32(p.aux + obase + c0, x1);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] *= act_grad_t<ACT, GBWD>(x1[i]);
-      store_bf16x32(p.out0 + obase + c0, v);
-    } else {
-      store_bf16x32(p.out0 + obase + c0, v);
-    }
+  }
+}
+
+// Issued before the wait for the accumulator: the first two prefetch steps and the bias strip.
+template <int MODE>
+__device__ __forceinline__ void epilogue_prefetch(const TcParams& p, int64_t obase,
+                                                  const __nv_bfloat16* bias, float* bias_s,
+                                                  int c_begin, int c_end, uint32_t (&pre0)[16],
+                                                  uint32_t (&pre1)[16]) {
+  const bool need = MODE == TC_WGRAD ? p.accumulate != 0 : p.epi == EPI_DACT;
+  if (need) {
+    const __nv_bfloat16* src = MODE == TC_WGRAD ? p.out0 : p.aux;
+    ld_packed32(src + obase + c_begin, pre0);
+    ld_packed32(src + obase + c_begin + 32, pre1);
+  }
+  if (MODE == TC_ROWS && bias != nullptr) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();                       // the strip's previous readers are done
+    for (int i = lane; i < c_end - c_begin; i += 32) bias_s[i] = __bfloat162float(bias[c_begin + i]);
+    __syncwarp();
   }
 }
 
 template <int MODE>
 __device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t taddr, bool empty,
-                                                 int64_t obase, const __nv_bfloat16* bias,
-                                                 int c_begin, int c_end) {
+                                                 int64_t obase, bool has_bias, const float* bias_s,
+                                                 int c_begin, int c_end, uint32_t (&pre0)[16],
+                                                 uint32_t (&pre1)[16]) {
 #define MOLE_EPI(E, A, G, B, C) \
-  epilogue_loop<E, A, G, B, C>(p, taddr, empty, obase, bias, c_begin, c_end)
+  epilogue_loop<E, A, G, B, C>(p, taddr, empty, obase, bias_s, c_begin, c_end, pre0, pre1)
   if (MODE == TC_WGRAD) {
     if (p.accumulate) MOLE_EPI(EPI_WGRAD, 0, 0, false, true);
     else MOLE_EPI(EPI_WGRAD, 0, 0, false, false);
   } else if (p.epi == EPI_FC1) {
     if (p.act == MOLE_ACT_GELU) {
-      if (bias) MOLE_EPI(EPI_FC1, MOLE_ACT_GELU, 0, true, false);
+      if (has_bias) MOLE_EPI(EPI_FC1, MOLE_ACT_GELU, 0, true, false);
       else MOLE_EPI(EPI_FC1, MOLE_ACT_GELU, 0, false, false);
     } else {
-      if (bias) MOLE_EPI(EPI_FC1, MOLE_ACT_RELU, 0, true, false);
+      if (has_bias) MOLE_EPI(EPI_FC1, MOLE_ACT_RELU, 0, true, false);
       else MOLE_EPI(EPI_FC1, MOLE_ACT_RELU, 0, false, false);
     }
   } else if (p.epi == EPI_BIAS) {
-    if (bias) MOLE_EPI(EPI_BIAS, 0, 0, true, false);
+    if (has_bias) MOLE_EPI(EPI_BIAS, 0, 0, true, false);
     else MOLE_EPI(EPI_BIAS, 0, 0, false, false);
   } else if (p.epi == EPI_DACT) {
     if (p.act == MOLE_ACT_RELU) MOLE_EPI(EPI_DACT, MOLE_ACT_RELU, 0, false, false);
@@ -407,6 +463,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
+  __shared__ float bias_strip[kEpiWarps][128];      // per epilogue warp: bias of its 128 columns
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -518,18 +575,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int e = p.e_begin + w.el;
       const int slot = p.slot.s[e];
       const bool empty = MODE == TC_WGRAD && w.t1 == w.t0;
-      if (!empty) {
-        mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4);
-        tcgen05_fence_after();
-      }
       const int lrow = quarter * 32 + lane;
       int64_t obase;            // element offset of (row, n0) in the output
       if (MODE == TC_ROWS) obase = (int64_t)(w.row0 + lrow) * p.N + w.n0;
       else obase = ((int64_t)slot * p.P + w.row0 + lrow) * p.N + w.n0;
       const __nv_bfloat16* bias =
           (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
+      uint32_t pre0[16], pre1[16];
+      epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], chalf * (BN / 2), (chalf + 1) * (BN / 2),
+                              pre0, pre1);
+      if (!empty) {
+        mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4);
+        tcgen05_fence_after();
+      }
       epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, obase,
-                             bias, chalf * (BN / 2), (chalf + 1) * (BN / 2));
+                             bias != nullptr, bias_strip[ew], chalf * (BN / 2), (chalf + 1) * (BN / 2),
+                             pre0, pre1);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -668,6 +729,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
+  __shared__ float bias_strip[kEpiWarps][128];      // per epilogue warp: bias of its 128 columns
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -787,21 +849,26 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (!w.valid) break;
       const int slot = p.slot.s[p.e_begin + w.el];
       const bool empty = MODE == TC_WGRAD && w.t1 == w.t0;
+      const int lrow = quarter * 32 + lane;
+      const int r0 = w.row0[rank];
+      int64_t obase = 0;
+      const __nv_bfloat16* bias = nullptr;
+      uint32_t pre0[16], pre1[16];
+      if (r0 >= 0) {
+        if (MODE == TC_ROWS) obase = (int64_t)(r0 + lrow) * p.N + w.n0;
+        else obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
+        bias = (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
+        epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], chalf * (kBN2 / 2),
+                                (chalf + 1) * (kBN2 / 2), pre0, pre1);
+      }
       if (!empty) {
         mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14);
         tcgen05_fence_after();
       }
-      const int lrow = quarter * 32 + lane;
-      const int r0 = w.row0[rank];
-      if (r0 >= 0) {
-        int64_t obase;
-        if (MODE == TC_ROWS) obase = (int64_t)(r0 + lrow) * p.N + w.n0;
-        else obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
-        const __nv_bfloat16* bias =
-            (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
+      if (r0 >= 0)
         epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty,
-                               obase, bias, chalf * (kBN2 / 2), (chalf + 1) * (kBN2 / 2));
-      }
+                               obase, bias != nullptr, bias_strip[ew], chalf * (kBN2 / 2),
+                               (chalf + 1) * (kBN2 / 2), pre0, pre1);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
