@@ -30,7 +30,7 @@ namespace mole {
 constexpr int kBM = 128;          // rows of one UMMA (cta_group::1)
 constexpr int kBK = 64;           // K elements per stage = one 128-byte swizzle span of bf16
 constexpr int kUmmaK = 16;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr uint32_t kABytes = kBM * kBK * 2;
 
@@ -296,99 +296,101 @@ __device__ __forceinline__ float bf16_round(float v) {
   return __uint_as_float((__float_as_uint(v) + 0x7fffu + ((__float_as_uint(v) >> 16) & 1u)) & 0xffff0000u);
 }
 
-// 64 bytes of bf16 as packed words (two 32-byte vectors), and their conversion
-__device__ __forceinline__ void ld_packed32(const __nv_bfloat16* p, uint32_t (&w)[16]) {
-  uint32_t a[8], b[8];
-  ld_v8(p, a);
-  ld_v8(p + 16, b);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) { w[i] = a[i]; w[8 + i] = b[i]; }
-}
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&b);
 }
-__device__ __forceinline__ void st_packed32(__nv_bfloat16* p, const uint32_t (&w)[16]) {
-  uint32_t a[8], b[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) { a[i] = w[i]; b[i] = w[8 + i]; }
-  st_v8(p, a);
-  st_v8(p + 16, b);
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
 }
 
-// Global operands of the epilogue (pre-activation for dX2, old gradient for "+=") are fetched
-// two 32-column steps ahead, the first two before the accumulator is even ready: under the
-// TMA traffic of the main loop a global load takes microseconds, and a load-use chain per step
-// made the FC1 / dX2 epilogues several times longer than their arithmetic.  The bias slice of
-// the tile sits in a per-warp shared-memory strip, filled at the same early point.
+// The epilogue works in steps of 16 columns: one tcgen05.ld of 16 accumulator columns, the fused
+// arithmetic, one 32-byte store per output and thread.  Sixteen epilogue warps (four per
+// scheduler) share a tile: with eight, each warp issued once in ~6.5 cycles (TMEM and global
+// load latency, MUFU results) and the FC1 / dX2 epilogues took three times as long as the main
+// loop they should hide behind.  Global operands of the epilogue (pre-activation for dX2, old
+// gradient for "+=") are fetched two steps ahead, the first two before the accumulator is ready;
+// the bias slice of the tile sits in a per-warp shared-memory strip filled at the same point.
+constexpr int kEpiStep = 16;
+
 template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM>
 __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
                                               int64_t obase, const float* bias_s,
-                                              int c_begin, int c_end, uint32_t (&pre0)[16],
-                                              uint32_t (&pre1)[16]) {
+                                              int c_begin, int c_end, uint32_t (&pre0)[8],
+                                              uint32_t (&pre1)[8]) {
   constexpr bool kPrefetch = EPI == EPI_DACT || (EPI == EPI_WGRAD && ACCUM);
   const __nv_bfloat16* src = EPI == EPI_DACT ? p.aux : p.out0;
 #pragma unroll 1
-  for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+  for (int c0 = c_begin; c0 < c_end; c0 += 2 * kEpiStep) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int c = c0 + 32 * half;
-      uint32_t (&cur)[16] = half == 0 ? pre0 : pre1;
-      float v[32];
+      const int c = c0 + kEpiStep * half;
+      uint32_t (&cur)[8] = half == 0 ? pre0 : pre1;
+      uint32_t r[16];
       if (!empty) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c, r);
+        tmem_ld16(taddr + c, r);
         tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        for (int i = 0; i < 16; ++i) r[i] = 0u;
       }
-      uint32_t o[16];
+      uint32_t o[8];
       if (EPI == EPI_WGRAD) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = v[2 * i], hi = v[2 * i + 1];
+        for (int i = 0; i < 8; ++i) {
+          float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
           if (ACCUM) { lo += bf16_lo(cur[i]); hi += bf16_hi(cur[i]); }
           o[i] = pack_bf16(lo, hi);
         }
-        st_packed32(p.out0 + obase + c, o);
+        st_v8(p.out0 + obase + c, o);
       } else if (EPI == EPI_FC1) {
-        uint32_t h[16];
+        uint32_t h[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = v[2 * i], hi = v[2 * i + 1];
-          if (HAS_BIAS) { lo += bias_s[c - c_begin + 2 * i]; hi += bias_s[c - c_begin + 2 * i + 1]; }
+        for (int i = 0; i < 8; ++i) {
+          float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
+          if (HAS_BIAS) {
+            const float2 b = *reinterpret_cast<const float2*>(bias_s + (c - c_begin) + 2 * i);
+            lo += b.x; hi += b.y;
+          }
           // the saved pre-activation is bf16: the activation is taken of the rounded value so
           // that backward's act'(x1) and forward's act(x1) see the same x1
           o[i] = pack_bf16(lo, hi);
           h[i] = pack_bf16(act_fwd_t<ACT>(bf16_lo(o[i])), act_fwd_t<ACT>(bf16_hi(o[i])));
         }
-        st_packed32(p.out0 + obase + c, o);
-        st_packed32(p.out1 + obase + c, h);
+        st_v8(p.out0 + obase + c, o);
+        st_v8(p.out1 + obase + c, h);
       } else if (EPI == EPI_BIAS) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = v[2 * i], hi = v[2 * i + 1];
-          if (HAS_BIAS) { lo += bias_s[c - c_begin + 2 * i]; hi += bias_s[c - c_begin + 2 * i + 1]; }
+        for (int i = 0; i < 8; ++i) {
+          float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
+          if (HAS_BIAS) {
+            const float2 b = *reinterpret_cast<const float2*>(bias_s + (c - c_begin) + 2 * i);
+            lo += b.x; hi += b.y;
+          }
           o[i] = pack_bf16(lo, hi);
         }
-        st_packed32(p.out0 + obase + c, o);
+        st_v8(p.out0 + obase + c, o);
       } else if (EPI == EPI_DACT) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          o[i] = pack_bf16(v[2 * i] * act_grad_t<ACT, GBWD>(bf16_lo(cur[i])),
-                           v[2 * i + 1] * act_grad_t<ACT, GBWD>(bf16_hi(cur[i])));
-        st_packed32(p.out0 + obase + c, o);
+        for (int i = 0; i < 8; ++i)
+          o[i] = pack_bf16(__uint_as_float(r[2 * i]) * act_grad_t<ACT, GBWD>(bf16_lo(cur[i])),
+                           __uint_as_float(r[2 * i + 1]) * act_grad_t<ACT, GBWD>(bf16_hi(cur[i])));
+        st_v8(p.out0 + obase + c, o);
       } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-        st_packed32(p.out0 + obase + c, o);
+        for (int i = 0; i < 8; ++i)
+          o[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        st_v8(p.out0 + obase + c, o);
       }
-      if (kPrefetch && c + 64 < c_end) ld_packed32(src + obase + c + 64, cur);   // two steps ahead
+      if (kPrefetch && c + 2 * kEpiStep < c_end) ld_v8(src + obase + c + 2 * kEpiStep, cur);
     }
   }
 }
@@ -397,13 +399,13 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
 template <int MODE>
 __device__ __forceinline__ void epilogue_prefetch(const TcParams& p, int64_t obase,
                                                   const __nv_bfloat16* bias, float* bias_s,
-                                                  int c_begin, int c_end, uint32_t (&pre0)[16],
-                                                  uint32_t (&pre1)[16]) {
+                                                  int c_begin, int c_end, uint32_t (&pre0)[8],
+                                                  uint32_t (&pre1)[8]) {
   const bool need = MODE == TC_WGRAD ? p.accumulate != 0 : p.epi == EPI_DACT;
   if (need) {
     const __nv_bfloat16* src = MODE == TC_WGRAD ? p.out0 : p.aux;
-    ld_packed32(src + obase + c_begin, pre0);
-    ld_packed32(src + obase + c_begin + 32, pre1);
+    ld_v8(src + obase + c_begin, pre0);
+    ld_v8(src + obase + c_begin + kEpiStep, pre1);
   }
   if (MODE == TC_ROWS && bias != nullptr) {
     const int lane = threadIdx.x & 31;
@@ -416,8 +418,8 @@ __device__ __forceinline__ void epilogue_prefetch(const TcParams& p, int64_t oba
 template <int MODE>
 __device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t taddr, bool empty,
                                                  int64_t obase, bool has_bias, const float* bias_s,
-                                                 int c_begin, int c_end, uint32_t (&pre0)[16],
-                                                 uint32_t (&pre1)[16]) {
+                                                 int c_begin, int c_end, uint32_t (&pre0)[8],
+                                                 uint32_t (&pre1)[8]) {
 #define MOLE_EPI(E, A, G, B, C) \
   epilogue_loop<E, A, G, B, C>(p, taddr, empty, obase, bias_s, c_begin, c_end, pre0, pre1)
   if (MODE == TC_WGRAD) {
@@ -463,7 +465,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
-  __shared__ float bias_strip[kEpiWarps][128];      // per epilogue warp: bias of its 128 columns
+  __shared__ float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -566,7 +568,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------- epilogue -----------------------------------------
     const int ew = warp - 2;
     const int quarter = warp & 3;                     // TMEM lanes this warp may read
-    const int chalf = ew >> 2;                        // which half of the BN columns
+    const int cq = ew >> 2;                           // which quarter of the BN columns
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int item = blockIdx.x;; item += gridDim.x) {
@@ -581,15 +583,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       else obase = ((int64_t)slot * p.P + w.row0 + lrow) * p.N + w.n0;
       const __nv_bfloat16* bias =
           (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
-      uint32_t pre0[16], pre1[16];
-      epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], chalf * (BN / 2), (chalf + 1) * (BN / 2),
+      uint32_t pre0[8], pre1[8];
+      epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], cq * (BN / 4), (cq + 1) * (BN / 4),
                               pre0, pre1);
       if (!empty) {
         mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4);
         tcgen05_fence_after();
       }
       epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, obase,
-                             bias != nullptr, bias_strip[ew], chalf * (BN / 2), (chalf + 1) * (BN / 2),
+                             bias != nullptr, bias_strip[ew], cq * (BN / 4), (cq + 1) * (BN / 4),
                              pre0, pre1);
       if (!empty) {
         tcgen05_fence_before();
@@ -729,7 +731,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
-  __shared__ float bias_strip[kEpiWarps][128];      // per epilogue warp: bias of its 128 columns
+  __shared__ float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -841,7 +843,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------- epilogue (both CTAs) -----------------------------
     const int ew = warp - 2;
     const int quarter = warp & 3;
-    const int chalf = ew >> 2;
+    const int cq = ew >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int item = cluster_id;; item += n_clusters) {
@@ -853,13 +855,13 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int r0 = w.row0[rank];
       int64_t obase = 0;
       const __nv_bfloat16* bias = nullptr;
-      uint32_t pre0[16], pre1[16];
+      uint32_t pre0[8], pre1[8];
       if (r0 >= 0) {
         if (MODE == TC_ROWS) obase = (int64_t)(r0 + lrow) * p.N + w.n0;
         else obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
         bias = (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
-        epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], chalf * (kBN2 / 2),
-                                (chalf + 1) * (kBN2 / 2), pre0, pre1);
+        epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], cq * (kBN2 / 4),
+                                (cq + 1) * (kBN2 / 4), pre0, pre1);
       }
       if (!empty) {
         mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14);
@@ -867,8 +869,8 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
       if (r0 >= 0)
         epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty,
-                               obase, bias != nullptr, bias_strip[ew], chalf * (kBN2 / 2),
-                               (chalf + 1) * (kBN2 / 2), pre0, pre1);
+                               obase, bias != nullptr, bias_strip[ew], cq * (kBN2 / 4),
+                               (cq + 1) * (kBN2 / 4), pre0, pre1);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
