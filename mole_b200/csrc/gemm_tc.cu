@@ -317,23 +317,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // scheduler) share a tile: with eight, each warp issued once in ~6.5 cycles (TMEM and global
 // load latency, MUFU results) and the FC1 / dX2 epilogues took three times as long as the main
 // loop they should hide behind.  Global operands of the epilogue (pre-activation for dX2, old
-// gradient for "+=") are fetched two steps ahead, the first two before the accumulator is ready;
-// the bias slice of the tile sits in a per-warp shared-memory strip filled at the same point.
+// gradient for "+=") are all fetched before the wait for the accumulator, so their latency
+// overlaps the main loop; the bias slice of the tile sits in a per-warp shared-memory strip
+// filled at the same point.
 constexpr int kEpiStep = 16;
 
-template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM>
+template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM, int NSTEPS>
 __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
                                               int64_t obase, const float* bias_s,
-                                              int c_begin, int c_end, uint32_t (&pre0)[8],
-                                              uint32_t (&pre1)[8]) {
-  constexpr bool kPrefetch = EPI == EPI_DACT || (EPI == EPI_WGRAD && ACCUM);
-  const __nv_bfloat16* src = EPI == EPI_DACT ? p.aux : p.out0;
-#pragma unroll 1
-  for (int c0 = c_begin; c0 < c_end; c0 += 2 * kEpiStep) {
+                                              int c_begin, uint32_t (&pre)[NSTEPS][8]) {
+  {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int c = c0 + kEpiStep * half;
-      uint32_t (&cur)[8] = half == 0 ? pre0 : pre1;
+    for (int step = 0; step < NSTEPS; ++step) {
+      const int c = c_begin + kEpiStep * step;
+      uint32_t (&cur)[8] = pre[step];
       uint32_t r[16];
       if (!empty) {
         tmem_ld16(taddr + c, r);
@@ -390,38 +387,35 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
           o[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
         st_v8(p.out0 + obase + c, o);
       }
-      if (kPrefetch && c + 2 * kEpiStep < c_end) ld_v8(src + obase + c + 2 * kEpiStep, cur);
     }
   }
 }
 
 // Issued before the wait for the accumulator: the first two prefetch steps and the bias strip.
-template <int MODE>
+template <int MODE, int NSTEPS>
 __device__ __forceinline__ void epilogue_prefetch(const TcParams& p, int64_t obase,
                                                   const __nv_bfloat16* bias, float* bias_s,
-                                                  int c_begin, int c_end, uint32_t (&pre0)[8],
-                                                  uint32_t (&pre1)[8]) {
+                                                  int c_begin, uint32_t (&pre)[NSTEPS][8]) {
   const bool need = MODE == TC_WGRAD ? p.accumulate != 0 : p.epi == EPI_DACT;
   if (need) {
     const __nv_bfloat16* src = MODE == TC_WGRAD ? p.out0 : p.aux;
-    ld_v8(src + obase + c_begin, pre0);
-    ld_v8(src + obase + c_begin + kEpiStep, pre1);
+#pragma unroll
+    for (int step = 0; step < NSTEPS; ++step) ld_v8(src + obase + c_begin + kEpiStep * step, pre[step]);
   }
   if (MODE == TC_ROWS && bias != nullptr) {
     const int lane = threadIdx.x & 31;
     __syncwarp();                       // the strip's previous readers are done
-    for (int i = lane; i < c_end - c_begin; i += 32) bias_s[i] = __bfloat162float(bias[c_begin + i]);
+    for (int i = lane; i < NSTEPS * kEpiStep; i += 32) bias_s[i] = __bfloat162float(bias[c_begin + i]);
     __syncwarp();
   }
 }
 
-template <int MODE>
+template <int MODE, int NSTEPS>
 __device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t taddr, bool empty,
                                                  int64_t obase, bool has_bias, const float* bias_s,
-                                                 int c_begin, int c_end, uint32_t (&pre0)[8],
-                                                 uint32_t (&pre1)[8]) {
+                                                 int c_begin, uint32_t (&pre)[NSTEPS][8]) {
 #define MOLE_EPI(E, A, G, B, C) \
-  epilogue_loop<E, A, G, B, C>(p, taddr, empty, obase, bias_s, c_begin, c_end, pre0, pre1)
+  epilogue_loop<E, A, G, B, C, NSTEPS>(p, taddr, empty, obase, bias_s, c_begin, pre)
   if (MODE == TC_WGRAD) {
     if (p.accumulate) MOLE_EPI(EPI_WGRAD, 0, 0, false, true);
     else MOLE_EPI(EPI_WGRAD, 0, 0, false, false);
@@ -583,16 +577,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       else obase = ((int64_t)slot * p.P + w.row0 + lrow) * p.N + w.n0;
       const __nv_bfloat16* bias =
           (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
-      uint32_t pre0[8], pre1[8];
-      epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], cq * (BN / 4), (cq + 1) * (BN / 4),
-                              pre0, pre1);
+      constexpr int NSTEPS = BN / 4 / kEpiStep;
+      uint32_t pre[NSTEPS][8];
+      epilogue_prefetch<MODE, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (BN / 4), pre);
       if (!empty) {
         mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4);
         tcgen05_fence_after();
       }
-      epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, obase,
-                             bias != nullptr, bias_strip[ew], cq * (BN / 4), (cq + 1) * (BN / 4),
-                             pre0, pre1);
+      epilogue_columns<MODE, NSTEPS>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty,
+                                     obase, bias != nullptr, bias_strip[ew], cq * (BN / 4), pre);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -855,22 +848,22 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int r0 = w.row0[rank];
       int64_t obase = 0;
       const __nv_bfloat16* bias = nullptr;
-      uint32_t pre0[8], pre1[8];
+      constexpr int NSTEPS = kBN2 / 4 / kEpiStep;
+      uint32_t pre[NSTEPS][8];
       if (r0 >= 0) {
         if (MODE == TC_ROWS) obase = (int64_t)(r0 + lrow) * p.N + w.n0;
         else obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
         bias = (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
-        epilogue_prefetch<MODE>(p, obase, bias, bias_strip[ew], cq * (kBN2 / 4),
-                                (cq + 1) * (kBN2 / 4), pre0, pre1);
+        epilogue_prefetch<MODE, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (kBN2 / 4), pre);
       }
       if (!empty) {
         mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14);
         tcgen05_fence_after();
       }
       if (r0 >= 0)
-        epilogue_columns<MODE>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty,
-                               obase, bias != nullptr, bias_strip[ew], cq * (kBN2 / 4),
-                               (cq + 1) * (kBN2 / 4), pre0, pre1);
+        epilogue_columns<MODE, NSTEPS>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2,
+                                       empty, obase, bias != nullptr, bias_strip[ew], cq * (kBN2 / 4),
+                                       pre);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
