@@ -6,10 +6,12 @@ saying how to build it, and every call that returns a non-zero status raises.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "lib" / "libmole_b200.so"
+# MOLE_B200_LIB points at another build of the same library (kernel A/B comparisons)
+LIB_PATH = Path(os.environ.get("MOLE_B200_LIB") or _HERE / "lib" / "libmole_b200.so")
 
 MOLE_F32, MOLE_BF16 = 0, 1
 ACT_GELU, ACT_RELU = 0, 1

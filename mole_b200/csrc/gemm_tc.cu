@@ -391,18 +391,36 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
   }
 }
 
+// Epilogue variants.  Each kernel instantiation carries exactly one: a kernel that holds all of
+// them behind a run-time switch is several times larger and misses in the instruction cache.
+enum EpiVariant : int {
+  EV_FC1_GELU_B, EV_FC1_GELU, EV_FC1_RELU_B, EV_FC1_RELU,     // FC1 with / without bias
+  EV_DACT_GELU, EV_DACT_TANH, EV_DACT_RELU,                   // dX2
+  EV_BIAS, EV_STORE,                                          // FC2 with bias / FC2 without, dX
+  EV_WGRAD, EV_WGRAD_ACC
+};
+template <int EV> struct EvTraits {
+  static constexpr int epi = EV <= EV_FC1_RELU ? EPI_FC1 : EV <= EV_DACT_RELU ? EPI_DACT
+                             : EV == EV_BIAS ? EPI_BIAS : EV == EV_STORE ? EPI_STORE : EPI_WGRAD;
+  static constexpr int act = (EV == EV_FC1_RELU_B || EV == EV_FC1_RELU || EV == EV_DACT_RELU)
+                                 ? MOLE_ACT_RELU : MOLE_ACT_GELU;
+  static constexpr int gbwd = EV == EV_DACT_TANH ? MOLE_GELU_BWD_TANH : MOLE_GELU_BWD_EXACT;
+  static constexpr bool bias = EV == EV_FC1_GELU_B || EV == EV_FC1_RELU_B || EV == EV_BIAS;
+  static constexpr bool accum = EV == EV_WGRAD_ACC;
+  static constexpr bool prefetch = epi == EPI_DACT || accum;
+};
+
 // Issued before the wait for the accumulator: the first two prefetch steps and the bias strip.
-template <int MODE, int NSTEPS>
+template <int EV, int NSTEPS>
 __device__ __forceinline__ void epilogue_prefetch(const TcParams& p, int64_t obase,
                                                   const __nv_bfloat16* bias, float* bias_s,
                                                   int c_begin, uint32_t (&pre)[NSTEPS][8]) {
-  const bool need = MODE == TC_WGRAD ? p.accumulate != 0 : p.epi == EPI_DACT;
-  if (need) {
-    const __nv_bfloat16* src = MODE == TC_WGRAD ? p.out0 : p.aux;
+  if (EvTraits<EV>::prefetch) {
+    const __nv_bfloat16* src = EvTraits<EV>::epi == EPI_WGRAD ? p.out0 : p.aux;
 #pragma unroll
     for (int step = 0; step < NSTEPS; ++step) ld_v8(src + obase + c_begin + kEpiStep * step, pre[step]);
   }
-  if (MODE == TC_ROWS && bias != nullptr) {
+  if (EvTraits<EV>::bias) {
     const int lane = threadIdx.x & 31;
     __syncwarp();                       // the strip's previous readers are done
     for (int i = lane; i < NSTEPS * kEpiStep; i += 32) bias_s[i] = __bfloat162float(bias[c_begin + i]);
@@ -410,37 +428,7 @@ __device__ __forceinline__ void epilogue_prefetch(const TcParams& p, int64_t oba
   }
 }
 
-template <int MODE, int NSTEPS>
-__device__ __forceinline__ void epilogue_columns(const TcParams& p, uint32_t taddr, bool empty,
-                                                 int64_t obase, bool has_bias, const float* bias_s,
-                                                 int c_begin, uint32_t (&pre)[NSTEPS][8]) {
-#define MOLE_EPI(E, A, G, B, C) \
-  epilogue_loop<E, A, G, B, C, NSTEPS>(p, taddr, empty, obase, bias_s, c_begin, pre)
-  if (MODE == TC_WGRAD) {
-    if (p.accumulate) MOLE_EPI(EPI_WGRAD, 0, 0, false, true);
-    else MOLE_EPI(EPI_WGRAD, 0, 0, false, false);
-  } else if (p.epi == EPI_FC1) {
-    if (p.act == MOLE_ACT_GELU) {
-      if (has_bias) MOLE_EPI(EPI_FC1, MOLE_ACT_GELU, 0, true, false);
-      else MOLE_EPI(EPI_FC1, MOLE_ACT_GELU, 0, false, false);
-    } else {
-      if (has_bias) MOLE_EPI(EPI_FC1, MOLE_ACT_RELU, 0, true, false);
-      else MOLE_EPI(EPI_FC1, MOLE_ACT_RELU, 0, false, false);
-    }
-  } else if (p.epi == EPI_BIAS) {
-    if (has_bias) MOLE_EPI(EPI_BIAS, 0, 0, true, false);
-    else MOLE_EPI(EPI_BIAS, 0, 0, false, false);
-  } else if (p.epi == EPI_DACT) {
-    if (p.act == MOLE_ACT_RELU) MOLE_EPI(EPI_DACT, MOLE_ACT_RELU, 0, false, false);
-    else if (p.gelu_bwd == MOLE_GELU_BWD_TANH) MOLE_EPI(EPI_DACT, MOLE_ACT_GELU, MOLE_GELU_BWD_TANH, false, false);
-    else MOLE_EPI(EPI_DACT, MOLE_ACT_GELU, MOLE_GELU_BWD_EXACT, false, false);
-  } else {
-    MOLE_EPI(EPI_STORE, 0, 0, false, false);
-  }
-#undef MOLE_EPI
-}
-
-template <int MODE, bool B_KMAJOR, int BN, int STAGES>
+template <int MODE, bool B_KMAJOR, int BN, int STAGES, int EV>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ TcParams p) {
@@ -579,13 +567,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
       constexpr int NSTEPS = BN / 4 / kEpiStep;
       uint32_t pre[NSTEPS][8];
-      epilogue_prefetch<MODE, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (BN / 4), pre);
+      epilogue_prefetch<EV, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (BN / 4), pre);
       if (!empty) {
         mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4);
         tcgen05_fence_after();
       }
-      epilogue_columns<MODE, NSTEPS>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty,
-                                     obase, bias != nullptr, bias_strip[ew], cq * (BN / 4), pre);
+      using Ev = EvTraits<EV>;
+      epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
+          p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, obase, bias_strip[ew],
+          cq * (BN / 4), pre);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -707,7 +697,7 @@ __device__ __forceinline__ PairItem decode_pair(const TcParams& p, int item) {
   return w;
 }
 
-template <int MODE, bool B_KMAJOR, int STAGES>
+template <int MODE, bool B_KMAJOR, int STAGES, int EV>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ TcParams p) {
@@ -854,16 +844,19 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (MODE == TC_ROWS) obase = (int64_t)(r0 + lrow) * p.N + w.n0;
         else obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
         bias = (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
-        epilogue_prefetch<MODE, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (kBN2 / 4), pre);
+        epilogue_prefetch<EV, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (kBN2 / 4), pre);
       }
       if (!empty) {
         mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14);
         tcgen05_fence_after();
       }
       if (r0 >= 0)
-        epilogue_columns<MODE, NSTEPS>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2,
-                                       empty, obase, bias != nullptr, bias_strip[ew], cq * (kBN2 / 4),
-                                       pre);
+      {
+        using Ev = EvTraits<EV>;
+        epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
+            p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, obase,
+            bias_strip[ew], cq * (kBN2 / 4), pre);
+      }
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -975,12 +968,12 @@ static int sm_count() {
 
 bool tc_supported(int M, int F) { return M % 128 == 0 && F % 128 == 0 && M >= 128 && F >= 128; }
 
-template <int MODE, bool B_KMAJOR, int BN>
+template <int MODE, bool B_KMAJOR, int BN, int EV>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_items,
                      cudaStream_t st) {
   constexpr int STAGES = BN == 256 ? 4 : 6;
   constexpr size_t smem = (size_t)STAGES * (kABytes + BN * kBK * 2) + 1024;
-  auto kern = tc_gemm_kernel<MODE, B_KMAJOR, BN, STAGES>;
+  auto kern = tc_gemm_kernel<MODE, B_KMAJOR, BN, STAGES, EV>;
   static bool configured = false;
   if (!configured) {
     MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -997,12 +990,12 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
 }
 
 // Launch of the cta_group::2 kernel: grid = 2 x min(work units, clusters that can be resident).
-template <int MODE, bool B_KMAJOR>
+template <int MODE, bool B_KMAJOR, int EV>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_items,
                       cudaStream_t st) {
   constexpr int STAGES = 6;
   constexpr size_t smem = (size_t)STAGES * kStage2Bytes + 1024;
-  auto kern = tc2_gemm_kernel<MODE, B_KMAJOR, STAGES>;
+  auto kern = tc2_gemm_kernel<MODE, B_KMAJOR, STAGES, EV>;
   static int max_clusters = 0;
   if (max_clusters == 0) {
     MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -1081,16 +1074,27 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   const int max_items = a.sched.max_tiles * (a.N / BN);
   for (const void* q : {a.bias, a.aux, (const void*)a.out0, (const void*)a.out1})
     MOLE_REQUIRE((reinterpret_cast<uintptr_t>(q) & 31) == 0, "epilogue operand %p not 32-byte aligned", q);
-  if (pair) {
-    return a.w_nk ? launch_tc2<TC_ROWS, true>(ma, mb, p, max_items, st)
-                  : launch_tc2<TC_ROWS, false>(ma, mb, p, max_items, st);
+  // one kernel per (operand layout, tile shape, epilogue variant)
+#define MOLE_ROWS(KM, EV)                                                                    \
+  return pair ? launch_tc2<TC_ROWS, KM, EV>(ma, mb, p, max_items, st)                        \
+              : BN == 256 ? launch_tc<TC_ROWS, KM, 256, EV>(ma, mb, p, max_items, st)        \
+                          : launch_tc<TC_ROWS, KM, 128, EV>(ma, mb, p, max_items, st)
+  const bool relu = a.act == MOLE_ACT_RELU;
+  if (a.epi == EPI_FC1) {
+    MOLE_REQUIRE(a.w_nk, "FC1 reads its weights K-major");
+    if (a.bias) { if (relu) { MOLE_ROWS(true, EV_FC1_RELU_B); } else { MOLE_ROWS(true, EV_FC1_GELU_B); } }
+    if (relu) { MOLE_ROWS(true, EV_FC1_RELU); } else { MOLE_ROWS(true, EV_FC1_GELU); }
   }
-  if (a.w_nk) {
-    return BN == 256 ? launch_tc<TC_ROWS, true, 256>(ma, mb, p, max_items, st)
-                     : launch_tc<TC_ROWS, true, 128>(ma, mb, p, max_items, st);
+  if (a.epi == EPI_DACT) {
+    MOLE_REQUIRE(a.w_nk, "dX2 reads its weights K-major");
+    if (relu) { MOLE_ROWS(true, EV_DACT_RELU); }
+    if (a.gelu_bwd == MOLE_GELU_BWD_TANH) { MOLE_ROWS(true, EV_DACT_TANH); }
+    MOLE_ROWS(true, EV_DACT_GELU);
   }
-  return BN == 256 ? launch_tc<TC_ROWS, false, 256>(ma, mb, p, max_items, st)
-                   : launch_tc<TC_ROWS, false, 128>(ma, mb, p, max_items, st);
+  MOLE_REQUIRE(!a.w_nk, "FC2 / dX read their weights N-major");
+  if (a.epi == EPI_BIAS && a.bias) { MOLE_ROWS(false, EV_BIAS); }
+  MOLE_ROWS(false, EV_STORE);
+#undef MOLE_ROWS
 }
 
 int tc_wgrad(const WgradArgs& a, cudaStream_t st) {
@@ -1121,11 +1125,15 @@ int tc_wgrad(const WgradArgs& a, cudaStream_t st) {
   p.fault = device_fault_word();
   p.slot = a.gslot;
   MOLE_REQUIRE((reinterpret_cast<uintptr_t>(a.out) & 31) == 0, "gradient base not 32-byte aligned");
-  if (BN == 256 && a.P % 256 == 0 && !a.single_cta)
-    return launch_tc2<TC_WGRAD, true>(ma, mb, p, a.n_experts * (a.P / 256) * (a.Q / 256), st);
   const int max_items = a.n_experts * (a.P / kBM) * (a.Q / BN);
-  return BN == 256 ? launch_tc<TC_WGRAD, true, 256>(ma, mb, p, max_items, st)
-                   : launch_tc<TC_WGRAD, true, 128>(ma, mb, p, max_items, st);
+#define MOLE_WG(EV)                                                                               \
+  if (BN == 256 && a.P % 256 == 0 && !a.single_cta)                                               \
+    return launch_tc2<TC_WGRAD, true, EV>(ma, mb, p, a.n_experts * (a.P / 256) * (a.Q / 256), st); \
+  return BN == 256 ? launch_tc<TC_WGRAD, true, 256, EV>(ma, mb, p, max_items, st)                 \
+                   : launch_tc<TC_WGRAD, true, 128, EV>(ma, mb, p, max_items, st)
+  if (a.accumulate) { MOLE_WG(EV_WGRAD_ACC); }
+  MOLE_WG(EV_WGRAD);
+#undef MOLE_WG
 }
 
 }  // namespace mole
