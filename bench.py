@@ -55,6 +55,8 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per rank (debugging)")
     ap.add_argument("--ffn-backend", type=int, default=0,
                     help="0 default (CTA pairs), 1 CUDA cores, 2 one-CTA tcgen05 (for comparisons)")
+    ap.add_argument("--host-profile", action="store_true",
+                    help="cProfile of the host side of a few steps on rank 0, printed to stderr")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-report", action="store_true")
     return ap.parse_args()
@@ -219,6 +221,21 @@ def run_ours(args):
     fault = ops.device_fault()
     if fault:
         raise RuntimeError(f"device fault word = {fault}: a kernel's bounded wait ran out")
+
+    if args.host_profile and rank == 0:
+        import cProfile
+        import pstats
+        prof = cProfile.Profile()
+        prof.enable()
+        for _ in range(5):
+            step()
+        prof.disable()
+        torch.cuda.synchronize()
+        pstats.Stats(prof, stream=sys.stderr).sort_stats("cumulative").print_stats(45)
+    elif args.host_profile:
+        for _ in range(5):
+            step()
+    barrier()
 
     # ---- device-resident timed region --------------------------------------------------------
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
