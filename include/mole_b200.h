@@ -87,6 +87,30 @@ int mole_gate_route_fwd(const void* x, const void* wg, const float* logit_bias,
                         int32_t* first_hist, float* l_aux,
                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* mole_gate_route_fwd for callers that cannot allocate a workspace.  Some hosts of this library
+ * hand the whole of device memory to a pool of their own when they start (inference servers
+ * that reserve HBM up front, trainers whose caching allocator is frozen after warm-up), or call
+ * from a point where a driver allocation's implicit synchronisation would stall their other
+ * streams; they can neither ask the driver for the routing scratch nor lend the library an
+ * allocator.  This variant keeps the scratch in a fixed 4 MiB array inside the library's device
+ * image, which every GPU that loads the library holds until the process exits.  It allocates
+ * nothing (no cudaMalloc, no cudaFree, no allocating library routine).
+ *   - limit: (k + 1) * ceil(T / 64) * E * 4 bytes <= 4 MiB (e.g. 32768 tokens, 128 experts,
+ *     top-2, or 16384 tokens, 256 experts, top-3); larger problems get MOLE_ERR_UNSUPPORTED and
+ *     must use mole_gate_route_fwd.
+ *   - the first call on a device looks up the array's device address; make that call before
+ *     any stream capture.
+ *   - all calls share the one array and it keeps the last call's contents; nothing in it has to
+ *     start at zero (each call writes every entry it later reads), but two calls whose kernels
+ *     overlap on the GPU -- different streams, or different threads -- race on it.
+ * No counterpart in the reference. */
+int mole_gate_route_fwd_static(const void* x, const void* wg, const float* logit_bias,
+                               int64_t T, int32_t M, int32_t E, int32_t k, int32_t C,
+                               int32_t normalize_gate, int32_t dtype,
+                               float* scores, int32_t* idx, int32_t* slot, float* gates,
+                               int32_t* counts, int32_t* offsets, int32_t* perm,
+                               int32_t* first_hist, float* l_aux, void* stream);
+
 /* the same routing-index build from caller-provided scores [T,E] f32: identical scores in,
  * identical integers out */
 int mole_route_from_scores(const float* scores, int64_t T, int32_t E, int32_t k, int32_t C,

@@ -48,6 +48,8 @@ SIGNATURES = {
     "mole_route_workspace_bytes": (C.c_int, [_i64, _i32, _i32, _pi64]),
     "mole_gate_route_fwd": (C.c_int, [_p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
                                       _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _p]),
+    "mole_gate_route_fwd_static": (C.c_int, [_p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
+                                             _p, _p, _p, _p, _p, _p, _p, _p, _p, _p]),
     "mole_route_from_scores": (C.c_int, [_p, _i64, _i32, _i32, _i32, _i32,
                                          _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _p]),
     "mole_gate_bwd": (C.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _p, _p]),

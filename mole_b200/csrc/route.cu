@@ -13,6 +13,8 @@
 //
 // All integer outputs are produced by integer arithmetic in a fixed order: no atomics decide
 // a slot, so the result is a pure function of the scores.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mole {
@@ -648,6 +650,68 @@ extern "C" int mole_gate_route_fwd(const void* x, const void* wg, const float* l
            ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg)) & 15) == 0)
     rc = dispatch_gate_mma(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
   else if (dtype == MOLE_BF16)     // odd M or unaligned rows: CUDA-core gate
+    rc = dispatch_gate<__nv_bfloat16>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else
+    return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
+  if (rc) return rc;
+  return route_tail(w, T, E, k, C, idx, slot, gates, counts, offsets, perm, first_hist, l_aux, st);
+}
+
+// ---- the same gate + routing build for callers that cannot hand over a workspace -------------
+// The histogram / score-sum scratch lives in this fixed array inside the library's device image:
+// every GPU that loads the library holds these 4 MiB until the process exits.
+constexpr int64_t kStaticScratchBytes = 4 << 20;
+static __device__ __align__(256) unsigned char g_route_scratch[kStaticScratchBytes];
+
+// `g_route_scratch` in host code is only a handle for the runtime, not a device address: the
+// address each device gave the array is looked up once per device (with that device current)
+// and cached.
+static int static_scratch(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* ptrs[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  MOLE_CUDA_OK(cudaGetDevice(&dev));
+  MOLE_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    MOLE_CUDA_OK(cudaGetSymbolAddress(&p, g_route_scratch));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return MOLE_OK;
+}
+
+extern "C" int mole_gate_route_fwd_static(const void* x, const void* wg, const float* logit_bias,
+                                          int64_t T, int32_t M, int32_t E, int32_t k, int32_t C,
+                                          int32_t normalize_gate, int32_t dtype, float* scores,
+                                          int32_t* idx, int32_t* slot, float* gates,
+                                          int32_t* counts, int32_t* offsets, int32_t* perm,
+                                          int32_t* first_hist, float* l_aux, void* stream) {
+  if (int rc = check_route_args(T, E, k, C)) return rc;
+  MOLE_REQUIRE(x && wg && scores && idx && slot && gates && counts && offsets && perm &&
+               first_hist && l_aux, "null pointer argument");
+  MOLE_REQUIRE(M >= 1, "M=%d", M);
+  const int64_t need = route_ws_bytes(T, E, k);
+  if (need > kStaticScratchBytes)
+    return fail(MOLE_ERR_UNSUPPORTED,
+                "T=%lld tokens x E=%d experts x top-%d needs %lld bytes of routing scratch, the "
+                "built-in scratch holds %lld: use mole_gate_route_fwd with a caller workspace",
+                (long long)T, E, k, (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // every scratch entry the scan reads is written by the gate kernel of this call first, so
+  // nothing has to be cleared although the array keeps the previous call's contents
+  RouteWs w = carve(scratch, T, E, k);
+  int rc;
+  if (dtype == MOLE_F32)
+    rc = dispatch_gate<float>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else if (dtype == MOLE_BF16 && M % kMmaKC == 0 &&
+           ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg)) & 15) == 0)
+    rc = dispatch_gate_mma(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else if (dtype == MOLE_BF16)
     rc = dispatch_gate<__nv_bfloat16>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
   else
     return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);

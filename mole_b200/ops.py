@@ -103,6 +103,26 @@ def gate_route(x: torch.Tensor, wg: torch.Tensor, k: int, cap: int,
     return plan
 
 
+def gate_route_static(x: torch.Tensor, wg: torch.Tensor, k: int, cap: int,
+                      logit_bias: Optional[torch.Tensor] = None, normalize: bool = False,
+                      plan: Optional[RoutePlan] = None) -> RoutePlan:
+    """``gate_route`` through the entry point that allocates nothing: the routing scratch is the
+    library's built-in 4 MiB array.  For hosts that have given all device memory to their own
+    pool or must not trigger a driver allocation; pass a pre-allocated ``plan`` to keep this
+    wrapper allocation-free too.  Calls that overlap on the GPU race on the shared scratch."""
+    T, M = x.shape
+    E = wg.shape[0]
+    if wg.shape[1] != M or wg.dtype != x.dtype:
+        raise ValueError("gate weight must be [E, M] in the dtype of x")
+    if plan is None:
+        plan = _alloc_plan(T, E, k, cap, normalize, x.device)
+    check(lib.mole_gate_route_fwd_static(
+        _ptr(x), _ptr(wg), _ptr(logit_bias), T, M, E, k, cap, int(normalize), _dt(x),
+        _ptr(plan.scores), _ptr(plan.idx), _ptr(plan.slot), _ptr(plan.gates), _ptr(plan.counts),
+        _ptr(plan.offsets), _ptr(plan.perm), _ptr(plan.first_hist), _ptr(plan.l_aux), _stream()))
+    return plan
+
+
 def route_from_scores(scores: torch.Tensor, k: int, cap: int, normalize: bool = False) -> RoutePlan:
     """Routing-index build from given fp32 scores (identical scores in, identical integers out)."""
     if scores.dtype != torch.float32:
