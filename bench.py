@@ -218,6 +218,25 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # A freshly started box can spend its first seconds paging the image in, and the host then
+    # enqueues slower than the GPU executes.  Keep warming (untimed, at most 60 more steps) until
+    # a synchronised step is within 15 % of the best one seen; every rank runs the same count.
+    best, extra = float("inf"), 0
+    while extra < 60:
+        t0 = time.perf_counter()
+        step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        extra += 1
+        settled = dt <= 1.15 * best and extra >= 3
+        best = min(best, dt)
+        if world > 1:
+            flag = torch.tensor([0 if settled else 1], device=device)
+            dist.all_reduce(flag)
+            settled = flag.item() == 0
+        if settled:
+            break
+    barrier()
     fault = ops.device_fault()
     if fault:
         raise RuntimeError(f"device fault word = {fault}: a kernel's bounded wait ran out")
@@ -336,7 +355,7 @@ def run_ours(args):
                    "l2": "per-step working set (weights, gradients, activations) is >10 GB, far above "
                          "the 126 MB L2, so no flush is needed between iterations"},
         "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": n1 - n0,
-        "host_enqueue_ms_per_step": host_ms,
+        "host_enqueue_ms_per_step": host_ms, "warmup_settling_steps": extra,
     }
     plan = m.last_plan
     pairs = int(plan.counts.sum().item())
