@@ -49,6 +49,13 @@ bool profile_enabled();
 void profile_begin(cudaStream_t st, int kind);
 void profile_end(cudaStream_t st);
 
+// bf16 backward products of the gate on warp-level tensor cores (gate_mma.cu); need M % 128 == 0
+int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t* slot,
+                            const float* dlogits, const void* wg, int64_t T, int M, int E, int k,
+                            int C, int Cs, void* dx, cudaStream_t st);
+int launch_gate_wgrad_mma(const float* dlogits, const void* x, int64_t T, int M, int E, float* dwg,
+                          cudaStream_t st);
+
 // device-side fault word: kernels with bounded waits record where they gave up
 int32_t* device_fault_word();   // lazily allocated once per process (4 bytes), zeroed
 

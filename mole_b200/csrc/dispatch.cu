@@ -261,6 +261,10 @@ extern "C" int mole_dispatch_bwd(const void* ddisp, const int32_t* idx, const in
   MOLE_REQUIRE((dlogits == nullptr) == (wg == nullptr), "dlogits and wg must be given together");
   MOLE_REQUIRE(C >= 1 && C <= Cs, "capacity %d not in [1, Cs=%d]", C, Cs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MOLE_BF16 && dlogits != nullptr && M % 128 == 0 &&
+      ((reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(ddisp) |
+        reinterpret_cast<uintptr_t>(dx)) & 15) == 0)
+    return launch_dispatch_bwd_mma(ddisp, idx, slot, dlogits, wg, T_, M, E, k, C, Cs, dx, st);
   dim3 grid((M + kDbCols - 1) / kDbCols, (unsigned)((T_ + kDbTok - 1) / kDbTok));
   MOLE_BY_DTYPE(dtype, dispatch_bwd_kernel<T><<<grid, 256, 0, st>>>(
       static_cast<const T*>(ddisp), idx, slot, dlogits, static_cast<const T*>(wg), T_, M, E, k, C,

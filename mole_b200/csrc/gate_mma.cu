@@ -1,0 +1,262 @@
+// bf16 backward products of the gate on the warp-level tensor-core path:
+//
+//   dispatch_bwd_mma_kernel   dx[t, :] = sum_j kept * ddisp[row(t, j), :] + dlogits[t, :] @ Wg
+//   gate_wgrad_mma_kernel     dWg[e, :] += sum_t dlogits[t, e] * x[t, :]
+//
+// Both contain a product with one tiny dimension (E <= 256 experts).  On CUDA cores they were
+// FMA-bound at 5-8 % of the HBM rate they should run at; a tcgen05 pipeline does not pay for a
+// 64-wide contraction.  mma.sync m16n8k16 with fp32 accumulation does.  dlogits is fp32: it
+// enters the bf16 MMA as hi + lo (two bf16 terms, two MMAs), which keeps 16 mantissa bits; the
+// other operand (Wg, x) is bf16 already.  The fp32 layer keeps the CUDA-core kernels.
+#include "common.cuh"
+
+namespace mole {
+
+__device__ __forceinline__ void ldsm_x4(const void* p, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(const void* p, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+  hi = __float2bfloat16_rn(v);
+  lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+constexpr int kGmTok = 64;       // tokens per MMA tile
+constexpr int kGmCols = 128;     // columns per block
+constexpr int kGmLdb = kGmCols + 8;
+
+// ---- dx = gather(ddisp) + dlogits @ Wg ------------------------------------------------------
+// Block: 8 warps, 64 tokens x 128 columns.  Warp w: tokens 16 (w & 3) .., columns 64 (w >> 2) ..
+__global__ void __launch_bounds__(256)
+dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* __restrict__ idx,
+                        const int32_t* __restrict__ slot, const float* __restrict__ dlogits,
+                        const __nv_bfloat16* __restrict__ wg, int64_t Ttok, int M, int E, int EP,
+                        int k, int C, int Cs, __nv_bfloat16* __restrict__ dx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int lda = EP + 8;
+  __nv_bfloat16* a_hi = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [64][lda]
+  __nv_bfloat16* a_lo = a_hi + kGmTok * lda;                              // [64][lda]
+  __nv_bfloat16* bs = a_lo + kGmTok * lda;                                // [EP][136]
+  float* cs = reinterpret_cast<float*>(smem_raw);                         // [64][132], after the MMAs
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t tok0 = (int64_t)blockIdx.y * kGmTok;
+  const int col0 = blockIdx.x * kGmCols;
+
+  for (int i = tid; i < kGmTok * EP; i += 256) {
+    const int tl = i / EP, e = i - tl * EP;
+    const int64_t t = tok0 + tl;
+    const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
+    split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+  }
+  for (int i = tid; i < EP * (kGmCols / 8); i += 256) {
+    const int e = i >> 4, v = i & 15;
+    uint4 w = make_uint4(0, 0, 0, 0);
+    if (e < E) w = *reinterpret_cast<const uint4*>(wg + (int64_t)e * M + col0 + v * 8);
+    *reinterpret_cast<uint4*>(bs + e * kGmLdb + v * 8) = w;
+  }
+  __syncthreads();
+
+  const int mt = warp & 3, nh = warp >> 2;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int ks = 0; ks < EP / 16; ++ks) {
+    uint32_t ah[4], al[4];
+    const int arow = mt * 16 + (lane & 15), acol = ks * 16 + (lane >> 4) * 8;
+    ldsm_x4(a_hi + arow * lda + acol, ah);
+    ldsm_x4(a_lo + arow * lda + acol, al);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      // four 8x8 blocks of the [k][n] tile: (k 0-7, n 0-7) (k 8-15, n 0-7) (k 0-7, n 8-15) ...
+      const int krow = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int ncol = nh * 64 + p * 16 + (lane >> 4) * 8;
+      uint32_t b[4];
+      ldsm_x4_trans(bs + krow * kGmLdb + ncol, b);
+      mma16816(acc[2 * p], ah, b[0], b[1]);
+      mma16816(acc[2 * p], al, b[0], b[1]);
+      mma16816(acc[2 * p + 1], ah, b[2], b[3]);
+      mma16816(acc[2 * p + 1], al, b[2], b[3]);
+    }
+  }
+  __syncthreads();                                  // operand tiles are dead: reuse as the C tile
+  constexpr int ldc = kGmCols + 4;
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      cs[(mt * 16 + g + (j >> 1) * 8) * ldc + nh * 64 + i * 8 + 2 * q + (j & 1)] = acc[i][j];
+  __syncthreads();
+
+  // gather pass: a thread owns 8 consecutive columns of one token
+#pragma unroll
+  for (int it = 0; it < kGmTok * (kGmCols / 8) / 256; ++it) {
+    const int w = tid + 256 * it;
+    const int tl = w >> 4, c8 = (w & 15) * 8;
+    const int64_t t = tok0 + tl;
+    if (t >= Ttok) continue;
+    float v[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) v[c] = cs[tl * ldc + c8 + c];
+    for (int j = 0; j < k && ddisp != nullptr; ++j) {
+      const int s = slot[t * k + j];
+      if (s >= C) continue;
+      const int64_t r = (int64_t)idx[t * k + j] * Cs + s;
+      float d[8];
+      Vec16<__nv_bfloat16>::load(ddisp + r * M + col0 + c8, d);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] += d[c];
+    }
+    Vec16<__nv_bfloat16>::store(dx + t * M + col0 + c8, v);
+  }
+}
+
+int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t* slot,
+                            const float* dlogits, const void* wg, int64_t T, int M, int E, int k,
+                            int C, int Cs, void* dx, cudaStream_t st) {
+  const int EP = (E + 15) / 16 * 16;
+  const size_t ops = (size_t)(2 * kGmTok * (EP + 8) + EP * kGmLdb) * 2;
+  const size_t ctile = (size_t)kGmTok * (kGmCols + 4) * 4;
+  const size_t smem = ops > ctile ? ops : ctile;
+  static size_t configured = 0;
+  if (smem > configured) {
+    MOLE_CUDA_OK(cudaFuncSetAttribute(dispatch_bwd_mma_kernel,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  dim3 grid(M / kGmCols, (unsigned)((T + kGmTok - 1) / kGmTok));
+  dispatch_bwd_mma_kernel<<<grid, 256, smem, st>>>(
+      static_cast<const __nv_bfloat16*>(ddisp), idx, slot, dlogits,
+      static_cast<const __nv_bfloat16*>(wg), T, M, E, EP, k, C, Cs, static_cast<__nv_bfloat16*>(dx));
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+// ---- dWg += dlogits^T @ x -------------------------------------------------------------------
+// Block: 8 warps, all experts x 128 columns, 256 tokens in four sub-chunks of 64; partial sums
+// go to the fp32 accumulator with atomics (split over tokens).  Warp w: columns 64 (w >> 2) ..,
+// expert tiles (w & 3) + 4 i.  Both operands sit in shared memory token-major ([k][m], [k][n]),
+// so both fragments come from transposing ldmatrix loads.
+constexpr int kWgChunk = 256;
+template <int MT>                       // expert tiles of 16 per warp: EP <= 64 * MT
+__global__ void __launch_bounds__(256)
+gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ x,
+                      int64_t Ttok, int M, int E, int EP, float* __restrict__ dwg) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int lda = EP + 8;
+  __nv_bfloat16* a_hi = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [64 tok][lda]
+  __nv_bfloat16* a_lo = a_hi + kGmTok * lda;
+  __nv_bfloat16* xs = a_lo + kGmTok * lda;                                // [64 tok][136]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int mg = warp & 3, nh = warp >> 2;
+  const int col0 = blockIdx.x * kGmCols;
+  const int64_t chunk0 = (int64_t)blockIdx.y * kWgChunk;
+  float acc[MT][8][4];
+#pragma unroll
+  for (int a = 0; a < MT; ++a)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[a][i][j] = 0.f;
+
+  for (int sub = 0; sub < kWgChunk / kGmTok; ++sub) {
+    const int64_t tok0 = chunk0 + sub * kGmTok;
+    if (tok0 >= Ttok) break;                                  // block-uniform
+    for (int i = tid; i < kGmTok * EP; i += 256) {
+      const int tl = i / EP, e = i - tl * EP;
+      const int64_t t = tok0 + tl;
+      const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
+      split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+    }
+    for (int i = tid; i < kGmTok * (kGmCols / 8); i += 256) {
+      const int tl = i >> 4, v = i & 15;
+      const int64_t t = tok0 + tl;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (t < Ttok) w = *reinterpret_cast<const uint4*>(x + t * M + col0 + v * 8);
+      *reinterpret_cast<uint4*>(xs + tl * kGmLdb + v * 8) = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < kGmTok / 16; ++ks) {
+      uint32_t b[4][4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const int krow = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+        const int ncol = nh * 64 + p * 16 + (lane >> 4) * 8;
+        ldsm_x4_trans(xs + krow * kGmLdb + ncol, b[p]);
+      }
+#pragma unroll
+      for (int a = 0; a < MT; ++a) {
+        const int m0 = (mg + 4 * a) * 16;
+        if (m0 >= EP) continue;                               // warp-uniform
+        // A[m][k] from [k][m] storage: blocks (m 0-7, k 0-7) (m 8-15, k 0-7) (m 0-7, k 8-15) ...
+        const int krow = ks * 16 + (lane >> 4) * 8 + (lane & 7);
+        const int mcol = m0 + ((lane >> 3) & 1) * 8;
+        uint32_t ah[4], al[4];
+        ldsm_x4_trans(a_hi + krow * lda + mcol, ah);
+        ldsm_x4_trans(a_lo + krow * lda + mcol, al);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          mma16816(acc[a][2 * p], ah, b[p][0], b[p][1]);
+          mma16816(acc[a][2 * p], al, b[p][0], b[p][1]);
+          mma16816(acc[a][2 * p + 1], ah, b[p][2], b[p][3]);
+          mma16816(acc[a][2 * p + 1], al, b[p][2], b[p][3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int a = 0; a < MT; ++a)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = (mg + 4 * a) * 16 + g + (j >> 1) * 8;
+        const int m = col0 + nh * 64 + i * 8 + 2 * q + (j & 1);
+        if (e < E) atomicAdd(&dwg[(int64_t)e * M + m], acc[a][i][j]);
+      }
+}
+
+template <int MT>
+static int launch_wgrad_mma_t(const float* dlogits, const void* x, int64_t T, int M, int E, int EP,
+                              float* dwg, cudaStream_t st) {
+  const size_t smem = (size_t)(2 * kGmTok * (EP + 8) + kGmTok * kGmLdb) * 2;
+  auto kern = gate_wgrad_mma_kernel<MT>;
+  static size_t configured = 0;
+  if (smem > configured) {
+    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  dim3 grid(M / kGmCols, (unsigned)((T + kWgChunk - 1) / kWgChunk));
+  kern<<<grid, 256, smem, st>>>(dlogits, static_cast<const __nv_bfloat16*>(x), T, M, E, EP, dwg);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+int launch_gate_wgrad_mma(const float* dlogits, const void* x, int64_t T, int M, int E, float* dwg,
+                          cudaStream_t st) {
+  const int EP = (E + 15) / 16 * 16;
+  if (EP <= 64) return launch_wgrad_mma_t<1>(dlogits, x, T, M, E, EP, dwg, st);
+  if (EP <= 128) return launch_wgrad_mma_t<2>(dlogits, x, T, M, E, EP, dwg, st);
+  return launch_wgrad_mma_t<4>(dlogits, x, T, M, E, EP, dwg, st);
+}
+
+}  // namespace mole

@@ -773,6 +773,8 @@ extern "C" int mole_gate_wgrad(const float* dlogits, const void* x, int64_t T, i
   if (int rc = check_route_args(T, E, 1, 1)) return rc;
   MOLE_REQUIRE(dlogits && x && dwg32, "null pointer argument");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MOLE_BF16 && M % 128 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
+    return launch_gate_wgrad_mma(dlogits, x, T, M, E, dwg32, st);
   if (dtype == MOLE_F32) return launch_wgrad<float>(dlogits, x, T, M, E, dwg32, st);
   if (dtype == MOLE_BF16) return launch_wgrad<__nv_bfloat16>(dlogits, x, T, M, E, dwg32, st);
   return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
