@@ -162,6 +162,10 @@ int mole_dispatch_bwd(const void* ddisp, const int32_t* idx, const int32_t* slot
  * (MOLE/cpp/core.cpp:344-367, 381-456, 457-514), the re-layouts either side of them
  * (core.cpp:233, 240, 291, 320) and the GELU' kernel (MOLE/cpp/gelu.cu:16-58).
  *
+ * The workspace is scratch of one call (tile schedule; with n_src > 1 on the tensor-core path
+ * also the packed copies of x and dout and the row map).  x1, h and dx1 are private to the
+ * fwd/bwd pair: backward must be called with the descriptor fields n_src, Cs, L, dtype, backend,
+ * compact that forward used.
  * Rows are capacity-strided: chunk c = w*L + l holds what source rank w sent for local
  * expert l (n_src = 1 on a single GPU).  counts [n_src*L] i32 lives on the device; no
  * host synchronisation happens.  Weights are batched [n_slots, F, M] (W1 and W2 both, as in
@@ -181,6 +185,9 @@ typedef struct {
   int32_t n_slots;        /* leading extent of the weight arrays */
   int32_t n_grad_slots;   /* leading extent of the gradient arrays (0: same as n_slots) */
   int32_t accumulate;     /* backward: weight grads += instead of = (core.cpp:457-514) */
+  int32_t compact;        /* 0: with n_src > 1 the tensor-core path packs each expert's rows of all
+                             sources into one run before the GEMMs (x1, h, dx1 are then in that
+                             layout); 2: never pack */
   int32_t backend;        /* 0: tensor cores for bf16 (CTA pairs, cta_group::2, where the shape
                              allows), CUDA cores for fp32 (the fp32 layer needs fp32-exact
                              products); 1: CUDA-core kernels also for bf16, used to bisect

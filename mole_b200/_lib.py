@@ -30,7 +30,7 @@ class MoleError(RuntimeError):
 class FfnDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "dtype", "act", "gelu_bwd", "M", "F", "L", "n_src", "Cs", "e_begin", "e_end",
-        "n_slots", "n_grad_slots", "accumulate", "backend")]
+        "n_slots", "n_grad_slots", "accumulate", "compact", "backend")]
 
 
 _p, _i32, _i64 = C.c_void_p, C.c_int32, C.c_int64

@@ -51,6 +51,42 @@ static int single_cta(const mole_ffn_desc* d) {
   return d->n_src * (d->Cs / kTileRows) < 12;
 }
 
+// With several source ranks per expert the tensor-core path first packs each expert's rows of
+// all sources into one run (gemm_simt.cu, "per-expert compaction"): x1, h and dX1 then live in that
+// layout, FC2 / dX scatter their output rows back to the (source, expert) chunks.  `desc.compact`
+// = 2 switches it off (comparisons).
+static bool compacting(const mole_ffn_desc* d) { return use_tc(d) && d->n_src > 1 && d->compact != 2; }
+
+struct Workspace {
+  Schedule sched;
+  int32_t* rowmap;   // [rows_total]
+  void* buf_a;       // [rows_total, M]
+  void* buf_b;       // [rows_total, M]
+};
+static int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
+static int64_t workspace_bytes_of(const mole_ffn_desc* d) {
+  int64_t b = align256(schedule_bytes(d->L, d->n_src, d->Cs));
+  if (compacting(d)) {
+    const int64_t rows = (int64_t)d->L * d->n_src * d->Cs;
+    b += align256(rows * 4) + 2 * align256(rows * d->M * 2);
+  }
+  return b;
+}
+static Workspace carve_workspace(const mole_ffn_desc* d, void* ws) {
+  Workspace w{};
+  w.sched = carve_schedule(ws, d->L, d->n_src, d->Cs);
+  if (compacting(d)) {
+    const int64_t rows = (int64_t)d->L * d->n_src * d->Cs;
+    char* p = static_cast<char*>(ws) + align256(schedule_bytes(d->L, d->n_src, d->Cs));
+    w.rowmap = reinterpret_cast<int32_t*>(p);
+    p += align256(rows * 4);
+    w.buf_a = p;
+    p += align256(rows * d->M * 2);
+    w.buf_b = p;
+  }
+  return w;
+}
+
 static int row_gemm(const mole_ffn_desc* d, const RowGemmArgs& a, cudaStream_t st) {
   return use_tc(d) ? tc_row_gemm(a, st) : simt_row_gemm(d->dtype, a, st);
 }
@@ -65,7 +101,7 @@ using namespace mole;
 extern "C" int mole_ffn_workspace_bytes(const mole_ffn_desc* d, int64_t* bytes) {
   if (int rc = check_desc(d)) return rc;
   MOLE_REQUIRE(bytes != nullptr, "bytes is null");
-  *bytes = schedule_bytes(d->L, d->n_src, d->Cs);
+  *bytes = workspace_bytes_of(d);
   return MOLE_OK;
 }
 
@@ -76,11 +112,20 @@ extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
   if (int rc = check_desc(d)) return rc;
   MOLE_REQUIRE(counts && x && w1 && b1 && w2 && b2 && x1 && h && out && workspace,
                "null pointer argument");
-  MOLE_REQUIRE(workspace_bytes >= schedule_bytes(d->L, d->n_src, d->Cs), "workspace too small");
+  MOLE_REQUIRE(workspace_bytes >= workspace_bytes_of(d), "workspace too small");
   if (d->e_begin == d->e_end) return MOLE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  Schedule s = carve_schedule(workspace, d->L, d->n_src, d->Cs);
-  if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+  const Workspace wk = carve_workspace(d, workspace);
+  const Schedule s = wk.sched;
+  const bool compact = compacting(d);
+  if (compact) {
+    if (int rc = build_schedule_compact(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+    if (int rc = compact_gather(d->dtype, x, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, d->M,
+                                wk.buf_a, wk.rowmap, st)) return rc;
+    x = wk.buf_a;
+  } else {
+    if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+  }
 
   RowGemmArgs a{};
   if (int rc = fill_slots(a.wslot, d, slot_of_expert, d->n_slots)) return rc;
@@ -100,6 +145,7 @@ extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
   // FC2: [rows, F] x W2_e ([F, M] read as [K=F][N=M])
   a.A = h; a.W = w2; a.w_nk = 0; a.N = d->M; a.K = d->F; a.bias = b2;
   a.out0 = out; a.out1 = nullptr; a.epi = EPI_BIAS;
+  a.rowmap = compact ? wk.rowmap : nullptr;          // back to the (source, expert) chunks
   return row_gemm(d, a, st);
 }
 
@@ -112,11 +158,23 @@ extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
   if (int rc = check_desc(d)) return rc;
   MOLE_REQUIRE(counts && dout && x && x1 && h && w1 && w2 && dx1 && gw1 && gb1 && gw2 && gb2 &&
                workspace, "null pointer argument");
-  MOLE_REQUIRE(workspace_bytes >= schedule_bytes(d->L, d->n_src, d->Cs), "workspace too small");
+  MOLE_REQUIRE(workspace_bytes >= workspace_bytes_of(d), "workspace too small");
   if (d->e_begin == d->e_end) return MOLE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  Schedule s = carve_schedule(workspace, d->L, d->n_src, d->Cs);
-  if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+  const Workspace wk = carve_workspace(d, workspace);
+  const Schedule s = wk.sched;
+  const bool compact = compacting(d);
+  if (compact) {      // x1, h come compacted from forward; x and dout are packed the same way here
+    if (int rc = build_schedule_compact(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+    if (int rc = compact_gather(d->dtype, x, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, d->M,
+                                wk.buf_a, wk.rowmap, st)) return rc;
+    if (int rc = compact_gather(d->dtype, dout, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end,
+                                d->M, wk.buf_b, nullptr, st)) return rc;
+    x = wk.buf_a;
+    dout = wk.buf_b;
+  } else {
+    if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
+  }
   const int64_t total_rows = (int64_t)d->L * d->n_src * d->Cs;
   const int n_experts = d->e_end - d->e_begin;
 
@@ -157,6 +215,7 @@ extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
   if (dx != nullptr) {
     a.A = dx1; a.W = w1; a.w_nk = 0; a.N = d->M; a.K = d->F; a.bias = nullptr; a.aux = nullptr;
     a.out0 = dx; a.out1 = nullptr; a.epi = EPI_STORE;
+    a.rowmap = compact ? wk.rowmap : nullptr;
     if (int rc = row_gemm(d, a, st)) return rc;
   }
   return MOLE_OK;

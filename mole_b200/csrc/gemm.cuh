@@ -30,6 +30,7 @@ struct RowGemmArgs {
   int epi, act, gelu_bwd;
   int e_begin, n_experts;   // experts covered by the schedule
   int single_cta;           // tensor cores: keep to the one-CTA kernel (A/B comparisons)
+  const int32_t* rowmap;    // tensor cores, FC2 / dX: scatter output rows (-1 = drop), or null
   Schedule sched;
   SlotMap wslot;
 };
@@ -62,6 +63,10 @@ struct ColsumArgs {
 
 int build_schedule(const int32_t* counts, int L, int n_src, int Cs, int e_begin, int e_end,
                    Schedule s, cudaStream_t st);
+int build_schedule_compact(const int32_t* counts, int L, int n_src, int Cs, int e_begin, int e_end,
+                           Schedule s, cudaStream_t st);
+int compact_gather(int dtype, const void* src, const int32_t* counts, int L, int n_src, int Cs,
+                   int e_begin, int e_end, int width, void* dst, int32_t* rowmap, cudaStream_t st);
 int64_t schedule_bytes(int L, int n_src, int Cs);
 Schedule carve_schedule(void* ws, int L, int n_src, int Cs);
 

@@ -79,6 +79,109 @@ int build_schedule(const int32_t* counts, int L, int n_src, int Cs, int e_begin,
   return MOLE_OK;
 }
 
+// ---- per-expert compaction (several source ranks per expert) -------------------------------
+// The exchange leaves expert l's rows in n_src chunks [w][l][Cs], each with its own ragged last
+// tile.  The compacted layout is [l][n_src * Cs]: the expert's valid rows of all sources packed at
+// the front of its region (source order), zero rows up to the next multiple of 128.  One ragged
+// tile per expert instead of one per (source, expert): at 8 source ranks x ~256 rows that is 17
+// tiles instead of 20-24.  The region of an expert does not depend on which experts a call covers.
+__global__ void __launch_bounds__(256)
+schedule_compact_kernel(const int32_t* __restrict__ counts, int L, int n_src, int Cs, int e_begin,
+                        int e_end, Schedule s) {
+  __shared__ int tiles[256];
+  const int tid = threadIdx.x;
+  const int ne = e_end - e_begin;
+  int nt = 0;
+  if (tid < ne) {
+    int rows = 0;
+    for (int w = 0; w < n_src; ++w) rows += min(counts[w * L + e_begin + tid], Cs);
+    nt = (rows + kTileRows - 1) / kTileRows;
+  }
+  tiles[tid] = nt;
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0, pairs = 0;
+    for (int i = 0; i < ne; ++i) {
+      s.expert_tile_start[i] = run;
+      s.expert_pair_start[i] = pairs;
+      run += tiles[i];
+      pairs += (tiles[i] + 1) / 2;
+    }
+    s.expert_tile_start[ne] = run;
+    s.expert_pair_start[ne] = pairs;
+    *s.n_tiles = run;
+  }
+  __syncthreads();
+  if (tid < ne) {
+    const int t0 = s.expert_tile_start[tid];
+    const int row0 = (e_begin + tid) * n_src * Cs;
+    for (int i = 0; i < nt; ++i) {
+      s.tile_row0[t0 + i] = row0 + i * kTileRows;
+      s.tile_expert[t0 + i] = e_begin + tid;
+    }
+  }
+}
+
+// One warp per row of the compacted layout: finds the (source, slot) the row comes from, records
+// it in rowmap (when given) and copies the row; pad rows are zeroed and mapped to -1.
+template <typename T>
+__global__ void __launch_bounds__(256)
+compact_gather_kernel(const T* __restrict__ src, const int32_t* __restrict__ counts, int L,
+                      int n_src, int Cs, int e_begin, int e_end, int width,
+                      T* __restrict__ dst, int32_t* __restrict__ rowmap) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);      // row inside the range
+  const int region = n_src * Cs;
+  if (r >= (int64_t)(e_end - e_begin) * region) return;
+  const int l = e_begin + (int)(r / region);
+  int j = (int)(r % region);
+  int total = 0;
+  for (int w = 0; w < n_src; ++w) total += min(counts[w * L + l], Cs);
+  const int padded = (total + kTileRows - 1) / kTileRows * kTileRows;
+  if (j >= padded) return;
+  const int64_t drow = (int64_t)l * region + j;
+  int64_t srow = -1;
+  if (j < total) {
+    for (int w = 0; w < n_src; ++w) {
+      const int c = min(counts[w * L + l], Cs);
+      if (j < c) { srow = ((int64_t)w * L + l) * Cs + j; break; }
+      j -= c;
+    }
+  }
+  if (rowmap != nullptr && lane == 0) rowmap[drow] = (int32_t)srow;
+  uint4* d4 = reinterpret_cast<uint4*>(dst + drow * width);
+  const int nvec = width / Vec16<T>::N;
+  if (srow < 0) {
+    for (int i = lane; i < nvec; i += 32) d4[i] = make_uint4(0, 0, 0, 0);
+  } else {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + srow * width);
+    for (int i = lane; i < nvec; i += 32) d4[i] = __ldg(s4 + i);
+  }
+}
+
+int build_schedule_compact(const int32_t* counts, int L, int n_src, int Cs, int e_begin, int e_end,
+                           Schedule s, cudaStream_t st) {
+  schedule_compact_kernel<<<1, 256, 0, st>>>(counts, L, n_src, Cs, e_begin, e_end, s);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+int compact_gather(int dtype, const void* src, const int32_t* counts, int L, int n_src, int Cs,
+                   int e_begin, int e_end, int width, void* dst, int32_t* rowmap, cudaStream_t st) {
+  const int64_t rows = (int64_t)(e_end - e_begin) * n_src * Cs;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype == MOLE_F32)
+    compact_gather_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), counts, L, n_src,
+                                                       Cs, e_begin, e_end, width,
+                                                       static_cast<float*>(dst), rowmap);
+  else
+    compact_gather_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(src), counts, L, n_src, Cs, e_begin, e_end, width,
+        static_cast<__nv_bfloat16*>(dst), rowmap);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
 // ---- CUDA-core row-grouped GEMM -------------------------------------------------------
 constexpr int kSB = 64;    // block tile 64 x 64
 constexpr int kSK = 16;
@@ -260,6 +363,7 @@ colsum_kernel(const __grid_constant__ ColsumArgs a) {
 int simt_row_gemm(int dtype, const RowGemmArgs& a, cudaStream_t st) {
   MOLE_REQUIRE(a.N % kSB == 0 && a.K % kSK == 0, "CUDA-core GEMM needs N %% 64 == 0, K %% 16 == 0");
   MOLE_REQUIRE(a.sched.max_tiles * 2 <= 65535, "too many row tiles for the CUDA-core GEMM grid");
+  MOLE_REQUIRE(a.rowmap == nullptr, "the CUDA-core GEMM does not scatter its output rows");
   dim3 grid(a.N / kSB, a.sched.max_tiles * 2);
   if (dtype == MOLE_F32) simt_row_gemm_kernel<float><<<grid, 256, 0, st>>>(a);
   else simt_row_gemm_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a);

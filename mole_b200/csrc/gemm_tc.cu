@@ -220,6 +220,7 @@ struct TcParams {
   const int32_t* tile_row0;
   const int32_t* tile_expert;
   const int32_t* expert_pair_start;   // 2-CTA kernel: prefix of ceil(tiles / 2) per expert
+  const int32_t* rowmap;              // FC2 / dX: output row of every GEMM row (-1: none), or null
   int n_experts, e_begin;
   int N, K;                 // rows mode: output columns / reduction.  wgrad: Q / unused
   int P;                    // wgrad: output rows per expert
@@ -324,7 +325,7 @@ constexpr int kEpiStep = 16;
 
 template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM, int NSTEPS>
 __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
-                                              int64_t obase, const float* bias_s,
+                                              bool valid, int64_t obase, const float* bias_s,
                                               int c_begin, uint32_t (&pre)[NSTEPS][8]) {
   {
 #pragma unroll
@@ -374,7 +375,7 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
           }
           o[i] = pack_bf16(lo, hi);
         }
-        st_v8(p.out0 + obase + c, o);
+        if (valid) st_v8(p.out0 + obase + c, o);
       } else if (EPI == EPI_DACT) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -385,7 +386,7 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           o[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-        st_v8(p.out0 + obase + c, o);
+        if (valid) st_v8(p.out0 + obase + c, o);
       }
     }
   }
@@ -408,6 +409,7 @@ template <int EV> struct EvTraits {
   static constexpr bool bias = EV == EV_FC1_GELU_B || EV == EV_FC1_RELU_B || EV == EV_BIAS;
   static constexpr bool accum = EV == EV_WGRAD_ACC;
   static constexpr bool prefetch = epi == EPI_DACT || accum;
+  static constexpr bool scatter = epi == EPI_BIAS || epi == EPI_STORE;   // outputs that may be scattered
 };
 
 // Issued before the wait for the accumulator: the first two prefetch steps and the bias strip.
@@ -561,8 +563,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool empty = MODE == TC_WGRAD && w.t1 == w.t0;
       const int lrow = quarter * 32 + lane;
       int64_t obase;            // element offset of (row, n0) in the output
-      if (MODE == TC_ROWS) obase = (int64_t)(w.row0 + lrow) * p.N + w.n0;
-      else obase = ((int64_t)slot * p.P + w.row0 + lrow) * p.N + w.n0;
+      bool valid = true;
+      if (MODE == TC_ROWS) {
+        int64_t orow = w.row0 + lrow;
+        if (EvTraits<EV>::scatter && p.rowmap != nullptr) {
+          orow = p.rowmap[orow];
+          valid = orow >= 0;
+        }
+        obase = orow * p.N + w.n0;
+      } else {
+        obase = ((int64_t)slot * p.P + w.row0 + lrow) * p.N + w.n0;
+      }
       const __nv_bfloat16* bias =
           (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
       constexpr int NSTEPS = BN / 4 / kEpiStep;
@@ -574,7 +585,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       using Ev = EvTraits<EV>;
       epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
-          p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, obase, bias_strip[ew],
+          p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, valid, obase, bias_strip[ew],
           cq * (BN / 4), pre);
       if (!empty) {
         tcgen05_fence_before();
@@ -837,12 +848,21 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int lrow = quarter * 32 + lane;
       const int r0 = w.row0[rank];
       int64_t obase = 0;
+      bool valid = true;
       const __nv_bfloat16* bias = nullptr;
       constexpr int NSTEPS = kBN2 / 4 / kEpiStep;
       uint32_t pre[NSTEPS][8];
       if (r0 >= 0) {
-        if (MODE == TC_ROWS) obase = (int64_t)(r0 + lrow) * p.N + w.n0;
-        else obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
+        if (MODE == TC_ROWS) {
+          int64_t orow = r0 + lrow;
+          if (EvTraits<EV>::scatter && p.rowmap != nullptr) {
+            orow = p.rowmap[orow];
+            valid = orow >= 0;
+          }
+          obase = orow * p.N + w.n0;
+        } else {
+          obase = ((int64_t)slot * p.P + r0 + lrow) * p.N + w.n0;
+        }
         bias = (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
         epilogue_prefetch<EV, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (kBN2 / 4), pre);
       }
@@ -854,7 +874,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       {
         using Ev = EvTraits<EV>;
         epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
-            p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, obase,
+            p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, valid, obase,
             bias_strip[ew], cq * (kBN2 / 4), pre);
       }
       if (!empty) {
@@ -1071,6 +1091,9 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   p.out1 = static_cast<__nv_bfloat16*>(a.out1);
   p.fault = device_fault_word();
   p.slot = a.wslot;
+  p.rowmap = a.rowmap;
+  MOLE_REQUIRE(a.rowmap == nullptr || a.epi == EPI_BIAS || a.epi == EPI_STORE,
+               "only FC2 / dX outputs can be scattered");
   const int max_items = a.sched.max_tiles * (a.N / BN);
   for (const void* q : {a.bias, a.aux, (const void*)a.out0, (const void*)a.out1})
     MOLE_REQUIRE((reinterpret_cast<uintptr_t>(q) & 31) == 0, "epilogue operand %p not 32-byte aligned", q);

@@ -198,9 +198,9 @@ def dispatch_bwd(ddisp: Optional[torch.Tensor], plan: RoutePlan, M: int, dtype, 
 # ---- grouped FFN -----------------------------------------------------------------------
 def make_ffn_desc(dtype, act: str, gelu_bwd: str, M: int, F: int, L: int, n_src: int, Cs: int,
                   e_begin: int, e_end: int, n_slots: int, accumulate: bool = False,
-                  backend: int = 0, n_grad_slots: int = 0) -> FfnDesc:
+                  backend: int = 0, n_grad_slots: int = 0, compact: int = 0) -> FfnDesc:
     return FfnDesc(_DTYPES[dtype], _ACTS[act], _GELU_BWD[gelu_bwd], M, F, L, n_src, Cs,
-                   e_begin, e_end, n_slots, n_grad_slots, int(accumulate), backend)
+                   e_begin, e_end, n_slots, n_grad_slots, int(accumulate), compact, backend)
 
 
 def ffn_workspace(desc: FfnDesc, device) -> torch.Tensor:

@@ -47,7 +47,7 @@ def test_argument_validation_needs_no_gpu():
     assert b"E=1000" in lib.mole_last_error_string()
     assert lib.mole_route_workspace_bytes(4096, 8, 9, C.byref(n)) == -1         # k > E
     d = _lib.FfnDesc(dtype=1, act=0, gelu_bwd=0, M=1000, F=4096, L=8, n_src=1, Cs=128, e_begin=0,
-                     e_end=8, n_slots=8, n_grad_slots=0, accumulate=0, backend=0)
+                     e_end=8, n_slots=8, n_grad_slots=0, accumulate=0, compact=0, backend=0)
     assert lib.mole_ffn_workspace_bytes(C.byref(d), C.byref(n)) == -1           # M % 64 != 0
     d.M = 192                                                                   # bf16 needs % 128
     assert lib.mole_ffn_workspace_bytes(C.byref(d), C.byref(n)) == -4

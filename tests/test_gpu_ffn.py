@@ -45,14 +45,15 @@ class Case:
         return r["out"], r["dx"], [r["gw1"], r["gb1"], r["gw2"], r["gb2"]]
 
 
-def run_gpu(case, e_begin=0, e_end=None, backend=0, accumulate=False, slots=None, grads=None):
+def run_gpu(case, e_begin=0, e_end=None, backend=0, accumulate=False, slots=None, grads=None,
+            compact=0):
     from mole_b200 import ops
     c = case
     e_end = c.L if e_end is None else e_end
     dev = torch.device("cuda")
     n_slots = c.L if slots is None else max(slots) + 1
     desc = ops.make_ffn_desc(c.dtype, c.act, "exact", c.M, c.F, c.L, c.n_src, c.Cs, e_begin, e_end,
-                             n_slots, accumulate, backend)
+                             n_slots, accumulate, backend, compact=compact)
     ws = ops.ffn_workspace(desc, dev)
     rows = c.n_src * c.L * c.Cs
     x = c.x.view(rows, c.M).cuda()
@@ -128,6 +129,29 @@ def test_ffn_bf16_tcgen05_narrow_tiles_two_sources():
     case = Case(M=128, F=384, L=4, n_src=2, Cs=256, counts=counts, dtype=torch.bfloat16, seed=2)
     out, dx, grads = run_gpu(case)
     check(case, out, dx, grads, range(4))
+
+
+@pytest.mark.parametrize("backend", [2, 3])
+def test_ffn_bf16_four_sources_packed_per_expert(backend):
+    """Four source ranks per expert: the tensor-core path packs each expert's rows of all sources
+    into one run (rows cross 128-row tile edges inside a source's chunk), computes there and
+    scatters out / dx back to the (source, expert) chunks.  Checked against the oracle, and
+    against the same call with packing switched off, on a sub-range of experts."""
+    counts = [100, 0, 256, 1, 7, 128,
+              30, 0, 129, 0, 250, 128,
+              0, 0, 5, 200, 255, 128,
+              127, 0, 1, 56, 3, 128]            # [n_src=4][L=6]; expert 1 is empty everywhere
+    case = Case(M=256, F=512, L=6, n_src=4, Cs=256, counts=counts, dtype=torch.bfloat16, seed=7)
+    out, dx, grads = run_gpu(case, backend=backend)
+    check(case, out, dx, grads, range(6))
+    out_r, dx_r, grads_r = run_gpu(case, e_begin=2, e_end=5, backend=backend)
+    out_c, dx_c, grads_c = run_gpu(case, e_begin=2, e_end=5, backend=backend, compact=2)
+    check(case, out_r, dx_r, grads_r, (2, 3, 4))
+    for l in (2, 3, 4):
+        assert_close(case.expert_rows(out_r, l), case.expert_rows(out_c, l), case.dtype, f"out {l}")
+        assert_close(case.expert_rows(dx_r, l), case.expert_rows(dx_c, l), case.dtype, f"dx {l}")
+    for l in (0, 1, 5):
+        assert torch.isnan(out_r[:, l].float()).all()
 
 
 def test_ffn_bf16_expert_range_slots_and_accumulate():
