@@ -392,6 +392,68 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
   }
 }
 
+// Epilogue with whole-line stores.  After tcgen05.ld a thread holds 16 consecutive columns of ONE
+// row, so a plain warp store writes 32 rows x 32 bytes: 32 separate L2 requests and 9 LSU
+// wavefronts per instruction, and the weight-gradient GEMM, whose output is its main traffic,
+// spent half of its L2 tag and LSU capacity on them.  Here the warp's 32 rows x (NSTEPS * 16)
+// columns go through a 2 KB shared-memory strip in passes of 16 rows (NSTEPS = 4); after a pass,
+// NSTEPS neighbouring lanes hold one row's NSTEPS * 32 contiguous bytes and the store
+// instruction writes whole 128-byte lines.  16-byte chunks are XOR-swizzled with the row so that
+// neither side has bank conflicts.  The next use of the strip (next tile) comes after the
+// TMEM wait of that tile, a warp-wide instruction, which orders it behind this tile's reads.
+constexpr int kStripBytes = 2048;
+template <int NSTEPS>
+__device__ __forceinline__ void epilogue_lines(__nv_bfloat16* out, int64_t warp_base, int ldo,
+                                               uint32_t taddr, bool empty, int c_begin,
+                                               uint8_t* strip) {
+  constexpr int kRowBytes = NSTEPS * 32;
+  constexpr int kRows = kStripBytes / kRowBytes;      // rows per pass
+  constexpr int kPasses = 32 / kRows;
+  constexpr int kPieces = kRows * NSTEPS / 32;        // 32-byte pieces a lane stores per pass
+  constexpr int kMask = (2 * NSTEPS - 1) & 7;
+  const int lane = threadIdx.x & 31;
+  uint32_t o[NSTEPS][8];
+#pragma unroll
+  for (int q = 0; q < NSTEPS; ++q) {
+    uint32_t r[16];
+    if (!empty) {
+      tmem_ld16(taddr + c_begin + kEpiStep * q, r);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) r[i] = 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      o[q][i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+  }
+  const int wr = lane % kRows, wpass = lane / kRows;      // as a writer of the strip
+  __syncwarp();                                           // the previous tile's readers are done
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    if (wpass == j) {
+#pragma unroll
+      for (int q = 0; q < NSTEPS; ++q)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          *reinterpret_cast<uint4*>(strip + wr * kRowBytes + (((2 * q + h) ^ (wr & kMask)) << 4)) =
+              make_uint4(o[q][4 * h], o[q][4 * h + 1], o[q][4 * h + 2], o[q][4 * h + 3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < kPieces; ++k) {
+      const int idx = lane + 32 * k;
+      const int rr = idx / NSTEPS, ra = idx % NSTEPS;     // row of the pass, 32-byte piece of the row
+      const uint8_t* row = strip + rr * kRowBytes;
+      const uint4 lo = *reinterpret_cast<const uint4*>(row + (((2 * ra) ^ (rr & kMask)) << 4));
+      const uint4 hi = *reinterpret_cast<const uint4*>(row + (((2 * ra + 1) ^ (rr & kMask)) << 4));
+      const uint32_t v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+      st_v8(out + warp_base + (int64_t)(kRows * j + rr) * ldo + c_begin + kEpiStep * ra, v);
+    }
+    if (j + 1 < kPasses) __syncwarp();
+  }
+}
+
 // Epilogue variants.  Each kernel instantiation carries exactly one: a kernel that holds all of
 // them behind a run-time switch is several times larger and misses in the instruction cache.
 enum EpiVariant : int {
@@ -450,6 +512,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
   __shared__ float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
+  __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -584,9 +647,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tcgen05_fence_after();
       }
       using Ev = EvTraits<EV>;
-      epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
-          p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, valid, obase, bias_strip[ew],
-          cq * (BN / 4), pre);
+      if (EV == EV_WGRAD)
+        epilogue_lines<NSTEPS>(p.out0, obase - (int64_t)lane * p.N, p.N,
+                               tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty,
+                               cq * (BN / 4), store_strip[ew]);
+      else
+        epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
+            p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, valid, obase,
+            bias_strip[ew], cq * (BN / 4), pre);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -726,6 +794,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
   __shared__ float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
+  __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -873,9 +942,14 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (r0 >= 0)
       {
         using Ev = EvTraits<EV>;
-        epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
-            p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, valid, obase,
-            bias_strip[ew], cq * (kBN2 / 4), pre);
+        if (EV == EV_WGRAD)
+          epilogue_lines<NSTEPS>(p.out0, obase - (int64_t)lane * p.N, p.N,
+                                 tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty,
+                                 cq * (kBN2 / 4), store_strip[ew]);
+        else
+          epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
+              p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, valid, obase,
+              bias_strip[ew], cq * (kBN2 / 4), pre);
       }
       if (!empty) {
         tcgen05_fence_before();
