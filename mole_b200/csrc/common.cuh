@@ -142,6 +142,7 @@ struct Schedule {
   int32_t* expert_pair_start;  // [L + 1]  prefix of ceil(tiles / 2): work units of the 2-CTA GEMM
   int32_t* tile_row0;          // [max_tiles]
   int32_t* tile_expert;        // [max_tiles]
+  int32_t* tile_rows;          // [max_tiles]  valid rows of the tile (1..128); the rest are zero rows
   int32_t max_tiles;
 };
 

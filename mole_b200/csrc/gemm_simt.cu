@@ -11,7 +11,7 @@ namespace mole {
 // ---- schedule -----------------------------------------------------------------------
 int64_t schedule_bytes(int L, int n_src, int Cs) {
   const int64_t max_tiles = (int64_t)L * n_src * (Cs / kTileRows);
-  return (1 + 2 * (L + 1) + 2 * max_tiles + 16) * 4;
+  return (1 + 2 * (L + 1) + 3 * max_tiles + 16) * 4;
 }
 Schedule carve_schedule(void* ws, int L, int n_src, int Cs) {
   Schedule s;
@@ -22,6 +22,7 @@ Schedule carve_schedule(void* ws, int L, int n_src, int Cs) {
   s.expert_pair_start = s.expert_tile_start + (L + 1);
   s.tile_row0 = s.expert_pair_start + (L + 1) + 3;
   s.tile_expert = s.tile_row0 + s.max_tiles;
+  s.tile_rows = s.tile_expert + s.max_tiles;
   return s;
 }
 
@@ -52,11 +53,13 @@ schedule_kernel(const int32_t* __restrict__ counts, int L, int n_src, int Cs, in
   for (int p = p0; p < p1; ++p) {
     const int l = e_begin + p / n_src, w = p % n_src;
     if (w == 0) s.expert_tile_start[l - e_begin] = t;
-    const int nt = (min(counts[w * L + l], Cs) + kTileRows - 1) / kTileRows;
+    const int cnt = min(counts[w * L + l], Cs);
+    const int nt = (cnt + kTileRows - 1) / kTileRows;
     const int row0 = (w * L + l) * Cs;
     for (int i = 0; i < nt; ++i) {
       s.tile_row0[t + i] = row0 + i * kTileRows;
       s.tile_expert[t + i] = l;
+      s.tile_rows[t + i] = min(kTileRows, cnt - i * kTileRows);
     }
     t += nt;
   }
@@ -91,9 +94,8 @@ schedule_compact_kernel(const int32_t* __restrict__ counts, int L, int n_src, in
   __shared__ int tiles[256];
   const int tid = threadIdx.x;
   const int ne = e_end - e_begin;
-  int nt = 0;
+  int nt = 0, rows = 0;
   if (tid < ne) {
-    int rows = 0;
     for (int w = 0; w < n_src; ++w) rows += min(counts[w * L + e_begin + tid], Cs);
     nt = (rows + kTileRows - 1) / kTileRows;
   }
@@ -118,6 +120,7 @@ schedule_compact_kernel(const int32_t* __restrict__ counts, int L, int n_src, in
     for (int i = 0; i < nt; ++i) {
       s.tile_row0[t0 + i] = row0 + i * kTileRows;
       s.tile_expert[t0 + i] = e_begin + tid;
+      s.tile_rows[t0 + i] = min(kTileRows, rows - i * kTileRows);
     }
   }
 }

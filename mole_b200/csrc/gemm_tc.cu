@@ -219,6 +219,7 @@ struct TcParams {
   const int32_t* expert_tile_start;
   const int32_t* tile_row0;
   const int32_t* tile_expert;
+  const int32_t* tile_rows;           // valid rows per tile: the weight-gradient GEMM stops its K loop there
   const int32_t* expert_pair_start;   // 2-CTA kernel: prefix of ceil(tiles / 2) per expert
   const int32_t* rowmap;              // FC2 / dX: output row of every GEMM row (-1: none), or null
   int n_experts, e_begin;
@@ -551,13 +552,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const WorkItem w = decode_item<MODE, BN>(p, item);
         if (!w.valid) break;
         const int slot = p.slot.s[p.e_begin + w.el];
-        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
-        for (int kb = 0; kb < nkb; ++kb) {
-          mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1);
-          const uint32_t bar = full0 + 8 * stage;
-          const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
-          mbar_expect_tx(bar, kStageBytes);
-          if (MODE == TC_ROWS) {
+        if (MODE == TC_ROWS) {
+          const int nkb = p.K / kBK;
+          for (int kb = 0; kb < nkb; ++kb) {
+            mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1);
+            const uint32_t bar = full0 + 8 * stage;
+            const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
+            mbar_expect_tx(bar, kStageBytes);
             tma_load_2d(sa, &tmap_a, bar, kb * kBK, w.row0);
             if (B_KMAJOR) {
               tma_load_3d(sb, &tmap_b, bar, kb * kBK, w.n0, slot);
@@ -566,16 +567,30 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               for (int i = 0; i < BN / 64; ++i)
                 tma_load_3d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, kb * kBK, slot);
             }
-          } else {
-            const int row = p.tile_row0[w.t0 + (kb >> 1)] + (kb & 1) * kBK;
-#pragma unroll
-            for (int i = 0; i < kBM / 64; ++i)
-              tma_load_2d(sa + i * 8192, &tmap_a, bar, w.row0 + 64 * i, row);
-#pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              tma_load_2d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, row);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        } else {
+          // K runs over the expert's rows, tile by tile, and stops at each tile's valid rows
+          // (64-row blocks here, 16-row MMA steps in the issuer): with ~256 rows per expert the
+          // zero rows up to the next multiple of 128 would be a fifth of the work.
+          for (int t = w.t0; t < w.t1; ++t) {
+            const int trow = p.tile_row0[t];
+            const int halves = p.tile_rows[t] > kBK ? 2 : 1;
+            for (int hf = 0; hf < halves; ++hf) {
+              mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1);
+              const uint32_t bar = full0 + 8 * stage;
+              const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
+              const int row = trow + hf * kBK;
+              mbar_expect_tx(bar, kStageBytes);
+#pragma unroll
+              for (int i = 0; i < kBM / 64; ++i)
+                tma_load_2d(sa + i * 8192, &tmap_a, bar, w.row0 + 64 * i, row);
+#pragma unroll
+              for (int i = 0; i < BN / 64; ++i)
+                tma_load_2d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, row);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          }
         }
       }
     }
@@ -587,25 +602,42 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int item = blockIdx.x;; item += gridDim.x) {
         const WorkItem w = decode_item<MODE, BN>(p, item);
         if (!w.valid) break;
-        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
-        if (nkb == 0) continue;                       // empty expert: epilogue writes zeros
+        if (MODE == TC_WGRAD && w.t1 == w.t0) continue;      // empty expert: epilogue writes zeros
         mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 2);
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < nkb; ++kb) {
+        // one shared-memory stage: `ksteps` MMAs of K = 16
+        auto issue_stage = [&](int ksteps, bool first) {
           mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 3);
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
 #pragma unroll
           for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
-            const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
-                                     : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
-            const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
-                                     : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
-            tcgen05_mma_bf16(d_tmem, ad, bd, kIdesc, (kb | ks) != 0 ? 1u : 0u);
+            if (ks < ksteps) {
+              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
+                                       : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
+              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
+                                       : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
+              tcgen05_mma_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
+            }
           }
           tcgen05_commit(empty0 + 8 * stage);         // frees the smem stage when the MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        };
+        if (MODE == TC_ROWS) {
+          const int nkb = p.K / kBK;
+          for (int kb = 0; kb < nkb; ++kb) issue_stage(kBK / kUmmaK, kb == 0);
+        } else {
+          bool first = true;
+          for (int t = w.t0; t < w.t1; ++t) {
+            const int v = p.tile_rows[t];
+            const int halves = v > kBK ? 2 : 1;
+            for (int hf = 0; hf < halves; ++hf) {
+              const int left = v - hf * kBK;
+              issue_stage(left >= kBK ? kBK / kUmmaK : (left + kUmmaK - 1) / kUmmaK, first);
+              first = false;
+            }
+          }
         }
         tcgen05_commit(tfull0 + 8 * acc);             // accumulator ready for the epilogue
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
@@ -837,18 +869,18 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const PairItem w = decode_pair<MODE>(p, item);
         if (!w.valid) break;
         const int slot = p.slot.s[p.e_begin + w.el];
-        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
         const bool have_a = w.row0[rank] >= 0;
         const uint32_t tx = MODE == TC_ROWS
                                 ? kABytes * (w.row0[1] >= 0 ? 2u : 1u) + 2u * kBHalfBytes
                                 : 2u * kStage2Bytes;
         const int nh = w.n0 + 128 * (int)rank;         // this CTA's half of the B columns
-        for (int kb = 0; kb < nkb; ++kb) {
-          mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11);
-          const uint32_t bar = (full0 + 8 * stage) & kPeerMask;     // the even CTA's barrier
-          const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
-          if (leader) mbar_expect_tx(full0 + 8 * stage, tx);
-          if (MODE == TC_ROWS) {
+        if (MODE == TC_ROWS) {
+          const int nkb = p.K / kBK;
+          for (int kb = 0; kb < nkb; ++kb) {
+            mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11);
+            const uint32_t bar = (full0 + 8 * stage) & kPeerMask;     // the even CTA's barrier
+            const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
+            if (leader) mbar_expect_tx(full0 + 8 * stage, tx);
             if (have_a) tma2_load_2d(sa, &tmap_a, bar, kb * kBK, w.row0[rank]);
             if (B_KMAJOR) {
               tma2_load_3d(sb, &tmap_b, bar, kb * kBK, nh, slot);
@@ -857,16 +889,27 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               for (int i = 0; i < 2; ++i)
                 tma2_load_3d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, kb * kBK, slot);
             }
-          } else {
-            const int row = p.tile_row0[w.t0 + (kb >> 1)] + (kb & 1) * kBK;
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-              tma2_load_2d(sa + i * 8192, &tmap_a, bar, w.row0[rank] + 64 * i, row);
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-              tma2_load_2d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, row);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        } else {
+          for (int t = w.t0; t < w.t1; ++t) {            // K stops at each tile's valid rows
+            const int trow = p.tile_row0[t];
+            const int halves = p.tile_rows[t] > kBK ? 2 : 1;
+            for (int hf = 0; hf < halves; ++hf) {
+              mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11);
+              const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
+              const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
+              const int row = trow + hf * kBK;
+              if (leader) mbar_expect_tx(full0 + 8 * stage, tx);
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                tma2_load_2d(sa + i * 8192, &tmap_a, bar, w.row0[rank] + 64 * i, row);
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                tma2_load_2d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, row);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          }
         }
       }
     }
@@ -878,25 +921,41 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       for (int item = cluster_id;; item += n_clusters) {
         const PairItem w = decode_pair<MODE>(p, item);
         if (!w.valid) break;
-        const int nkb = MODE == TC_ROWS ? p.K / kBK : (w.t1 - w.t0) * (kTileRows / kBK);
-        if (nkb == 0) continue;
+        if (MODE == TC_WGRAD && w.t1 == w.t0) continue;
         mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12);
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN2;
-        for (int kb = 0; kb < nkb; ++kb) {
+        auto issue_stage = [&](int ksteps, bool first) {
           mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 13);
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
 #pragma unroll
           for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
-            const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
-                                     : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
-            const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
-                                     : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
-            tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (kb | ks) != 0 ? 1u : 0u);
+            if (ks < ksteps) {
+              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
+                                       : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
+              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
+                                       : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
+              tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
+            }
           }
           tcgen05_commit2(empty0 + 8 * stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        };
+        if (MODE == TC_ROWS) {
+          const int nkb = p.K / kBK;
+          for (int kb = 0; kb < nkb; ++kb) issue_stage(kBK / kUmmaK, kb == 0);
+        } else {
+          bool first = true;
+          for (int t = w.t0; t < w.t1; ++t) {
+            const int v = p.tile_rows[t];
+            const int halves = v > kBK ? 2 : 1;
+            for (int hf = 0; hf < halves; ++hf) {
+              const int left = v - hf * kBK;
+              issue_stage(left >= kBK ? kBK / kUmmaK : (left + kUmmaK - 1) / kUmmaK, first);
+              first = false;
+            }
+          }
         }
         tcgen05_commit2(tfull0 + 8 * acc);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
@@ -1123,6 +1182,7 @@ static void fill_sched(TcParams& p, const Schedule& s) {
   p.expert_tile_start = s.expert_tile_start;
   p.tile_row0 = s.tile_row0;
   p.tile_expert = s.tile_expert;
+  p.tile_rows = s.tile_rows;
   p.expert_pair_start = s.expert_pair_start;
 }
 
