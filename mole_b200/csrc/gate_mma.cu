@@ -149,15 +149,15 @@ int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t
 }
 
 // ---- dWg += dlogits^T @ x -------------------------------------------------------------------
-// Block: 8 warps, all experts x 128 columns, 256 tokens in four sub-chunks of 64; partial sums
-// go to the fp32 accumulator with atomics (split over tokens).  Warp w: columns 64 (w >> 2) ..,
+// Block: 8 warps, all experts x 128 columns, `chunk` tokens in sub-chunks of 64; partial sums
+// go to the fp32 accumulator with atomics (split over tokens).  The chunk is sized for about two
+// blocks per SM: every block ends with E x 128 atomics, so fewer, longer blocks cost less.  Warp w: columns 64 (w >> 2) ..,
 // expert tiles (w & 3) + 4 i.  Both operands sit in shared memory token-major ([k][m], [k][n]),
 // so both fragments come from transposing ldmatrix loads.
-constexpr int kWgChunk = 256;
 template <int MT>                       // expert tiles of 16 per warp: EP <= 64 * MT
 __global__ void __launch_bounds__(256)
 gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ x,
-                      int64_t Ttok, int M, int E, int EP, float* __restrict__ dwg) {
+                      int64_t Ttok, int M, int E, int EP, int chunk, float* __restrict__ dwg) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lda = EP + 8;
   __nv_bfloat16* a_hi = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [64 tok][lda]
@@ -166,7 +166,7 @@ gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int mg = warp & 3, nh = warp >> 2;
   const int col0 = blockIdx.x * kGmCols;
-  const int64_t chunk0 = (int64_t)blockIdx.y * kWgChunk;
+  const int64_t chunk0 = (int64_t)blockIdx.y * chunk;
   float acc[MT][8][4];
 #pragma unroll
   for (int a = 0; a < MT; ++a)
@@ -175,7 +175,7 @@ gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[a][i][j] = 0.f;
 
-  for (int sub = 0; sub < kWgChunk / kGmTok; ++sub) {
+  for (int sub = 0; sub < chunk / kGmTok; ++sub) {
     const int64_t tok0 = chunk0 + sub * kGmTok;
     if (tok0 >= Ttok) break;                                  // block-uniform
     for (int i = tid; i < kGmTok * EP; i += 256) {
@@ -245,8 +245,16 @@ static int launch_wgrad_mma_t(const float* dlogits, const void* x, int64_t T, in
     MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  dim3 grid(M / kGmCols, (unsigned)((T + kWgChunk - 1) / kWgChunk));
-  kern<<<grid, 256, smem, st>>>(dlogits, static_cast<const __nv_bfloat16*>(x), T, M, E, EP, dwg);
+  int dev = 0, sms = 0;
+  MOLE_CUDA_OK(cudaGetDevice(&dev));
+  MOLE_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int col_blocks = M / kGmCols;
+  const int64_t want = (2 * sms + col_blocks - 1) / col_blocks;          // token chunks wanted
+  int64_t chunk = ((T + want - 1) / want + kGmTok - 1) / kGmTok * kGmTok;
+  if (chunk < 256) chunk = 256;
+  dim3 grid(col_blocks, (unsigned)((T + chunk - 1) / chunk));
+  kern<<<grid, 256, smem, st>>>(dlogits, static_cast<const __nv_bfloat16*>(x), T, M, E, EP,
+                                (int)chunk, dwg);
   MOLE_LAUNCH_OK();
   return MOLE_OK;
 }

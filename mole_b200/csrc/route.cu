@@ -224,6 +224,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 
 constexpr int kMmaKC = 64;            // K elements per stage
 constexpr int kMmaLds = kMmaKC + 8;   // padded row (144 bytes): conflict-free ldmatrix
+constexpr int kMmaStages = 4;         // cp.async ring: one block per SM has nothing else to hide latency
 
 template <int NT>                     // expert tiles of 8: experts padded to NT * 8 >= 32
 __global__ void __launch_bounds__(kGateThreads)
@@ -234,8 +235,8 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
                      float* __restrict__ me_part, int nblk) {
   extern __shared__ float smem[];
   constexpr int EP = NT * 8, NTW = NT / 2;
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);          // [2][64][72]
-  __nv_bfloat16* wsm = xs + 2 * kGateTok * kMmaLds;                    // [2][EP][72]
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);          // [stages][64][72]
+  __nv_bfloat16* wsm = xs + kMmaStages * kGateTok * kMmaLds;           // [stages][EP][72]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int mt = warp & 3, nh = warp >> 2;
   const int64_t tok0 = (int64_t)blockIdx.x * kGateTok;
@@ -264,16 +265,19 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
   const int nchunks = M / kMmaKC;
-  load_chunk(0, 0);
+  // one commit group per chunk slot (empty past the end), so "all but the newest stages - 2
+  // groups are complete" always means chunk c has landed
+#pragma unroll
+  for (int c = 0; c < kMmaStages - 1; ++c) {
+    if (c < nchunks) load_chunk(c, c);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   for (int c = 0; c < nchunks; ++c) {
-    const int st = c & 1;
-    if (c + 1 < nchunks) {
-      load_chunk(c + 1, st ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+    const int st = c % kMmaStages;
+    asm volatile("cp.async.wait_group %0;" ::"n"(kMmaStages - 2) : "memory");
+    __syncthreads();                       // chunk c visible; stage of chunk c - 1 free again
+    if (c + kMmaStages - 1 < nchunks) load_chunk(c + kMmaStages - 1, (c + kMmaStages - 1) % kMmaStages);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
     const __nv_bfloat16* xa = xs + st * kGateTok * kMmaLds;
     const __nv_bfloat16* wb = wsm + st * EP * kMmaLds;
 #pragma unroll
@@ -290,8 +294,9 @@ gate_topk_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
         mma_bf16_16816(acc[2 * p + 1], a, b[2], b[3]);
       }
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
   // logits tile to shared memory (operand stages are dead after the last barrier)
   float* ls = smem;
   const int ldl = E + 1;
@@ -580,7 +585,7 @@ static int launch_gate_mma(const void* x, const void* wg, const float* bias, int
                            int E, int k, int normalize, float* scores, int32_t* idx, float* gates,
                            RouteWs w, cudaStream_t st) {
   const int nb = nblocks(Ttok);
-  const size_t tiles = (size_t)2 * (kGateTok + NT * 8) * kMmaLds * 2;
+  const size_t tiles = (size_t)kMmaStages * (kGateTok + NT * 8) * kMmaLds * 2;
   const size_t tail = (size_t)kGateTok * (E + 1) * 4 + (size_t)k * E * 4;
   const size_t smem = tiles > tail ? tiles : tail;
   auto kern = gate_topk_mma_kernel<NT>;
