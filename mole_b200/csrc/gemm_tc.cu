@@ -512,7 +512,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
-  __shared__ float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
+  __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
   volatile int* abort_flag = &abort_flag_s;
 
@@ -825,7 +825,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
-  __shared__ float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
+  __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
   volatile int* abort_flag = &abort_flag_s;
 
