@@ -48,8 +48,8 @@ CONFIGS = {
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per rank (debugging)")
@@ -364,9 +364,11 @@ def run_ours(args):
 
     pk = peaks()
     if rank == 0 or world > 1:
-        out["roofline"], out["gemm_launches"] = gemm_roofline(step, pairs, M, F, pk, barrier)
+        out["roofline"], out["gemm_launches"] = gemm_roofline(step, pairs, M, F, L, pk, barrier)
     if rank == 0 and not args.no_kernel_report and not cfg.get("offload"):
         out["hbm_kernels"] = hbm_kernel_report(m, x, gy, cf, pk)
+    if rank == 0 and world == 1 and not args.no_kernel_report and not cfg.get("offload"):
+        out["stock_torch_gpu"] = stock_torch_gpu(m, x, gy, k, cf)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_sample(cfg, steps=3, warmup=1)
     barrier()
@@ -379,7 +381,12 @@ def run_ours(args):
 KINDS = {0: "FC1", 1: "FC2", 2: "dX2", 3: "dX", 4: "dW"}
 
 
-def gemm_roofline(step, pairs, M, F, pk, barrier):
+# DRAM traffic of the six grouped-GEMM launches over their algorithmic bytes, from one ncu capture
+# (profiles/tc_gemm_c2_tokens8192_ncu_full.md: 4601 MB measured, 4498 MB algorithmic).
+NCU_TRAFFIC_OVER_ALGORITHMIC = 1.02
+
+
+def gemm_roofline(step, pairs, M, F, n_experts, pk, barrier):
     """Per-launch durations of the tensor-core grouped GEMM (CUDA events on its own stream, inside
     two extra layer steps).  Algorithmic work of every one of the six launches is 2*P*M*F flops
     (P = kept pairs); padding rows, empty tiles and recomputation do not count."""
@@ -411,12 +418,86 @@ def gemm_roofline(step, pairs, M, F, pk, barrier):
                           "tflops": flops * (2 if name == "dW" else 1) / (per_step * 1e-3) / 1e12
                           if per_step > 0 else None}
     achieved = 6 * flops / (total_ms * 1e-3) / 1e12 if total_ms > 0 else 0.0
+    # HBM side of the same launches (bf16): every launch moves the local experts' weights or
+    # weight gradients once (n_experts * M * F elements) plus its row operands and outputs.
+    wbytes = 2.0 * n_experts * M * F
+    rows_m, rows_f = 2.0 * pairs * M, 2.0 * pairs * F
+    alg_bytes = {"FC1": wbytes + rows_m + 2 * rows_f, "FC2": wbytes + rows_f + rows_m,
+                 "dX2": wbytes + rows_m + 2 * rows_f, "dX": wbytes + rows_f + rows_m,
+                 "dW": 2 * wbytes + 2 * (rows_f + rows_m)}
+    total_bytes = sum(alg_bytes.values())
+    # ncu, dram__bytes_read.sum + dram__bytes_write.sum of the six launches over their algorithmic
+    # bytes, from the capture summarised in profiles/ (measured once, not live)
+    traffic_ratio = NCU_TRAFFIC_OVER_ALGORITHMIC
     roof = {"bound": "tensor", "kernel": "tc_gemm_kernel (6 launches per step: FC1, FC2, dW2, dX2, dW1, dX)",
             "achieved": achieved, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
-            "frac": achieved / pk["tf_sustained"], "traffic": None,
+            "frac": achieved / pk["tf_sustained"],
+            "traffic": total_bytes * traffic_ratio / 6 if traffic_ratio else None,
+            "traffic_note": "bytes per launch, mean of the six: algorithmic bytes x the DRAM-traffic / "
+                            "algorithmic ratio ncu measured on a smaller case of the same kernels "
+                            "(traffic grows with the weights and rows like the algorithmic bytes do)",
             "peak_source": pk["source"] + ", sustained figure: the kernel is timed inside a long step",
-            "algorithmic_flops_per_launch": flops, "ms_per_step_all_launches": total_ms}
+            "algorithmic_flops_per_launch": flops, "ms_per_step_all_launches": total_ms,
+            "hbm_side": {"algorithmic_bytes_per_step": total_bytes,
+                         "achieved_gbs": total_bytes / (total_ms * 1e-3) / 1e9 if total_ms > 0 else None,
+                         "peak_gbs": pk["hbm"],
+                         "frac": total_bytes / (total_ms * 1e-3) / 1e9 / pk["hbm"] if total_ms > 0 else None,
+                         "note": "few rows per expert put these GEMMs at the ridge: the same launches "
+                                 "read against the measured copy bandwidth"}}
     return roof, launches
+
+
+def stock_torch_gpu(m, x, gy, k, cf, steps=5):
+    """The reference's own GPU arithmetic restated with stock PyTorch on this GPU, as the kernel to
+    beat: softmax gate, top-k routing with capacity (one-hot cumsum), capacity-padded [E, C, M]
+    buffer, torch.baddbmm -> gelu -> torch.baddbmm over ALL padded rows (MOLE/cpp/core.cpp:350-353),
+    weighted combine; backward by autograd.  Same weights, tokens and upstream gradient as the
+    measured step; cuBLAS strided-batched GEMMs.  Device-resident, one GPU."""
+    import math
+    import torch.nn.functional as Fn
+    T, M = x.shape
+    wg = m.gate[0].linear.weight.detach().clone().requires_grad_(True)
+    params = [p.all_tensors.detach().clone().requires_grad_(True)
+              for p in (m.FC1_W_GPU, m.FC1_B_GPU, m.FC2_W_GPU, m.FC2_B_GPU)]
+    w1, b1, w2, b2 = params
+    E = w1.shape[0]
+    cap = max(1, math.ceil(k * cf * T / E))
+    xin = x.detach().clone().requires_grad_(True)
+    tok = torch.arange(T, device=x.device).repeat(k)
+
+    def one():
+        for t in (xin, wg, *params):
+            t.grad = None
+        scores = torch.softmax(xin.float() @ wg.float().t(), -1)
+        gates, idx = torch.topk(scores, k, dim=-1)
+        flat = idx.t().reshape(-1)                                   # all first choices, then second
+        pos = (Fn.one_hot(flat, E).cumsum(0) - 1).gather(1, flat[:, None]).squeeze(1)
+        keep = pos < cap
+        disp = xin.new_zeros(E, cap, M)
+        disp = disp.index_put((flat[keep], pos[keep]), xin[tok[keep]])
+        h = Fn.gelu(torch.baddbmm(b1.view(E, 1, -1), disp, w1.transpose(1, 2)))
+        o = torch.baddbmm(b2.view(E, 1, -1), h, w2)
+        g = (gates.t().reshape(-1) * keep).to(o.dtype)
+        rows = o[flat, pos.clamp(max=cap - 1)] * g[:, None]
+        y = torch.zeros_like(xin).index_add_(0, tok, rows)
+        y.backward(gy)
+
+    for _ in range(2):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    del params, wg, xin
+    torch.cuda.empty_cache()
+    return {"value": T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": steps,
+            "note": "stock PyTorch on the same GPU (cuBLAS strided-batched baddbmm over the "
+                    "capacity-padded [E, C, M] buffer, autograd backward): the reference's GPU "
+                    "arithmetic, not this library"}
 
 
 def hbm_kernel_report(m, x, gy, cf, pk):
