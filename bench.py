@@ -513,13 +513,17 @@ def hbm_kernel_report(m, x, gy, cf, pk):
     wg = m.gate[0].linear.weight.detach()
     rows = ops.dispatch(xd, plan)
     drows = torch.empty_like(rows)
-    big = torch.empty(256 << 20, dtype=torch.uint8, device=x.device)   # L2 flush
+    # L2 flush by READING a 256 MiB buffer that is never written: afterwards L2 holds clean lines
+    # only.  (A memset flush leaves 126 MB of dirty lines whose write-back then competes with the
+    # timed kernel: the ~20 us launches here read 8-10 us longer after one.)
+    big = torch.zeros(64 << 20, dtype=torch.int32, device=x.device)
 
     def timeit(fn):
         fn()
         ts = []
         for _ in range(5):
-            big.zero_()
+            big.sum()
+            torch.cuda._sleep(400_000)      # ~0.2 ms of GPU spin: the host enqueues the rest meanwhile
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -541,12 +545,16 @@ def hbm_kernel_report(m, x, gy, cf, pk):
     add("combine_fwd", lambda: ops.combine(rows, plan, plan.gates), (P + T) * M * es)
     add("combine_bwd", lambda: ops.combine_bwd(gy, rows, plan, plan.gates), 3 * P * M * es + P * 4)
     add("dispatch_bwd", lambda: ops.dispatch_bwd(rows, plan, M, x.dtype, x.device), (P + T) * M * es)
+    dlogits = torch.randn(T, E, device=x.device) * 1e-3
+    add("dispatch_bwd_with_gate_dx (the launch the layer uses: + dlogits @ Wg)",
+        lambda: ops.dispatch_bwd(rows, plan, M, x.dtype, x.device, dlogits, wg),
+        (P + T) * M * es + T * E * 4 + E * M * es)
     fill = torch.empty(1 << 30, dtype=torch.uint8, device=x.device)
     add("memset_1GiB (write-only reference)", lambda: fill.zero_(), fill.numel())
     src = torch.empty(1 << 30, dtype=torch.uint8, device=x.device)
     add("copy_1GiB (read+write reference)", lambda: fill.copy_(src), 2 * fill.numel())
     rep["peak_gbs"] = pk["hbm"]
-    rep["note"] = "L2 flushed (256 MiB memset) before every timed launch"
+    rep["note"] = "L2 flushed (a 256 MiB read-only buffer is summed) before every timed launch"
     return rep
 
 

@@ -41,7 +41,7 @@ constexpr int kGmLdb = kGmCols + 8;
 
 // ---- dx = gather(ddisp) + dlogits @ Wg ------------------------------------------------------
 // Block: 8 warps, 64 tokens x 128 columns.  Warp w: tokens 16 (w & 3) .., columns 64 (w >> 2) ..
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* __restrict__ idx,
                         const int32_t* __restrict__ slot, const float* __restrict__ dlogits,
                         const __nv_bfloat16* __restrict__ wg, int64_t Ttok, int M, int E, int EP,
@@ -56,11 +56,52 @@ dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* 
   const int64_t tok0 = (int64_t)blockIdx.y * kGmTok;
   const int col0 = blockIdx.x * kGmCols;
 
-  for (int i = tid; i < kGmTok * EP; i += 256) {
-    const int tl = i / EP, e = i - tl * EP;
-    const int64_t t = tok0 + tl;
-    const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
-    split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+  // The gathered gradient rows are the kernel's HBM traffic: for k <= 2 their loads are issued
+  // first, so that they are in flight while the gate product is staged and computed.
+  constexpr int kIt = kGmTok * (kGmCols / 8) / 256;
+  const bool early = k <= 2 && ddisp != nullptr;
+  uint4 pre[kIt][2];
+  if (early) {
+#pragma unroll
+    for (int it = 0; it < kIt; ++it) {
+      const int w = tid + 256 * it;
+      const int tl = w >> 4, c8 = (w & 15) * 8;
+      const int64_t t = tok0 + tl;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        pre[it][j] = make_uint4(0, 0, 0, 0);
+        if (t < Ttok && j < k) {
+          const int s = slot[t * k + j];
+          if (s < C)
+            pre[it][j] = *reinterpret_cast<const uint4*>(
+                ddisp + ((int64_t)idx[t * k + j] * Cs + s) * M + col0 + c8);
+        }
+      }
+    }
+  }
+
+  if (E == EP && (E & 3) == 0) {            // four experts per thread and step: 16-byte loads
+    const int q4 = EP >> 2;
+    for (int i = tid; i < kGmTok * q4; i += 256) {
+      const int tl = i / q4, e = (i - tl * q4) * 4;
+      const int64_t t = tok0 + tl;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t < Ttok) v = *reinterpret_cast<const float4*>(dlogits + t * E + e);
+      __nv_bfloat16 h[4], l[4];
+      split_bf16(v.x, h[0], l[0]);
+      split_bf16(v.y, h[1], l[1]);
+      split_bf16(v.z, h[2], l[2]);
+      split_bf16(v.w, h[3], l[3]);
+      *reinterpret_cast<uint2*>(a_hi + tl * lda + e) = *reinterpret_cast<const uint2*>(h);
+      *reinterpret_cast<uint2*>(a_lo + tl * lda + e) = *reinterpret_cast<const uint2*>(l);
+    }
+  } else {
+    for (int i = tid; i < kGmTok * EP; i += 256) {
+      const int tl = i / EP, e = i - tl * EP;
+      const int64_t t = tok0 + tl;
+      const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
+      split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+    }
   }
   for (int i = tid; i < EP * (kGmCols / 8); i += 256) {
     const int e = i >> 4, v = i & 15;
@@ -114,6 +155,19 @@ dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* 
     float v[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) v[c] = cs[tl * ldc + c8 + c];
+    if (early) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t wd[4] = {pre[it][j].x, pre[it][j].y, pre[it][j].z, pre[it][j].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          v[2 * c] += __uint_as_float(wd[c] << 16);
+          v[2 * c + 1] += __uint_as_float(wd[c] & 0xffff0000u);
+        }
+      }
+      Vec16<__nv_bfloat16>::store(dx + t * M + col0 + c8, v);
+      continue;
+    }
     for (int j = 0; j < k && ddisp != nullptr; ++j) {
       const int s = slot[t * k + j];
       if (s >= C) continue;
