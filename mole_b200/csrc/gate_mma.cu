@@ -87,7 +87,8 @@ dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* 
       const int64_t t = tok0 + tl;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (t < Ttok) v = *reinterpret_cast<const float4*>(dlogits + t * E + e);
-      __nv_bfloat16 h[4], l[4];
+      __align__(8) __nv_bfloat16 h[4];
+      __align__(8) __nv_bfloat16 l[4];
       split_bf16(v.x, h[0], l[0]);
       split_bf16(v.y, h[1], l[1]);
       split_bf16(v.z, h[2], l[2]);
@@ -232,11 +233,29 @@ gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __
   for (int sub = 0; sub < chunk / kGmTok; ++sub) {
     const int64_t tok0 = chunk0 + sub * kGmTok;
     if (tok0 >= Ttok) break;                                  // block-uniform
-    for (int i = tid; i < kGmTok * EP; i += 256) {
-      const int tl = i / EP, e = i - tl * EP;
-      const int64_t t = tok0 + tl;
-      const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
-      split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+    if (E == EP && (E & 3) == 0) {          // four experts per thread and step: 16-byte loads
+      const int q4 = EP >> 2;
+      for (int i = tid; i < kGmTok * q4; i += 256) {
+        const int tl = i / q4, e = (i - tl * q4) * 4;
+        const int64_t t = tok0 + tl;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < Ttok) v = *reinterpret_cast<const float4*>(dlogits + t * E + e);
+        __align__(8) __nv_bfloat16 h[4];
+      __align__(8) __nv_bfloat16 l[4];
+        split_bf16(v.x, h[0], l[0]);
+        split_bf16(v.y, h[1], l[1]);
+        split_bf16(v.z, h[2], l[2]);
+        split_bf16(v.w, h[3], l[3]);
+        *reinterpret_cast<uint2*>(a_hi + tl * lda + e) = *reinterpret_cast<const uint2*>(h);
+        *reinterpret_cast<uint2*>(a_lo + tl * lda + e) = *reinterpret_cast<const uint2*>(l);
+      }
+    } else {
+      for (int i = tid; i < kGmTok * EP; i += 256) {
+        const int tl = i / EP, e = i - tl * EP;
+        const int64_t t = tok0 + tl;
+        const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
+        split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+      }
     }
     for (int i = tid; i < kGmTok * (kGmCols / 8); i += 256) {
       const int tl = i >> 4, v = i & 15;
