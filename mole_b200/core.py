@@ -132,6 +132,14 @@ class Record:
     slots: List[int] = field(default_factory=list)
 
 
+def exchange_geometry(rec: "Record", local_experts: int, chunk_bytes: int):
+    """Byte geometry of one record's all-to-all inside the ``[W][L][Cs][M]`` chunk buffers:
+    ``(bytes_per_peer, peer_stride_bytes, byte_offset)``.  Peer ``q``'s block starts at
+    ``q * L * chunk``; the record covers its experts ``[base_in_all, base_in_all + batch_size)``
+    of every block (MOLE/cpp/core.cpp:144-179 addresses the same sub-blocks per expert batch)."""
+    return (rec.batch_size * chunk_bytes, local_experts * chunk_bytes, rec.base_in_all * chunk_bytes)
+
+
 def build_records(s_experts: int, d_experts: int, ebatch_size: int, use_pool: bool,
                   view_pool_size: int, prefetched: int):
     """Records and launch groups exactly as MOLE/cpp/core.cpp:1009-1051 builds them: GPU-resident
@@ -333,8 +341,7 @@ class MOLECore:
             for ri in g:
                 rec = records[ri]
                 if W > 1:       # first exchange of this record's experts, on the comm stream
-                    MOLEDist.all2all(x0, dispatched, rec.batch_size * chunk_bytes, L * chunk_bytes,
-                                     rec.base_in_all * chunk_bytes, stream=comm)
+                    MOLEDist.all2all(x0, dispatched, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
                 self._fetch_para(rec)
             for ri in g:
                 rec = records[ri]
@@ -352,8 +359,7 @@ class MOLECore:
                 rec = records[ri]
                 if W > 1:       # return exchange, on the comm stream after this record's compute
                     ExpertStreamCtx.wait(comm, comp)
-                    MOLEDist.all2all(ret, out_local, rec.batch_size * chunk_bytes, L * chunk_bytes,
-                                     rec.base_in_all * chunk_bytes, stream=comm)
+                    MOLEDist.all2all(ret, out_local, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
         if W > 1:
             ExpertStreamCtx.wait(comp, comm)
         if requires_grad:
@@ -403,8 +409,7 @@ class MOLECore:
             for ri in g:
                 rec = records[ri]
                 if W > 1:
-                    MOLEDist.all2all(g_local, dout, rec.batch_size * chunk_bytes, L * chunk_bytes,
-                                     rec.base_in_all * chunk_bytes, stream=comm)
+                    MOLEDist.all2all(g_local, dout, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
                 self._fetch_para(rec)          # weights are fetched again for backward
             for ri in g:
                 rec = records[ri]
@@ -430,8 +435,7 @@ class MOLECore:
                 rec = records[ri]
                 if W > 1 and input_requires_grad:
                     ExpertStreamCtx.wait(comm, comp)
-                    MOLEDist.all2all(ret, dx_local, rec.batch_size * chunk_bytes, L * chunk_bytes,
-                                     rec.base_in_all * chunk_bytes, stream=comm)
+                    MOLEDist.all2all(ret, dx_local, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
         if W > 1:
             ExpertStreamCtx.wait(comp, comm)
         if self.d_experts > 0:

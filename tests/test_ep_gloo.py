@@ -61,3 +61,70 @@ def test_oracle_ep_two_ranks_matches_single_process():
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+# --------------------------------------------------------------------------------------------
+# host side of the product's exchange: records -> byte geometry of each all-to-all
+# --------------------------------------------------------------------------------------------
+def _all2all_bytes(recv, send, bytes_per_peer, peer_stride, offset, rank, world):
+    """What the library's exchange does with these arguments, on CPU tensors through gloo: block
+    ``q`` of ``send`` (``bytes_per_peer`` bytes at ``offset + q * peer_stride``) goes to rank
+    ``q`` and lands in block ``rank`` of its ``recv``."""
+    sb, rb = send.view(torch.uint8).view(-1), recv.view(torch.uint8).view(-1)
+    outs = [sb[offset + q * peer_stride: offset + q * peer_stride + bytes_per_peer].clone()
+            for q in range(world)]
+    ins = [torch.empty(bytes_per_peer, dtype=torch.uint8) for _ in range(world)]
+    ins[rank].copy_(outs[rank])
+    reqs = [dist.isend(outs[q], q) for q in range(world) if q != rank]
+    reqs += [dist.irecv(ins[q], q) for q in range(world) if q != rank]
+    for r in reqs:
+        r.wait()
+    for r in range(world):
+        rb[offset + r * peer_stride: offset + r * peer_stride + bytes_per_peer] = ins[r]
+
+
+def _geometry_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mole_b200.core import build_records, exchange_geometry
+        L, Cs, Md = 6, 4, 8                        # 6 local experts in records of 4 and 2
+        E_total = L * world
+        # element (e, s, m) of rank r's dispatched buffer carries its own coordinates
+        disp = torch.empty(E_total, Cs, Md)
+        for e in range(E_total):
+            disp[e] = rank * 1000 + e * 10 + torch.arange(Cs)[:, None] + torch.zeros(Md)
+        records, groups = build_records(L, 0, 4, False, 0, 0)
+        assert [(r.base_in_all, r.batch_size) for r in records] == [(0, 4), (4, 2)]
+        chunk_bytes = Cs * Md * disp.element_size()
+        x0 = torch.full((world, L, Cs, Md), -1.0)
+        for rec in records:
+            _all2all_bytes(x0, disp, *exchange_geometry(rec, L, chunk_bytes), rank, world)
+        # rank `rank` owns global experts [rank * L, (rank + 1) * L): chunk [w][l] must be what
+        # source rank w dispatched to global expert rank * L + l
+        ok = True
+        for w in range(world):
+            for l in range(L):
+                want = w * 1000 + (rank * L + l) * 10 + torch.arange(Cs)[:, None] + torch.zeros(Md)
+                ok = ok and torch.equal(x0[w, l], want)
+        # the return exchange with the same geometry brings every chunk back to its source
+        back = torch.full_like(disp, -1.0)
+        for rec in records:
+            _all2all_bytes(back, x0, *exchange_geometry(rec, L, chunk_bytes), rank, world)
+        ok = ok and torch.equal(back, disp)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_record_exchange_geometry_two_ranks():
+    """The byte ranges the pipeline hands to the exchange, record by record, reproduce the
+    expert-parallel layout ([source rank][local expert] chunks) and its inverse."""
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_geometry_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert all(ret.get(r) for r in range(world)), dict(ret)
+
