@@ -327,8 +327,11 @@ class MOLECore:
             ExpertStreamCtx.wait(comm, comp)
             with torch.cuda.stream(comm):
                 MOLEDist.all2all(rcounts, counts, stream=comm)
-            for t in (x0, rcounts, out_local, ret, dispatched, counts):
-                t.record_stream(comm)
+            # No record_stream on these buffers: the compute stream joins the communication
+            # stream before this method returns, so every later use or reuse of their memory on
+            # the compute stream is already ordered behind the exchange.  (record_stream makes
+            # the caching allocator hold the blocks back and fall through to cudaMalloc on the
+            # next step: 0.2-0.9 ms per allocation.)
         else:
             x0, rcounts, out_local = dispatched, counts, torch.empty_like(dispatched)
             ret = out_local
@@ -395,9 +398,6 @@ class MOLECore:
             dx_local = torch.empty_like(g_local) if input_requires_grad else None
             ret = torch.empty_like(dout) if input_requires_grad else None
             ExpertStreamCtx.wait(comm, comp)
-            for t in (g_local, dx_local, ret, dout):
-                if t is not None:
-                    t.record_stream(comm)
         else:
             g_local = dout
             dx_local = torch.empty_like(dout) if input_requires_grad else None
