@@ -149,6 +149,23 @@ int mole_combine_bwd(const void* dy, const void* rows, const float* gates,
                      const int32_t* counts, const int32_t* offsets, const int32_t* perm,
                      int64_t T, int32_t M, int32_t E, int32_t k, int32_t Cs, int32_t dtype,
                      void* drows, float* dgates, void* stream);
+
+/* Push-style first exchange: dispatch (forward) and the combine's row gradient (backward) write
+ * their valid rows straight into the receive buffer of each expert's owner.  peer_rows[q] is
+ * rank q's buffer [W, L, Cs, M] mapped into this process, peer_counts[q] its int32 [W * L] count
+ * array; row (e, s) of this rank lands in chunk (rank, e % L) of rank e / L.  No pad rows are
+ * written: the receiver packs rows by count.  Replaces fast_encode + _BatchRecord::first_a2a
+ * (MOLE/moe/layer.py:448-449, MOLE/cpp/core.cpp:144-179) and the backward mirror. */
+int mole_dispatch_fwd_peer(const void* x, const int32_t* counts, const int32_t* offsets,
+                           const int32_t* perm, int64_t T, int32_t M, int32_t E, int32_t k,
+                           int32_t Cs, int32_t dtype, void* const* peer_rows,
+                           int32_t* const* peer_counts, int32_t n_peers, int32_t rank,
+                           void* stream);
+int mole_combine_bwd_peer(const void* dy, const void* rows, const float* gates,
+                          const int32_t* counts, const int32_t* offsets, const int32_t* perm,
+                          int64_t T, int32_t M, int32_t E, int32_t k, int32_t Cs, int32_t dtype,
+                          void* const* peer_rows, int32_t n_peers, int32_t rank, float* dgates,
+                          void* stream);
 /* backward of dispatch fused with the gate's input gradient:
  * dx[t] = sum_j kept * ddisp[idx*Cs + slot] + dlogits[t,:] @ wg
  * (ddisp may be NULL: gate term only; dlogits and wg may both be NULL: dispatch term only) */
@@ -215,6 +232,24 @@ int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts, const int32_t* s
                  void* dx1, void* dx, void* gw1, void* gb1, void* gw2, void* gb2,
                  void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The same two calls with the return exchange fused into the last GEMM: the output rows (FC2 in
+ * forward, dX in backward) are stored straight into the source ranks' receive buffers instead of
+ * a local buffer that an all-to-all then sends.  peer_out[w] / peer_dx[w] is rank w's buffer
+ * [E_total, Cs, M] mapped into this process (mole_peer_open; this rank's own buffer for
+ * w == rank); the rows of chunk (w, l) land in chunk rank * L + l of it.  bf16 tensor-core path
+ * with n_src > 1 only.  Replaces _BatchRecord::second_a2a (MOLE/cpp/core.cpp:180-210) and its
+ * backward mirror; the caller orders readers behind the writers with mole_barrier. */
+int mole_ffn_fwd_peer(const mole_ffn_desc* desc, const int32_t* counts,
+                      const int32_t* slot_of_expert, const void* x, const void* w1, const void* b1,
+                      const void* w2, const void* b2, void* x1, void* h, void* const* peer_out,
+                      int32_t rank, void* workspace, int64_t workspace_bytes, void* stream);
+int mole_ffn_bwd_peer(const mole_ffn_desc* desc, const int32_t* counts,
+                      const int32_t* slot_of_expert, const int32_t* grad_slot_of_expert,
+                      const void* dout, const void* x, const void* x1, const void* h,
+                      const void* w1, const void* w2, void* dx1, void* const* peer_dx,
+                      int32_t rank, void* gw1, void* gb1, void* gw2, void* gb2, void* workspace,
+                      int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * streams.  Replaces the 16-stream manager (MOLE/cpp/stream.cpp:38-144) and its wait
  * helpers (stream.cpp:156-205).  Roles follow the reference: 1 = H2D transfer, 2 = compute,
@@ -245,6 +280,20 @@ int mole_comm_destroy(mole_comm* comm);
  * expert batch of a capacity-strided buffer (MOLE/cpp/core.cpp:156-161) without re-layout. */
 int mole_all2all(mole_comm* comm, const void* send, void* recv, int64_t bytes_per_peer,
                  int64_t peer_stride_bytes, void* stream);
+
+/* Peer-visible device buffers for the push-style exchange: the owner allocates (plain device
+ * memory, zeroed) and exports a 64-byte CUDA IPC handle; a peer process opens it and passes the
+ * mapped pointer to the *_peer entry points, whose kernels store rows straight into it over
+ * NVLink (replaces the send buffer + grouped ncclSend/ncclRecv of MOLE/cpp/core.cpp:144-210,
+ * MOLE/cpp/communication.cpp:68-100).  mole_barrier: every rank has finished what it enqueued
+ * on `stream` before the call (4-byte grouped send/recv with every peer); `scratch` is 8 * world
+ * bytes of device memory. */
+int mole_peer_alloc(int64_t bytes, void** ptr);
+int mole_peer_free(void* ptr);
+int mole_peer_export(void* ptr, uint8_t* handle64);
+int mole_peer_open(const uint8_t* handle64, void** ptr);
+int mole_peer_close(void* ptr);
+int mole_barrier(mole_comm* comm, void* scratch, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * (e) offloaded experts.  Replaces _UniMem (MOLE/cpp/define.hpp:143-193,

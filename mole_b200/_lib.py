@@ -74,6 +74,20 @@ SIGNATURES = {
     "mole_comm_create": (C.c_int, [C.POINTER(C.c_uint8), _i32, _i32, _i32, C.POINTER(_p)]),
     "mole_comm_destroy": (C.c_int, [_p]),
     "mole_all2all": (C.c_int, [_p, _p, _p, _i64, _i64, _p]),
+    "mole_ffn_fwd_peer": (C.c_int, [C.POINTER(FfnDesc), _p, _pi32, _p, _p, _p, _p, _p, _p, _p,
+                                    C.POINTER(_p), _i32, _p, _i64, _p]),
+    "mole_ffn_bwd_peer": (C.c_int, [C.POINTER(FfnDesc), _p, _pi32, _pi32, _p, _p, _p, _p, _p, _p, _p,
+                                    C.POINTER(_p), _i32, _p, _p, _p, _p, _p, _i64, _p]),
+    "mole_dispatch_fwd_peer": (C.c_int, [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32,
+                                         C.POINTER(_p), C.POINTER(_p), _i32, _i32, _p]),
+    "mole_combine_bwd_peer": (C.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32,
+                                        C.POINTER(_p), _i32, _i32, _p, _p]),
+    "mole_peer_alloc": (C.c_int, [_i64, C.POINTER(_p)]),
+    "mole_peer_free": (C.c_int, [_p]),
+    "mole_peer_export": (C.c_int, [_p, C.POINTER(C.c_uint8)]),
+    "mole_peer_open": (C.c_int, [C.POINTER(C.c_uint8), C.POINTER(_p)]),
+    "mole_peer_close": (C.c_int, [_p]),
+    "mole_barrier": (C.c_int, [_p, _p, _p]),
     "mole_pool_create": (C.c_int, [_p, _i32, _i32, _i32, _i32, C.POINTER(_p)]),
     "mole_pool_destroy": (C.c_int, [_p]),
     "mole_pool_base": (C.c_int, [_p, _i32, C.POINTER(_p)]),

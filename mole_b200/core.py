@@ -132,6 +132,91 @@ class Record:
     slots: List[int] = field(default_factory=list)
 
 
+class _DeviceBytes:
+    """Raw device memory as a ``__cuda_array_interface__`` object (so that torch can view it)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class PeerExchange:
+    """Receive buffers of the push-style exchange of one layer, visible to every rank of the node.
+
+    Instead of filling a local buffer and sending it (``first_a2a`` / ``second_a2a``,
+    MOLE/cpp/core.cpp:144-210), the producing kernel stores each row straight into the memory of
+    the rank that consumes it, over NVLink:
+
+      x0   [W, L, Cs, M]   dispatch rows for my experts        written by every rank's dispatch
+      ret  [E, Cs, M]      expert outputs for my tokens        written by the owners' FC2 epilogue
+      g    [W, L, Cs, M]   output gradients for my experts     written by every rank's combine bwd
+      dx   [E, Cs, M]      input gradients for my tokens       written by the owners' dX epilogue
+      counts [W * L] i32   valid rows per (source, expert)     written with the dispatch rows
+
+    Each buffer is plain device memory exported through a CUDA IPC handle and mapped by the peers
+    (no multicast object).  Writers and readers are ordered by four barriers per fwd+bwd
+    (``mole_barrier``): every reader of a buffer has finished before the barrier that precedes
+    its next writer, see ``MOLECore.forward_peer`` / ``backward_peer``."""
+
+    KINDS = ("x0", "ret", "g", "dx", "counts")
+
+    def __init__(self, world, rank, L, Cs, M, dtype, device, group):
+        import torch.distributed as dist
+        self.world, self.rank, self.L, self.Cs, self.M, self.dtype = world, rank, L, Cs, M, dtype
+        self.key = (world, L, Cs, M, dtype)
+        es = torch.empty(0, dtype=dtype).element_size()
+        row_bytes = world * L * Cs * M * es
+        sizes = {"x0": row_bytes, "ret": row_bytes, "g": row_bytes, "dx": row_bytes,
+                 "counts": max(256, world * L * 4)}
+        self.own, handles = {}, []
+        for kind in self.KINDS:
+            p = C.c_void_p()
+            check(lib.mole_peer_alloc(sizes[kind], C.byref(p)))
+            self.own[kind] = p.value
+            h = (C.c_uint8 * 64)()
+            check(lib.mole_peer_export(p, h))
+            handles.append(bytes(h))
+        mine = torch.tensor(list(b"".join(handles)), dtype=torch.uint8, device=device)
+        every = torch.empty(world * mine.numel(), dtype=torch.uint8, device=device)
+        dist.all_gather_into_tensor(every, mine, group=group)
+        every = every.cpu().view(world, len(self.KINDS), 64)
+        self.mapped, self.table = [], {}
+        for ki, kind in enumerate(self.KINDS):
+            ptrs = []
+            for q in range(world):
+                if q == rank:
+                    ptrs.append(self.own[kind])
+                    continue
+                h = (C.c_uint8 * 64)(*every[q, ki].tolist())
+                p = C.c_void_p()
+                check(lib.mole_peer_open(h, C.byref(p)))
+                self.mapped.append(p.value)
+                ptrs.append(p.value)
+            self.table[kind] = (C.c_void_p * world)(*ptrs)
+
+        def view(kind, tdtype, shape):
+            mem = _DeviceBytes(self.own[kind], sizes[kind])
+            t = torch.as_tensor(mem, device=device)
+            n = 1
+            for s in shape:
+                n *= s
+            return t[: n * torch.empty(0, dtype=tdtype).element_size()].view(tdtype).view(*shape)
+
+        E = world * L
+        self.x0 = view("x0", dtype, (world, L, Cs, M))
+        self.g = view("g", dtype, (world, L, Cs, M))
+        self.ret = view("ret", dtype, (E, Cs, M))
+        self.dx = view("dx", dtype, (E, Cs, M))
+        self.counts = view("counts", torch.int32, (world * L,))
+        self.scratch = torch.zeros(8 * world, dtype=torch.uint8, device=device)
+        self.serial = 0          # forward passes so far: backward checks that its buffers are still its own
+        dist.barrier(group=group)
+
+    def barrier(self):
+        check(lib.mole_barrier(MOLEDist._instance.comm, C.c_void_p(self.scratch.data_ptr()),
+                               C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+
 def exchange_geometry(rec: "Record", local_experts: int, chunk_bytes: int):
     """Byte geometry of one record's all-to-all inside the ``[W][L][Cs][M]`` chunk buffers:
     ``(bytes_per_peer, peer_stride_bytes, byte_offset)``.  Peer ``q``'s block starts at
@@ -177,7 +262,7 @@ def build_records(s_experts: int, d_experts: int, ebatch_size: int, use_pool: bo
 class _Saved:
     """Activations one forward keeps for its backward (``x0`` and ``extras[0]`` of the
     reference's records, MOLE/cpp/define.hpp:638-639)."""
-    __slots__ = ("x0", "x1", "h", "counts", "Cs", "n_src")
+    __slots__ = ("x0", "x1", "h", "counts", "Cs", "n_src", "serial")
 
 
 class MOLECore:
@@ -208,6 +293,8 @@ class MOLECore:
         self._saved: Optional[_Saved] = None
         self._records: List[Record] = []
         self._grad_staging = None
+        self._peer: Optional[PeerExchange] = None
+        self._peer_failed = False
         if adv_adam:
             raise NotImplementedError(
                 "adv_adam (optimizer step fused after backward) is outside the MoE-layer hot path")
@@ -264,6 +351,87 @@ class MOLECore:
         if batch_size == 0:
             return
         _get_UniMem().fetch(self.cpu_params, 0, batch_size, 0, 0)
+
+    # -- push-style exchange ---------------------------------------------------------------
+    def peer_for(self, Cs: int, M: int, dtype, device) -> Optional[PeerExchange]:
+        """The layer's ``PeerExchange`` when the exchange can be pushed (several ranks of one
+        node, GPU-resident experts in one record, the bf16 tensor-core path), else ``None`` and
+        the pipeline uses the all-to-all.  ``MOLE_PEER_EXCHANGE=0`` switches it off."""
+        import os
+        W = self.world_size
+        L = self.s_experts + self.d_experts
+        if (W < 2 or W > 16 or self.d_experts > 0 or self.ebatch_size < L or self._peer_failed
+                or dtype != torch.bfloat16 or self.ffn_backend == 1
+                or os.environ.get("MOLE_PEER_EXCHANGE", "1") == "0"
+                or MOLEDist._instance is None or MOLEDist._instance.comm is None):
+            return None
+        F = self._ffn_dim()
+        if M % 128 or F % 128:
+            return None
+        key = (W, L, Cs, M, dtype)
+        if self._peer is None or self._peer.key != key:
+            try:
+                self._peer = PeerExchange(W, MOLEDist._instance.rank, L, Cs, M, dtype, device,
+                                          MOLEDist._instance.MOLE_group)
+            except Exception as e:      # no peer mapping on this system: keep the all-to-all
+                import warnings
+                warnings.warn(f"push-style exchange unavailable ({e}); using the all-to-all")
+                self._peer_failed = True
+                self._peer = None
+        return self._peer
+
+    def forward_peer(self, peer: PeerExchange, requires_grad: bool) -> torch.Tensor:
+        """Expert pipeline when the dispatch has already pushed this rank's rows into the owners'
+        ``x0`` buffers: barrier, grouped FFN whose FC2 epilogue stores the outputs into the
+        source ranks' ``ret`` buffers, barrier.  Returns this rank's ``ret`` ``[E, Cs, M]``."""
+        W, L, Cs, M = peer.world, peer.L, peer.Cs, peer.M
+        F = self._ffn_dim()
+        records, _ = build_records(self.s_experts, 0, self.ebatch_size, False, 0, 0)
+        rec = records[0]
+        peer.serial += 1
+        peer.barrier()                      # every rank's dispatch rows and counts have landed
+        rows_total = W * L * Cs
+        x1 = torch.empty(rows_total, F, dtype=self.dtype, device=peer.x0.device)
+        h = torch.empty(rows_total, F, dtype=self.dtype, device=peer.x0.device)
+        w1, b1, w2, b2, slots, n_slots = self._weights(rec)
+        desc = self._desc(M, F, W, Cs, rec, n_slots)
+        ws = ops.ffn_workspace(desc, peer.x0.device)
+        ops.ffn_fwd_peer(desc, peer.counts, peer.x0, w1, b1, w2, b2, x1, h, peer, ws, slots)
+        peer.barrier()                      # every owner's output rows have landed in my ret
+        if requires_grad:
+            s = _Saved()
+            s.x0, s.x1, s.h, s.counts, s.Cs, s.n_src = peer.x0, x1, h, peer.counts, Cs, W
+            s.serial = peer.serial
+            self._saved = s
+        return peer.ret
+
+    def backward_peer(self, peer: PeerExchange, input_requires_grad: bool = True) -> torch.Tensor:
+        """Mirror of ``forward_peer``: the combine's backward has pushed the output gradients
+        into the owners' ``g`` buffers; dX's epilogue stores into the source ranks' ``dx``."""
+        s = self._saved
+        if s is None:
+            raise RuntimeError("MOLECore.backward without a matching forward")
+        if getattr(s, "serial", None) != peer.serial:
+            raise RuntimeError(
+                "the layer ran forward again before this backward: the push-style exchange keeps "
+                "one set of buffers per layer (set MOLE_PEER_EXCHANGE=0 for such schedules)")
+        W, L, Cs, M = peer.world, peer.L, peer.Cs, peer.M
+        F = self._ffn_dim()
+        records, _ = build_records(self.s_experts, 0, self.ebatch_size, False, 0, 0)
+        rec = records[0]
+        peer.barrier()                      # every rank's gradient rows have landed in my g
+        dx1 = torch.empty(W * L * Cs, F, dtype=self.dtype, device=peer.g.device)
+        accumulate = self.acc_step > 1 and (self.step % self.acc_step) != 0
+        w1, _, w2, _, slots, n_slots = self._weights(rec)
+        desc = self._desc(M, F, W, Cs, rec, n_slots, accumulate, self.s_experts)
+        ws = ops.ffn_workspace(desc, peer.g.device)
+        grads = self.gpu_grads
+        ops.ffn_bwd_peer(desc, s.counts, peer.g, s.x0, s.x1, s.h, w1, w2, dx1, peer, grads[0],
+                         grads[1], grads[2], grads[3], ws, slots, slots)
+        peer.barrier()                      # every owner's dX rows have landed in my dx
+        self.step += 1
+        self._saved = None
+        return peer.dx
 
     # -- helpers ---------------------------------------------------------------------------
     def _desc(self, M, F, n_src, Cs, rec: Record, n_slots, accumulate=False, n_grad_slots=0):

@@ -136,6 +136,22 @@ __device__ __forceinline__ float act_grad(float x, int act, int gelu_bwd) {
 //   expert_tile_start[l - e_begin] .. [+1]  tile index range of expert l
 //   expert_pair_start  the same ranges counted in pairs of tiles (odd counts rounded up)
 //   n_tiles        total
+// Push-style exchange: where row (e, s) of a rank's expert-major [E][Cs] row space lives when it
+// is written straight into the memory of the expert's owner.  Rank q owns experts
+// [q * L, (q + 1) * L); its receive buffer is [W][L][Cs][width] (chunk [w][l] = what rank w
+// sent for local expert l) and base[q] is that buffer mapped into this process.
+constexpr int kMaxPeers = 16;
+struct PeerMap {
+  void* base[kMaxPeers];
+  int32_t* counts[kMaxPeers];     // rank q's [W * L] valid-row counts (dispatch only), or null
+  int n;                          // ranks; 0: no peers, rows stay local
+  int rank, L;
+};
+__device__ __forceinline__ int64_t peer_row(const PeerMap& pm, int e, int s, int Cs, int* owner) {
+  *owner = e / pm.L;
+  return ((int64_t)pm.rank * pm.L + (e - *owner * pm.L)) * Cs + s;
+}
+
 struct Schedule {
   int32_t* n_tiles;            // [1]
   int32_t* expert_tile_start;  // [L + 1]

@@ -19,16 +19,28 @@ template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32)
 dispatch_fwd_kernel(const T* __restrict__ x, const int32_t* __restrict__ counts,
                     const int32_t* __restrict__ offsets, const int32_t* __restrict__ perm,
-                    int M, int E, int k, int Cs, T* __restrict__ disp) {
+                    int M, int E, int k, int Cs, T* __restrict__ disp,
+                    const __grid_constant__ PeerMap pm) {
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (row >= (int64_t)E * Cs) return;
   const int e = (int)(row / Cs), s = (int)(row - (int64_t)e * Cs);
   const int cnt = counts[e];
+  uint4* dst;
+  if (pm.n > 0) {
+    // pushed to the expert's owner: valid rows only (the receiver packs rows by count and pads
+    // there), and the count itself
+    int owner;
+    const int64_t prow = peer_row(pm, e, s, Cs, &owner);
+    if (s == 0 && lane == 0) pm.counts[owner][prow / Cs] = cnt;
+    if (s >= cnt) return;
+    dst = reinterpret_cast<uint4*>(static_cast<T*>(pm.base[owner]) + prow * M);
+  } else {
+    dst = reinterpret_cast<uint4*>(disp + row * M);
+  }
   const int padded = (cnt + kTileRows - 1) / kTileRows * kTileRows;
   if (s >= padded) return;
-  uint4* dst = reinterpret_cast<uint4*>(disp + row * M);
   const int nvec = M / V;
   if (s >= cnt) {
     for (int i = lane; i < nvec; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
@@ -81,7 +93,8 @@ __global__ void __launch_bounds__(kRowWarps * 32)
 combine_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ rows,
                    const float* __restrict__ gates, const int32_t* __restrict__ counts,
                    const int32_t* __restrict__ offsets, const int32_t* __restrict__ perm, int M,
-                   int E, int k, int Cs, T* __restrict__ drows, float* __restrict__ dgates) {
+                   int E, int k, int Cs, T* __restrict__ drows, float* __restrict__ dgates,
+                   const __grid_constant__ PeerMap pm) {
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
@@ -91,7 +104,15 @@ combine_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ rows,
   const int padded = (cnt + kTileRows - 1) / kTileRows * kTileRows;
   if (s >= padded) return;
   const int nvec = M / V;
-  T* dst = drows + row * M;
+  T* dst;
+  if (pm.n > 0) {                      // gradient rows go straight to the expert's owner
+    if (s >= cnt) return;
+    int owner;
+    const int64_t prow = peer_row(pm, e, s, Cs, &owner);
+    dst = static_cast<T*>(pm.base[owner]) + prow * M;
+  } else {
+    dst = drows + row * M;
+  }
   if (s >= cnt) {
     uint4* d4 = reinterpret_cast<uint4*>(dst);
     for (int i = lane; i < nvec; i += 32) d4[i] = make_uint4(0, 0, 0, 0);
@@ -214,7 +235,46 @@ extern "C" int mole_dispatch_fwd(const void* x, const int32_t* counts, const int
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)(((int64_t)E * Cs + kRowWarps - 1) / kRowWarps);
   MOLE_BY_DTYPE(dtype, dispatch_fwd_kernel<T><<<grid, kRowWarps * 32, 0, st>>>(
-      static_cast<const T*>(x), counts, offsets, perm, M, E, k, Cs, static_cast<T*>(disp)));
+      static_cast<const T*>(x), counts, offsets, perm, M, E, k, Cs, static_cast<T*>(disp),
+      PeerMap{}));
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+static int fill_peer_map(PeerMap& pm, void* const* rows, int32_t* const* counts, int n_peers,
+                         int rank, int E) {
+  MOLE_REQUIRE(rows != nullptr, "null peer table");
+  MOLE_REQUIRE(n_peers >= 2 && n_peers <= kMaxPeers, "peer count %d not in [2, %d]", n_peers, kMaxPeers);
+  MOLE_REQUIRE(rank >= 0 && rank < n_peers, "rank %d outside the %d peers", rank, n_peers);
+  MOLE_REQUIRE(E % n_peers == 0, "%d experts do not divide over %d ranks", E, n_peers);
+  pm = PeerMap{};
+  for (int q = 0; q < n_peers; ++q) {
+    MOLE_REQUIRE(rows[q] != nullptr, "null buffer for peer %d", q);
+    pm.base[q] = rows[q];
+    if (counts) {
+      MOLE_REQUIRE(counts[q] != nullptr, "null count array for peer %d", q);
+      pm.counts[q] = counts[q];
+    }
+  }
+  pm.n = n_peers;
+  pm.rank = rank;
+  pm.L = E / n_peers;
+  return MOLE_OK;
+}
+
+extern "C" int mole_dispatch_fwd_peer(const void* x, const int32_t* counts, const int32_t* offsets,
+                                      const int32_t* perm, int64_t T_, int32_t M, int32_t E,
+                                      int32_t k, int32_t Cs, int32_t dtype, void* const* peer_rows,
+                                      int32_t* const* peer_counts, int32_t n_peers, int32_t rank,
+                                      void* stream) {
+  if (int rc = check_rows(T_, M, E, k, Cs, dtype)) return rc;
+  MOLE_REQUIRE(x && counts && offsets && perm && peer_counts, "null pointer argument");
+  PeerMap pm;
+  if (int rc = fill_peer_map(pm, peer_rows, peer_counts, n_peers, rank, E)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)(((int64_t)E * Cs + kRowWarps - 1) / kRowWarps);
+  MOLE_BY_DTYPE(dtype, dispatch_fwd_kernel<T><<<grid, kRowWarps * 32, 0, st>>>(
+      static_cast<const T*>(x), counts, offsets, perm, M, E, k, Cs, static_cast<T*>(nullptr), pm));
   MOLE_LAUNCH_OK();
   return MOLE_OK;
 }
@@ -246,7 +306,26 @@ extern "C" int mole_combine_bwd(const void* dy, const void* rows, const float* g
   const unsigned grid = (unsigned)(((int64_t)E * Cs + kRowWarps - 1) / kRowWarps);
   MOLE_BY_DTYPE(dtype, combine_bwd_kernel<T><<<grid, kRowWarps * 32, 0, st>>>(
       static_cast<const T*>(dy), static_cast<const T*>(rows), gates, counts, offsets, perm, M, E,
-      k, Cs, static_cast<T*>(drows), dgates));
+      k, Cs, static_cast<T*>(drows), dgates, PeerMap{}));
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+extern "C" int mole_combine_bwd_peer(const void* dy, const void* rows, const float* gates,
+                                     const int32_t* counts, const int32_t* offsets,
+                                     const int32_t* perm, int64_t T_, int32_t M, int32_t E,
+                                     int32_t k, int32_t Cs, int32_t dtype, void* const* peer_rows,
+                                     int32_t n_peers, int32_t rank, float* dgates, void* stream) {
+  if (int rc = check_rows(T_, M, E, k, Cs, dtype)) return rc;
+  MOLE_REQUIRE(dy && rows && gates && counts && offsets && perm && dgates, "null pointer argument");
+  PeerMap pm;
+  if (int rc = fill_peer_map(pm, peer_rows, nullptr, n_peers, rank, E)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MOLE_CUDA_OK(cudaMemsetAsync(dgates, 0, (size_t)T_ * k * 4, st));
+  const unsigned grid = (unsigned)(((int64_t)E * Cs + kRowWarps - 1) / kRowWarps);
+  MOLE_BY_DTYPE(dtype, combine_bwd_kernel<T><<<grid, kRowWarps * 32, 0, st>>>(
+      static_cast<const T*>(dy), static_cast<const T*>(rows), gates, counts, offsets, perm, M, E,
+      k, Cs, static_cast<T*>(nullptr), dgates, pm));
   MOLE_LAUNCH_OK();
   return MOLE_OK;
 }

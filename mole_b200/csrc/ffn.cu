@@ -105,12 +105,58 @@ extern "C" int mole_ffn_workspace_bytes(const mole_ffn_desc* d, int64_t* bytes) 
   return MOLE_OK;
 }
 
+// Push-style return exchange: the scattered output rows of FC2 (forward) and dX (backward) go
+// straight into the source ranks' receive buffers.  Needs the packed path (its row map).
+static int peers_for_ffn(const mole_ffn_desc* d, void* const* peer_rows, int rank, PeerMap& pm) {
+  MOLE_REQUIRE(compacting(d), "peer output needs the bf16 tensor-core path with n_src > 1");
+  MOLE_REQUIRE(peer_rows != nullptr, "null peer table");
+  MOLE_REQUIRE(d->n_src <= kMaxPeers, "at most %d source ranks", kMaxPeers);
+  MOLE_REQUIRE(rank >= 0 && rank < d->n_src, "rank %d outside the %d source ranks", rank, d->n_src);
+  pm = PeerMap{};
+  for (int q = 0; q < d->n_src; ++q) {
+    MOLE_REQUIRE(peer_rows[q] != nullptr, "null buffer for peer %d", q);
+    pm.base[q] = peer_rows[q];
+  }
+  pm.n = d->n_src;
+  pm.rank = rank;
+  pm.L = d->L;
+  return MOLE_OK;
+}
+
+static int ffn_fwd_impl(const mole_ffn_desc* d, const int32_t* counts,
+                        const int32_t* slot_of_expert, const void* x, const void* w1,
+                        const void* b1, const void* w2, const void* b2, void* x1, void* h,
+                        void* out, const PeerMap* peers, void* workspace,
+                        int64_t workspace_bytes, void* stream);
+
 extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
                             const int32_t* slot_of_expert, const void* x, const void* w1,
                             const void* b1, const void* w2, const void* b2, void* x1, void* h,
                             void* out, void* workspace, int64_t workspace_bytes, void* stream) {
+  MOLE_REQUIRE(out != nullptr, "null pointer argument");
+  return ffn_fwd_impl(d, counts, slot_of_expert, x, w1, b1, w2, b2, x1, h, out, nullptr, workspace,
+                      workspace_bytes, stream);
+}
+
+extern "C" int mole_ffn_fwd_peer(const mole_ffn_desc* d, const int32_t* counts,
+                                 const int32_t* slot_of_expert, const void* x, const void* w1,
+                                 const void* b1, const void* w2, const void* b2, void* x1, void* h,
+                                 void* const* peer_out, int32_t rank, void* workspace,
+                                 int64_t workspace_bytes, void* stream) {
   if (int rc = check_desc(d)) return rc;
-  MOLE_REQUIRE(counts && x && w1 && b1 && w2 && b2 && x1 && h && out && workspace,
+  PeerMap pm;
+  if (int rc = peers_for_ffn(d, peer_out, rank, pm)) return rc;
+  return ffn_fwd_impl(d, counts, slot_of_expert, x, w1, b1, w2, b2, x1, h, nullptr, &pm, workspace,
+                      workspace_bytes, stream);
+}
+
+static int ffn_fwd_impl(const mole_ffn_desc* d, const int32_t* counts,
+                        const int32_t* slot_of_expert, const void* x, const void* w1,
+                        const void* b1, const void* w2, const void* b2, void* x1, void* h,
+                        void* out, const PeerMap* peers, void* workspace,
+                        int64_t workspace_bytes, void* stream) {
+  if (int rc = check_desc(d)) return rc;
+  MOLE_REQUIRE(counts && x && w1 && b1 && w2 && b2 && x1 && h && (out || peers) && workspace,
                "null pointer argument");
   MOLE_REQUIRE(workspace_bytes >= workspace_bytes_of(d), "workspace too small");
   if (d->e_begin == d->e_end) return MOLE_OK;
@@ -146,8 +192,16 @@ extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
   a.A = h; a.W = w2; a.w_nk = 0; a.N = d->M; a.K = d->F; a.bias = b2;
   a.out0 = out; a.out1 = nullptr; a.epi = EPI_BIAS;
   a.rowmap = compact ? wk.rowmap : nullptr;          // back to the (source, expert) chunks
+  if (peers) { a.peers = *peers; a.peer_Cs = d->Cs; }
   return row_gemm(d, a, st);
 }
+
+static int ffn_bwd_impl(const mole_ffn_desc* d, const int32_t* counts,
+                        const int32_t* slot_of_expert, const int32_t* grad_slot_of_expert,
+                        const void* dout, const void* x, const void* x1, const void* h,
+                        const void* w1, const void* w2, void* dx1, void* dx, const PeerMap* peers,
+                        void* gw1, void* gb1, void* gw2, void* gb2, void* workspace,
+                        int64_t workspace_bytes, void* stream);
 
 extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
                             const int32_t* slot_of_expert, const int32_t* grad_slot_of_expert,
@@ -155,6 +209,30 @@ extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
                             const void* w1, const void* w2, void* dx1, void* dx, void* gw1,
                             void* gb1, void* gw2, void* gb2, void* workspace,
                             int64_t workspace_bytes, void* stream) {
+  return ffn_bwd_impl(d, counts, slot_of_expert, grad_slot_of_expert, dout, x, x1, h, w1, w2, dx1,
+                      dx, nullptr, gw1, gb1, gw2, gb2, workspace, workspace_bytes, stream);
+}
+
+extern "C" int mole_ffn_bwd_peer(const mole_ffn_desc* d, const int32_t* counts,
+                                 const int32_t* slot_of_expert,
+                                 const int32_t* grad_slot_of_expert, const void* dout,
+                                 const void* x, const void* x1, const void* h, const void* w1,
+                                 const void* w2, void* dx1, void* const* peer_dx, int32_t rank,
+                                 void* gw1, void* gb1, void* gw2, void* gb2, void* workspace,
+                                 int64_t workspace_bytes, void* stream) {
+  if (int rc = check_desc(d)) return rc;
+  PeerMap pm;
+  if (int rc = peers_for_ffn(d, peer_dx, rank, pm)) return rc;
+  return ffn_bwd_impl(d, counts, slot_of_expert, grad_slot_of_expert, dout, x, x1, h, w1, w2, dx1,
+                      nullptr, &pm, gw1, gb1, gw2, gb2, workspace, workspace_bytes, stream);
+}
+
+static int ffn_bwd_impl(const mole_ffn_desc* d, const int32_t* counts,
+                        const int32_t* slot_of_expert, const int32_t* grad_slot_of_expert,
+                        const void* dout, const void* x, const void* x1, const void* h,
+                        const void* w1, const void* w2, void* dx1, void* dx, const PeerMap* peers,
+                        void* gw1, void* gb1, void* gw2, void* gb2, void* workspace,
+                        int64_t workspace_bytes, void* stream) {
   if (int rc = check_desc(d)) return rc;
   MOLE_REQUIRE(counts && dout && x && x1 && h && w1 && w2 && dx1 && gw1 && gb1 && gw2 && gb2 &&
                workspace, "null pointer argument");
@@ -212,10 +290,11 @@ extern "C" int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts,
   c.A = dx1; c.N = d->F; c.out = gb1;
   if (int rc = colsum(d->dtype, c, st)) return rc;
   // dX = dX1 W1:  W1_e read as [K=F][N=M]
-  if (dx != nullptr) {
+  if (dx != nullptr || peers != nullptr) {
     a.A = dx1; a.W = w1; a.w_nk = 0; a.N = d->M; a.K = d->F; a.bias = nullptr; a.aux = nullptr;
     a.out0 = dx; a.out1 = nullptr; a.epi = EPI_STORE;
     a.rowmap = compact ? wk.rowmap : nullptr;
+    if (peers) { a.peers = *peers; a.peer_Cs = d->Cs; }
     if (int rc = row_gemm(d, a, st)) return rc;
   }
   return MOLE_OK;

@@ -31,6 +31,8 @@ struct RowGemmArgs {
   int e_begin, n_experts;   // experts covered by the schedule
   int single_cta;           // tensor cores: keep to the one-CTA kernel (A/B comparisons)
   const int32_t* rowmap;    // tensor cores, FC2 / dX: scatter output rows (-1 = drop), or null
+  PeerMap peers;            // with rowmap: the scattered rows go to their source ranks (n > 0)
+  int peer_Cs;              // rows per chunk of the receive buffers
   Schedule sched;
   SlotMap wslot;
 };

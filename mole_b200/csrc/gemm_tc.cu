@@ -155,6 +155,18 @@ __device__ __forceinline__ void st_v8(void* p, const uint32_t (&w)[8]) {
                ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
                  "r"(w[6]), "r"(w[7]) : "memory");
 }
+// Store of a scattered output row piece: rows that go to another GPU's memory (over NVLink) use
+// two 16-byte stores, local rows one 32-byte store.
+__device__ __forceinline__ void st_scatter(void* p, const uint32_t (&w)[8], bool remote) {
+  if (remote) {
+    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};"
+                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};"
+                 ::"l"(static_cast<char*>(p) + 16), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+  } else {
+    st_v8(p, w);
+  }
+}
 __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* p, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -222,6 +234,8 @@ struct TcParams {
   const int32_t* tile_rows;           // valid rows per tile: the weight-gradient GEMM stops its K loop there
   const int32_t* expert_pair_start;   // 2-CTA kernel: prefix of ceil(tiles / 2) per expert
   const int32_t* rowmap;              // FC2 / dX: output row of every GEMM row (-1: none), or null
+  void* peer_base[kMaxPeers];         // with rowmap: receive buffer of every source rank (peer_n > 0)
+  int peer_n, peer_rank, peer_L, peer_Cs;
   int n_experts, e_begin;
   int N, K;                 // rows mode: output columns / reduction.  wgrad: Q / unused
   int P;                    // wgrad: output rows per expert
@@ -326,8 +340,9 @@ constexpr int kEpiStep = 16;
 
 template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM, int NSTEPS>
 __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
-                                              bool valid, int64_t obase, const float* bias_s,
-                                              int c_begin, uint32_t (&pre)[NSTEPS][8]) {
+                                              bool valid, __nv_bfloat16* sout, int64_t obase,
+                                              const float* bias_s, int c_begin,
+                                              uint32_t (&pre)[NSTEPS][8]) {
   {
 #pragma unroll
     for (int step = 0; step < NSTEPS; ++step) {
@@ -376,7 +391,7 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
           }
           o[i] = pack_bf16(lo, hi);
         }
-        if (valid) st_v8(p.out0 + obase + c, o);
+        if (valid) st_scatter(sout + obase + c, o, p.peer_n > 0);
       } else if (EPI == EPI_DACT) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -387,7 +402,7 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           o[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-        if (valid) st_v8(p.out0 + obase + c, o);
+        if (valid) st_scatter(sout + obase + c, o, p.peer_n > 0);
       }
     }
   }
@@ -659,11 +674,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int lrow = quarter * 32 + lane;
       int64_t obase;            // element offset of (row, n0) in the output
       bool valid = true;
+      __nv_bfloat16* sout = p.out0;     // where a scattered row goes (FC2 / dX)
       if (MODE == TC_ROWS) {
         int64_t orow = w.row0 + lrow;
         if (EvTraits<EV>::scatter && p.rowmap != nullptr) {
           orow = p.rowmap[orow];
           valid = orow >= 0;
+          if (p.peer_n > 0 && valid) {          // row of chunk [w][l] -> source rank w's buffer
+            const int per_rank = p.peer_L * p.peer_Cs;
+            const int wq = (int)(orow / per_rank);
+            const int rem = (int)(orow - (int64_t)wq * per_rank);
+            const int l = rem / p.peer_Cs;
+            sout = static_cast<__nv_bfloat16*>(p.peer_base[wq]);
+            orow = ((int64_t)p.peer_rank * p.peer_L + l) * p.peer_Cs + (rem - l * p.peer_Cs);
+          }
         }
         obase = orow * p.N + w.n0;
       } else {
@@ -685,7 +709,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                cq * (BN / 4), store_strip[ew]);
       else
         epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
-            p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, valid, obase,
+            p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, valid, sout, obase,
             bias_strip[ew], cq * (BN / 4), pre);
       if (!empty) {
         tcgen05_fence_before();
@@ -977,6 +1001,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int r0 = w.row0[rank];
       int64_t obase = 0;
       bool valid = true;
+      __nv_bfloat16* sout = p.out0;
       const __nv_bfloat16* bias = nullptr;
       constexpr int NSTEPS = kBN2 / 4 / kEpiStep;
       uint32_t pre[NSTEPS][8];
@@ -986,6 +1011,14 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           if (EvTraits<EV>::scatter && p.rowmap != nullptr) {
             orow = p.rowmap[orow];
             valid = orow >= 0;
+            if (p.peer_n > 0 && valid) {
+              const int per_rank = p.peer_L * p.peer_Cs;
+              const int wq = (int)(orow / per_rank);
+              const int rem = (int)(orow - (int64_t)wq * per_rank);
+              const int l = rem / p.peer_Cs;
+              sout = static_cast<__nv_bfloat16*>(p.peer_base[wq]);
+              orow = ((int64_t)p.peer_rank * p.peer_L + l) * p.peer_Cs + (rem - l * p.peer_Cs);
+            }
           }
           obase = orow * p.N + w.n0;
         } else {
@@ -1007,7 +1040,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                                  cq * (kBN2 / 4), store_strip[ew]);
         else
           epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
-              p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, valid, obase,
+              p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, valid, sout, obase,
               bias_strip[ew], cq * (kBN2 / 4), pre);
       }
       if (!empty) {
@@ -1226,6 +1259,12 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   p.fault = device_fault_word();
   p.slot = a.wslot;
   p.rowmap = a.rowmap;
+  p.peer_n = a.peers.n;
+  p.peer_rank = a.peers.rank;
+  p.peer_L = a.peers.L;
+  p.peer_Cs = a.peer_Cs;
+  for (int q = 0; q < kMaxPeers; ++q) p.peer_base[q] = a.peers.base[q];
+  MOLE_REQUIRE(a.peers.n == 0 || a.rowmap != nullptr, "peer scatter needs the row map");
   MOLE_REQUIRE(a.rowmap == nullptr || a.epi == EPI_BIAS || a.epi == EPI_STORE,
                "only FC2 / dX outputs can be scattered");
   const int max_items = a.sched.max_tiles * (a.N / BN);

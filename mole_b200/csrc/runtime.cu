@@ -264,6 +264,57 @@ extern "C" int mole_all2all(mole_comm* c, const void* send, void* recv, int64_t 
   return MOLE_OK;
 }
 
+// ---- peer-visible buffers (push-style exchange) ------------------------------------------
+// Plain cudaMalloc memory exported with the CUDA IPC handle: a peer process maps it and its
+// kernels store rows straight into it over NVLink.  No multicast object is involved.
+extern "C" int mole_peer_alloc(int64_t bytes, void** ptr) {
+  MOLE_REQUIRE(ptr && bytes > 0, "bad argument");
+  MOLE_CUDA_OK(cudaMalloc(ptr, (size_t)bytes));
+  MOLE_CUDA_OK(cudaMemset(*ptr, 0, (size_t)bytes));
+  return MOLE_OK;
+}
+extern "C" int mole_peer_free(void* ptr) {
+  if (ptr) MOLE_CUDA_OK(cudaFree(ptr));
+  return MOLE_OK;
+}
+extern "C" int mole_peer_export(void* ptr, uint8_t* handle64) {
+  MOLE_REQUIRE(ptr && handle64, "bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  MOLE_CUDA_OK(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle64, &h, 64);
+  return MOLE_OK;
+}
+extern "C" int mole_peer_open(const uint8_t* handle64, void** ptr) {
+  MOLE_REQUIRE(ptr && handle64, "bad argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  MOLE_CUDA_OK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return MOLE_OK;
+}
+extern "C" int mole_peer_close(void* ptr) {
+  if (ptr) MOLE_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return MOLE_OK;
+}
+// All ranks have reached this point of `stream` (and with it every kernel enqueued before): a
+// 4-byte grouped send/recv with every peer.  `scratch` holds 8 * world bytes on the device.
+extern "C" int mole_barrier(mole_comm* c, void* scratch, void* stream) {
+  MOLE_REQUIRE(c && scratch, "bad argument");
+  if (c->world == 1) return MOLE_OK;
+  NcclApi* n = nccl_api();
+  if (!n) return fail(MOLE_ERR_NCCL, "libnccl.so.2 could not be loaded");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* s = static_cast<char*>(scratch);
+  MOLE_NCCL_OK(n, n->GroupStart());
+  for (int q = 0; q < c->world; ++q) {
+    if (q == c->rank) continue;
+    MOLE_NCCL_OK(n, n->Send(s + 4 * q, 4, ncclInt8, q, c->comm, st));
+    MOLE_NCCL_OK(n, n->Recv(s + 4 * (c->world + q), 4, ncclInt8, q, c->comm, st));
+  }
+  MOLE_NCCL_OK(n, n->GroupEnd());
+  return MOLE_OK;
+}
+
 // ---- offloaded-expert slot pool -----------------------------------------------------
 struct mole_pool {
   mole_ctx* ctx;

@@ -60,6 +60,12 @@ class Dispatch(torch.autograd.Function):
         ctx.plan = plan
         ctx.holder = holder
         ctx.meta = (x.shape[1], x.dtype, x.device)
+        peer = holder.get("peer") if holder is not None else None
+        if peer is not None:
+            # rows go straight into the owners' memory; the local [E, Cs, M] tensor is a
+            # placeholder that carries the autograd edge only
+            ops.dispatch_peer(x, plan, peer)
+            return x.new_zeros(1).expand(plan.E, plan.Cs, x.shape[1])
         return ops.dispatch(x, plan)
 
     @staticmethod
@@ -75,16 +81,20 @@ class Dispatch(torch.autograd.Function):
 
 class Combine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, rows, gates, plan):
+    def forward(ctx, rows, gates, plan, peer=None):
         ctx.plan = plan
+        ctx.peer = peer
         ctx.save_for_backward(rows, gates)
         return ops.combine(rows, plan, gates)
 
     @staticmethod
     def backward(ctx, dy):
         rows, gates = ctx.saved_tensors
+        if ctx.peer is not None:        # row gradients go straight to the experts' owners
+            dgates = ops.combine_bwd_peer(dy.contiguous(), rows, ctx.plan, gates, ctx.peer)
+            return dy.new_zeros(1).expand_as(rows), dgates, None, None
         drows, dgates = ops.combine_bwd(dy.contiguous(), rows, ctx.plan, gates)
-        return drows, dgates, None
+        return drows, dgates, None, None
 
 
 class BatchFusedFWD(torch.autograd.Function):
@@ -105,16 +115,23 @@ class BatchFusedFWD(torch.autograd.Function):
         ctx.input_requires_grad = ctx.needs_input_grad[0]
         ctx.dummy_shape = dummy_param.shape
         timer = module.timer if time_it and hasattr(module, "timer") else None
+        ctx.peer = getattr(module, "_peer_exchange", None)
         if timer:
             timer.start_fwd()
-        out = core.forward(dispatched_input.contiguous(), counts, True)
+        if ctx.peer is not None:
+            out = core.forward_peer(ctx.peer, True)
+        else:
+            out = core.forward(dispatched_input.contiguous(), counts, True)
         if timer:
             timer.stop_fwd()
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        dx = ctx.core.backward(grad_out.contiguous(), ctx.counts, ctx.input_requires_grad)
+        if ctx.peer is not None:
+            dx = ctx.core.backward_peer(ctx.peer, ctx.input_requires_grad)
+        else:
+            dx = ctx.core.backward(grad_out.contiguous(), ctx.counts, ctx.input_requires_grad)
         dummy_grad = torch.zeros(ctx.dummy_shape, device=grad_out.device, dtype=grad_out.dtype)
         return dx, None, dummy_grad, None, None
 

@@ -243,13 +243,19 @@ class MOLEModule(torch.nn.Module):
         # when x needs a gradient the gate's backward will run after the dispatch's and can fuse
         # the two contributions to dx
         holder["gate_needs_x_grad"] = bool(resized_input.requires_grad and torch.is_grad_enabled())
+        # several ranks of one node: rows are stored straight into the consuming rank's memory
+        # (dispatch -> owners, FC2 -> sources, and the mirror in backward) instead of all-to-alls
+        peer = self.MOLECore.peer_for(plan.Cs, self.embed_dim, self.dtype, resized_input.device)
+        holder["peer"] = peer
         dispatched_input = Dispatch.apply(resized_input, plan, holder)
 
         self._route_counts = plan.counts
+        self._peer_exchange = peer
         experts_output = BatchFusedFWD.apply(dispatched_input, self, self.dummy_param, time_it, prefetch)
         self._route_counts = None
+        self._peer_exchange = None
 
-        expert_output = Combine.apply(experts_output, gates, plan)
+        expert_output = Combine.apply(experts_output, gates, plan, peer)
         out = expert_output.reshape(original_shape).to(original_dtype)
 
         if prefetch:

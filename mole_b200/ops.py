@@ -233,6 +233,45 @@ def ffn_bwd(desc: FfnDesc, counts, dout, x, x1, h, w1, w2, dx1, dx, gw1, gb1, gw
                            _ptr(gw2), _ptr(gb2), _ptr(ws), ws.numel(), _stream()))
 
 
+# ---- push-style exchange (rows stored straight into the owner's / source's memory) -----------
+def dispatch_peer(x: torch.Tensor, plan: RoutePlan, peer) -> None:
+    """Dispatch whose rows (and per-expert counts) land in the receive buffers of the experts'
+    owners; ``peer`` is a ``core.PeerExchange``."""
+    T, M = x.shape
+    check(lib.mole_dispatch_fwd_peer(_ptr(x), _ptr(plan.counts), _ptr(plan.offsets), _ptr(plan.perm),
+                                     T, M, plan.E, plan.k, plan.Cs, _dt(x), peer.table["x0"],
+                                     peer.table["counts"], peer.world, peer.rank, _stream()))
+
+
+def combine_bwd_peer(dy: torch.Tensor, rows: torch.Tensor, plan: RoutePlan, gates: torch.Tensor,
+                     peer) -> torch.Tensor:
+    """Combine backward whose row gradients land in the owners' buffers; returns ``dgates``."""
+    M = rows.shape[-1]
+    dgates = torch.empty(plan.T, plan.k, dtype=torch.float32, device=rows.device)
+    check(lib.mole_combine_bwd_peer(_ptr(dy), _ptr(rows), _ptr(gates), _ptr(plan.counts),
+                                    _ptr(plan.offsets), _ptr(plan.perm), plan.T, M, plan.E, plan.k,
+                                    plan.Cs, _dt(rows), peer.table["g"], peer.world, peer.rank,
+                                    _ptr(dgates), _stream()))
+    return dgates
+
+
+def ffn_fwd_peer(desc: FfnDesc, counts, x, w1, b1, w2, b2, x1, h, peer, ws,
+                 slot_of_expert: Optional[Sequence[int]] = None) -> None:
+    check(lib.mole_ffn_fwd_peer(C.byref(desc), _ptr(counts), _slot_array(slot_of_expert, desc.L),
+                                _ptr(x), _ptr(w1), _ptr(b1), _ptr(w2), _ptr(b2), _ptr(x1), _ptr(h),
+                                peer.table["ret"], peer.rank, _ptr(ws), ws.numel(), _stream()))
+
+
+def ffn_bwd_peer(desc: FfnDesc, counts, dout, x, x1, h, w1, w2, dx1, peer, gw1, gb1, gw2, gb2, ws,
+                 slot_of_expert: Optional[Sequence[int]] = None,
+                 grad_slot_of_expert: Optional[Sequence[int]] = None) -> None:
+    check(lib.mole_ffn_bwd_peer(C.byref(desc), _ptr(counts), _slot_array(slot_of_expert, desc.L),
+                                _slot_array(grad_slot_of_expert, desc.L), _ptr(dout), _ptr(x),
+                                _ptr(x1), _ptr(h), _ptr(w1), _ptr(w2), _ptr(dx1), peer.table["dx"],
+                                peer.rank, _ptr(gw1), _ptr(gb1), _ptr(gw2), _ptr(gb2), _ptr(ws),
+                                ws.numel(), _stream()))
+
+
 def device_fault() -> int:
     """Code left by a kernel whose bounded wait ran out (0 = none); synchronises the stream."""
     f = C.c_int32()

@@ -34,16 +34,27 @@ def main():
         inp["b1"] = torch.randn(E, F, generator=torch.Generator().manual_seed(1)) * 0.05
         inp["b2"] = torch.randn(E, M, generator=torch.Generator().manual_seed(2)) * 0.05
     mine = per_rank[rank]
-    m = MOLEModule(0, E, M, F, -1, k, max(1, L // 2), {"local_rank": local, "world_size": world, "rank": rank},
+    # "records": two records per rank, NCCL all-to-all per record.  "push": one record, rows
+    # stored straight into the consuming rank's memory (dispatch / FC2 / combine bwd / dX).
+    mode = sys.argv[1] if len(sys.argv) > 1 else "records"
+    ebatch = L if mode == "push" else max(1, L // 2)
+    m = MOLEModule(0, E, M, F, -1, k, ebatch, {"local_rank": local, "world_size": world, "rank": rank},
                    "gelu", 1, False, False, dtype=dtype)
     sl = slice(rank * L, (rank + 1) * L)
     m.set_layer_state({"gate": [mine["wg"], None],
                        "experts": [[mine["w1"][e], mine["b1"][e], mine["w2"][e], mine["b2"][e]]
                                    for e in range(rank * L, (rank + 1) * L)]}, grad=False)
     x = mine["x"].to(dtype).cuda().requires_grad_(True)
-    y = m(x, capacity_factor=cf)
-    (y.float() * mine["gy"].cuda()).sum().backward()
+    for _ in range(2 if mode == "push" else 1):      # twice: the push buffers are reused per step
+        x.grad = None
+        m.gate[0].linear.weight.grad = None
+        y = m(x, capacity_factor=cf)
+        (y.float() * mine["gy"].cuda()).sum().backward()
     torch.cuda.synchronize()
+    if mode == "push":
+        assert m.MOLECore._peer is not None, "the push-style exchange was not taken"
+    else:
+        assert m.MOLECore._peer is None
 
     # every rank's routing decisions come from that rank's GPU scores
     scores = [torch.empty(T, E, device="cuda") for _ in range(world)]
@@ -69,7 +80,7 @@ def main():
         assert_close(g, want, dtype, f"rank {rank} {name}", scale=2.0)
     dist.barrier()
     if rank == 0:
-        print("EP_OK", world)
+        print("EP_OK", world, mode)
     dist.destroy_process_group()
 
 

@@ -19,14 +19,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("mode", ["records", "push"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_expert_parallel_layer_matches_oracle(world):
+def test_expert_parallel_layer_matches_oracle(world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           str(ROOT / "tests" / "ep_worker.py")]
+           str(ROOT / "tests" / "ep_worker.py"), mode]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    assert f"EP_OK {world}" in res.stdout
+    assert f"EP_OK {world} {mode}" in res.stdout
