@@ -168,31 +168,51 @@ class PeerExchange:
         row_bytes = world * L * Cs * M * es
         sizes = {"x0": row_bytes, "ret": row_bytes, "g": row_bytes, "dx": row_bytes,
                  "counts": max(256, world * L * 4)}
-        self.own, handles = {}, []
-        for kind in self.KINDS:
-            p = C.c_void_p()
-            check(lib.mole_peer_alloc(sizes[kind], C.byref(p)))
-            self.own[kind] = p.value
-            h = (C.c_uint8 * 64)()
-            check(lib.mole_peer_export(p, h))
-            handles.append(bytes(h))
-        mine = torch.tensor(list(b"".join(handles)), dtype=torch.uint8, device=device)
+        # Every rank takes the same decision: each phase ends in a collective that carries the
+        # ranks' success flags, and one failure anywhere makes all of them give the buffers up
+        # (the caller then uses the all-to-all pipeline on every rank).
+        self.own, self.mapped, self.table = {}, [], {}
+        handles, err = [], None
+        try:
+            for kind in self.KINDS:
+                p = C.c_void_p()
+                check(lib.mole_peer_alloc(sizes[kind], C.byref(p)))
+                self.own[kind] = p.value
+                h = (C.c_uint8 * 64)()
+                check(lib.mole_peer_export(p, h))
+                handles.append(bytes(h))
+        except Exception as e:
+            err = e
+            handles = [bytes(64)] * len(self.KINDS)
+        blob = b"".join(handles) + bytes([0 if err else 1])
+        mine = torch.tensor(list(blob), dtype=torch.uint8, device=device)
         every = torch.empty(world * mine.numel(), dtype=torch.uint8, device=device)
         dist.all_gather_into_tensor(every, mine, group=group)
-        every = every.cpu().view(world, len(self.KINDS), 64)
-        self.mapped, self.table = [], {}
-        for ki, kind in enumerate(self.KINDS):
-            ptrs = []
-            for q in range(world):
-                if q == rank:
-                    ptrs.append(self.own[kind])
-                    continue
-                h = (C.c_uint8 * 64)(*every[q, ki].tolist())
-                p = C.c_void_p()
-                check(lib.mole_peer_open(h, C.byref(p)))
-                self.mapped.append(p.value)
-                ptrs.append(p.value)
-            self.table[kind] = (C.c_void_p * world)(*ptrs)
+        every = every.cpu().view(world, -1)
+        if int(every[:, -1].min()) == 0:
+            self.close()
+            raise RuntimeError(f"peer buffers could not be allocated or exported on every rank ({err})")
+        every = every[:, :-1].reshape(world, len(self.KINDS), 64)
+        try:
+            for ki, kind in enumerate(self.KINDS):
+                ptrs = []
+                for q in range(world):
+                    if q == rank:
+                        ptrs.append(self.own[kind])
+                        continue
+                    h = (C.c_uint8 * 64)(*every[q, ki].tolist())
+                    p = C.c_void_p()
+                    check(lib.mole_peer_open(h, C.byref(p)))
+                    self.mapped.append(p.value)
+                    ptrs.append(p.value)
+                self.table[kind] = (C.c_void_p * world)(*ptrs)
+        except Exception as e:
+            err = e
+        flag = torch.tensor([0 if err else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 0:
+            self.close(group)
+            raise RuntimeError(f"peer buffers could not be mapped on every rank ({err})")
 
         def view(kind, tdtype, shape):
             mem = _DeviceBytes(self.own[kind], sizes[kind])
@@ -215,6 +235,20 @@ class PeerExchange:
     def barrier(self):
         check(lib.mole_barrier(MOLEDist._instance.comm, C.c_void_p(self.scratch.data_ptr()),
                                C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def close(self, group=None):
+        """Unmaps the peers' buffers, then frees this rank's own; with ``group`` (call on every
+        rank) a barrier sits between the two, because a mapping must be closed before its owner
+        frees the memory."""
+        for p in self.mapped:
+            lib.mole_peer_close(C.c_void_p(p))
+        self.mapped = []
+        if group is not None or self.world > 1 and self.table:
+            import torch.distributed as dist
+            dist.barrier(group=group)
+        for p in self.own.values():
+            lib.mole_peer_free(C.c_void_p(p))
+        self.own = {}
 
 
 def exchange_geometry(rec: "Record", local_experts: int, chunk_bytes: int):
