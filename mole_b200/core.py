@@ -211,7 +211,7 @@ class PeerExchange:
         flag = torch.tensor([0 if err else 1], dtype=torch.int32, device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
         if int(flag.item()) == 0:
-            self.close(group)
+            self.close(True, group)
             raise RuntimeError(f"peer buffers could not be mapped on every rank ({err})")
 
         def view(kind, tdtype, shape):
@@ -236,14 +236,14 @@ class PeerExchange:
         check(lib.mole_barrier(MOLEDist._instance.comm, C.c_void_p(self.scratch.data_ptr()),
                                C.c_void_p(torch.cuda.current_stream().cuda_stream)))
 
-    def close(self, group=None):
-        """Unmaps the peers' buffers, then frees this rank's own; with ``group`` (call on every
-        rank) a barrier sits between the two, because a mapping must be closed before its owner
-        frees the memory."""
+    def close(self, barrier=False, group=None):
+        """Unmaps the peers' buffers, then frees this rank's own.  ``barrier=True`` (then every
+        rank must call it) puts a barrier between the two: a mapping has to be closed before its
+        owner frees the memory."""
         for p in self.mapped:
             lib.mole_peer_close(C.c_void_p(p))
         self.mapped = []
-        if group is not None or self.world > 1 and self.table:
+        if barrier:
             import torch.distributed as dist
             dist.barrier(group=group)
         for p in self.own.values():
