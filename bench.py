@@ -164,6 +164,26 @@ def init_weights(m, cfg, rank, L, dtype, device):
             m.gate[0].logit_bias = (-cfg["zipf"] * beta * torch.log(ranks.float())).to(device)
 
 
+def bind_to_gpu_cores(index):
+    """Several ranks on one host: keep this process (and with it the pinned host buffers it
+    touches first) on the CPU cores next to its GPU, as NVML reports them.  A host-process
+    setting only; returns the number of cores kept, or None when nothing was changed."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        near = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1}
+        keep = near & os.sched_getaffinity(0)
+        if keep:
+            os.sched_setaffinity(0, keep)
+            return len(keep)
+    except Exception:
+        pass
+    return None
+
+
 def run_ours(args):
     import torch.distributed as dist
     from mole_b200 import MOLEModule, _lib, ops
@@ -172,6 +192,7 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    near_cores = bind_to_gpu_cores(local) if world > 1 else None
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
@@ -357,6 +378,8 @@ def run_ours(args):
         "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": n1 - n0,
         "host_enqueue_ms_per_step": host_ms, "warmup_settling_steps": extra,
     }
+    if near_cores:
+        out["host_cores_near_gpu"] = near_cores
     plan = m.last_plan
     pairs = int(plan.counts.sum().item())
     out["config"]["kept_pairs_rank0"] = pairs
