@@ -155,18 +155,6 @@ __device__ __forceinline__ void st_v8(void* p, const uint32_t (&w)[8]) {
                ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
                  "r"(w[6]), "r"(w[7]) : "memory");
 }
-// Store of a scattered output row piece: rows that go to another GPU's memory (over NVLink) use
-// two 16-byte stores, local rows one 32-byte store.
-__device__ __forceinline__ void st_scatter(void* p, const uint32_t (&w)[8], bool remote) {
-  if (remote) {
-    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};"
-                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
-    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};"
-                 ::"l"(static_cast<char*>(p) + 16), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-  } else {
-    st_v8(p, w);
-  }
-}
 __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* p, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -338,11 +326,61 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // filled at the same point.
 constexpr int kEpiStep = 16;
 
+// Scattered output rows that go to another GPU (push-style exchange): 16- or 32-byte stores
+// of 32 different rows per instruction cross NVLink as 32 small packets, and FC2 / dX ran at a
+// sixth of the link bandwidth.  The warp's 32 rows x (NSTEPS * 16) columns go through a 1 KB
+// shared-memory strip in passes (as in epilogue_lines below); after a pass NSTEPS neighbouring
+// lanes hold one row's NSTEPS * 32 contiguous bytes, and fetch that row's destination (each row
+// has its own: rank, chunk, slot) from the lane that owns the row.
+constexpr int kScatterStripBytes = 1024;
+template <int NSTEPS>
+__device__ __forceinline__ void scatter_lines(const uint32_t (&o)[NSTEPS][8], __nv_bfloat16* rowptr,
+                                              bool valid, uint8_t* strip) {
+  constexpr int kRowBytes = NSTEPS * 32;
+  constexpr int kRows = kScatterStripBytes / kRowBytes;   // rows per pass
+  constexpr int kPasses = 32 / kRows;
+  constexpr int kMask = (2 * NSTEPS - 1) & 7;
+  static_assert(kRows * NSTEPS == 32, "one 32-byte piece per lane and pass");
+  const int lane = threadIdx.x & 31;
+  const int wr = lane % kRows, wpass = lane / kRows;
+  const int rr = lane / NSTEPS, ra = lane % NSTEPS;
+  const uint64_t myptr = reinterpret_cast<uint64_t>(rowptr);
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    if (wpass == j) {
+#pragma unroll
+      for (int q = 0; q < NSTEPS; ++q)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          *reinterpret_cast<uint4*>(strip + wr * kRowBytes + (((2 * q + h) ^ (wr & kMask)) << 4)) =
+              make_uint4(o[q][4 * h], o[q][4 * h + 1], o[q][4 * h + 2], o[q][4 * h + 3]);
+    }
+    __syncwarp();
+    const int owner = kRows * j + rr;                      // lane whose row this lane stores
+    const uint64_t dptr = __shfl_sync(0xffffffffu, myptr, owner);
+    const int dvalid = __shfl_sync(0xffffffffu, (int)valid, owner);
+    const uint8_t* row = strip + rr * kRowBytes;
+    const uint4 lo = *reinterpret_cast<const uint4*>(row + (((2 * ra) ^ (rr & kMask)) << 4));
+    const uint4 hi = *reinterpret_cast<const uint4*>(row + (((2 * ra + 1) ^ (rr & kMask)) << 4));
+    if (dvalid) {
+      char* d = reinterpret_cast<char*>(dptr) + 32 * ra;
+      asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};"
+                   ::"l"(d), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+      asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};"
+                   ::"l"(d + 16), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+    }
+    __syncwarp();
+  }
+}
+
 template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM, int NSTEPS>
 __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
                                               bool valid, __nv_bfloat16* sout, int64_t obase,
                                               const float* bias_s, int c_begin,
-                                              uint32_t (&pre)[NSTEPS][8]) {
+                                              uint32_t (&pre)[NSTEPS][8], uint8_t* strip) {
+  const bool remote = (EPI == EPI_BIAS || EPI == EPI_STORE) && p.peer_n > 0;
+  uint32_t keep[NSTEPS][8];       // remote rows: the whole slice first, then whole-line stores
   {
 #pragma unroll
     for (int step = 0; step < NSTEPS; ++step) {
@@ -391,7 +429,12 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
           }
           o[i] = pack_bf16(lo, hi);
         }
-        if (valid) st_scatter(sout + obase + c, o, p.peer_n > 0);
+        if (remote) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) keep[step][i] = o[i];
+        } else if (valid) {
+          st_v8(sout + obase + c, o);
+        }
       } else if (EPI == EPI_DACT) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -402,10 +445,17 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           o[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-        if (valid) st_scatter(sout + obase + c, o, p.peer_n > 0);
+        if (remote) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) keep[step][i] = o[i];
+        } else if (valid) {
+          st_v8(sout + obase + c, o);
+        }
       }
     }
   }
+  if ((EPI == EPI_BIAS || EPI == EPI_STORE) && remote)
+    scatter_lines<NSTEPS>(keep, sout + obase + c_begin, valid, strip);
 }
 
 // Epilogue with whole-line stores.  After tcgen05.ld a thread holds 16 consecutive columns of ONE
@@ -529,6 +579,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ int abort_flag_s;
   __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
+  __shared__ __align__(16) uint8_t scatter_strip[kEpiWarps][kScatterStripBytes];   // ... scatter_lines
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -710,7 +761,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       else
         epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
             p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, valid, sout, obase,
-            bias_strip[ew], cq * (BN / 4), pre);
+            bias_strip[ew], cq * (BN / 4), pre, scatter_strip[ew]);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -851,6 +902,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __shared__ int abort_flag_s;
   __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
+  __shared__ __align__(16) uint8_t scatter_strip[kEpiWarps][kScatterStripBytes];   // ... scatter_lines
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1041,7 +1093,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         else
           epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
               p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, valid, sout, obase,
-              bias_strip[ew], cq * (kBN2 / 4), pre);
+              bias_strip[ew], cq * (kBN2 / 4), pre, scatter_strip[ew]);
       }
       if (!empty) {
         tcgen05_fence_before();
