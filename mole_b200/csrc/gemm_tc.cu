@@ -3,7 +3,7 @@
 //
 //   warp 0        TMA producer   (one lane): activation / weight tiles -> smem ring
 //   warp 1        MMA issuer     (one lane): tcgen05.mma over the ring, double-buffered TMEM
-//   warps 2..9    epilogue       TMEM -> registers -> fused epilogue -> global memory
+//   warps 2..17   epilogue       TMEM -> registers -> fused epilogue -> global memory
 //
 // One kernel template covers the six GEMMs of the expert FFN (MOLE/cpp/core.cpp:350-353
 // forward, :388-412 backward):

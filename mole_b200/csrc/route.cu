@@ -202,7 +202,7 @@ gate_topk_kernel(const T* __restrict__ x, const T* __restrict__ wg, const float*
 // The gate product is [T, M] x [M, E] with E <= 256: far too small for a tcgen05 tile pipeline to
 // pay off, but on CUDA cores it is FMA-bound at ~3 % of the HBM rate it should run at.  Warp-level
 // mma.sync (m16n8k16, bf16 in, fp32 accumulate in the hardware's fixed order) brings it to the
-// memory roofline: the kernel streams x once through a two-stage cp.async ring.
+// memory roofline: the kernel streams x once through a four-stage cp.async ring.
 // Block: 8 warps, 64 tokens; warp w owns tokens 16 * (w & 3) .. +15 and half of the experts.
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
