@@ -56,6 +56,13 @@ int64_t mole_capacity_stride(int64_t capacity);
 /* reads and clears the device-side fault word written by kernels whose bounded waits ran
  * out; *fault == 0 means none.  Synchronises `stream`. */
 int mole_device_fault(void* stream, int32_t* fault);
+/* the same check without a host wait, for a training loop: mole_device_fault_poll enqueues a copy
+ * of the fault word (of the current device) into pinned host memory behind the work already on
+ * `stream`; mole_device_fault_peek returns the value of the last such copy that has landed (0
+ * before the first).  MOLECore polls at the end of every backward and peeks at the start of the
+ * next forward.  The reference has no counterpart: its device code cannot time out. */
+int mole_device_fault_poll(void* stream);
+int mole_device_fault_peek(int32_t* fault);
 
 /* kernels this library has launched in this process (the benchmark reports it) */
 int mole_launch_count(int64_t* n);
@@ -127,9 +134,13 @@ int mole_gate_bwd(const float* scores, const int32_t* idx, const int32_t* slot,
                   int64_t T, int32_t E, int32_t k, int32_t C, int32_t normalize_gate,
                   float* dlogits, void* stream);
 
-/* dwg32 [E,M] f32 += dlogits^T @ x   (caller zeroes dwg32 first when it wants "=") */
+/* dwg32 [E,M] f32 += dlogits^T @ x   (caller zeroes dwg32 first when it wants "=").  The sum
+ * over tokens is taken in two stages with a fixed order (per-chunk partial products in the
+ * workspace, then one ordered reduction), so the result is bit-reproducible from run to run. */
+int mole_gate_wgrad_workspace_bytes(int64_t T, int32_t M, int32_t E, int32_t dtype, int64_t* bytes);
 int mole_gate_wgrad(const float* dlogits, const void* x, int64_t T, int32_t M, int32_t E,
-                    int32_t dtype, float* dwg32, void* stream);
+                    int32_t dtype, float* dwg32, void* workspace, int64_t workspace_bytes,
+                    void* stream);
 
 /* ------------------------------------------------------------------------------------
  * (b) dispatch / combine.  Replace fast_encode / fast_decode at

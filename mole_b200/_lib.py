@@ -42,6 +42,8 @@ SIGNATURES = {
     "mole_last_error_string": (C.c_char_p, []),
     "mole_capacity_stride": (_i64, [_i64]),
     "mole_device_fault": (C.c_int, [_p, _pi32]),
+    "mole_device_fault_poll": (C.c_int, [_p]),
+    "mole_device_fault_peek": (C.c_int, [_pi32]),
     "mole_launch_count": (C.c_int, [_pi64]),
     "mole_profile_gemm": (C.c_int, [_i32]),
     "mole_profile_read": (C.c_int, [C.POINTER(C.c_float), _pi32, _i32, _pi32]),
@@ -53,7 +55,8 @@ SIGNATURES = {
     "mole_route_from_scores": (C.c_int, [_p, _i64, _i32, _i32, _i32, _i32,
                                          _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _p]),
     "mole_gate_bwd": (C.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _p, _p]),
-    "mole_gate_wgrad": (C.c_int, [_p, _p, _i64, _i32, _i32, _i32, _p, _p]),
+    "mole_gate_wgrad_workspace_bytes": (C.c_int, [_i64, _i32, _i32, _i32, _pi64]),
+    "mole_gate_wgrad": (C.c_int, [_p, _p, _i64, _i32, _i32, _i32, _p, _p, _i64, _p]),
     "mole_dispatch_fwd": (C.c_int, [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _p, _p]),
     "mole_combine_fwd": (C.c_int, [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _p, _p]),
     "mole_combine_bwd": (C.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32,

@@ -162,12 +162,15 @@ class PeerExchange:
 
     def __init__(self, world, rank, L, Cs, M, dtype, device, group):
         import torch.distributed as dist
-        self.world, self.rank, self.L, self.Cs, self.M, self.dtype = world, rank, L, Cs, M, dtype
-        self.key = (world, L, Cs, M, dtype)
+        self.world, self.rank, self.L, self.M, self.dtype = world, rank, L, M, dtype
+        self.device, self.group = device, group
+        self.cap_Cs = Cs         # rows per chunk the buffers hold; smaller strides reuse them
+        self.key = (world, L, M, dtype)
         es = torch.empty(0, dtype=dtype).element_size()
         row_bytes = world * L * Cs * M * es
         sizes = {"x0": row_bytes, "ret": row_bytes, "g": row_bytes, "dx": row_bytes,
                  "counts": max(256, world * L * 4)}
+        self.sizes = sizes
         # Every rank takes the same decision: each phase ends in a collective that carries the
         # ranks' success flags, and one failure anywhere makes all of them give the buffers up
         # (the caller then uses the all-to-all pipeline on every rank).
@@ -213,24 +216,35 @@ class PeerExchange:
         if int(flag.item()) == 0:
             self.close(True, group)
             raise RuntimeError(f"peer buffers could not be mapped on every rank ({err})")
+        self.Cs = None
+        self.set_stride(Cs)
+        self.scratch = torch.zeros(8 * world, dtype=torch.uint8, device=device)
+        self.serial = 0          # forward passes so far: backward checks that its buffers are still its own
+        dist.barrier(group=group)
+
+    def set_stride(self, Cs: int) -> None:
+        """Views of the buffers for chunks of ``Cs <= cap_Cs`` rows (a shorter batch, another
+        capacity factor): the same memory with a smaller stride, nothing is reallocated."""
+        if Cs == self.Cs:
+            return
+        assert Cs <= self.cap_Cs
+        world, L, M, dtype = self.world, self.L, self.M, self.dtype
 
         def view(kind, tdtype, shape):
-            mem = _DeviceBytes(self.own[kind], sizes[kind])
-            t = torch.as_tensor(mem, device=device)
+            mem = _DeviceBytes(self.own[kind], self.sizes[kind])
+            t = torch.as_tensor(mem, device=self.device)
             n = 1
             for s in shape:
                 n *= s
             return t[: n * torch.empty(0, dtype=tdtype).element_size()].view(tdtype).view(*shape)
 
         E = world * L
+        self.Cs = Cs
         self.x0 = view("x0", dtype, (world, L, Cs, M))
         self.g = view("g", dtype, (world, L, Cs, M))
         self.ret = view("ret", dtype, (E, Cs, M))
         self.dx = view("dx", dtype, (E, Cs, M))
         self.counts = view("counts", torch.int32, (world * L,))
-        self.scratch = torch.zeros(8 * world, dtype=torch.uint8, device=device)
-        self.serial = 0          # forward passes so far: backward checks that its buffers are still its own
-        dist.barrier(group=group)
 
     def barrier(self):
         check(lib.mole_barrier(MOLEDist._instance.comm, C.c_void_p(self.scratch.data_ptr()),
@@ -245,10 +259,23 @@ class PeerExchange:
         self.mapped = []
         if barrier:
             import torch.distributed as dist
+            torch.cuda.synchronize()
             dist.barrier(group=group)
         for p in self.own.values():
             lib.mole_peer_free(C.c_void_p(p))
         self.own = {}
+        for name in ("x0", "g", "ret", "dx", "counts"):
+            self.__dict__.pop(name, None)
+
+    def __del__(self):
+        # Last resort (interpreter exit, a layer dropped without teardown): no collective is
+        # possible here, so only this process's mappings and memory are released.  The peers'
+        # mappings of this memory stay valid for them until they close them (CUDA IPC keeps the
+        # allocation alive while it is mapped elsewhere).
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def exchange_geometry(rec: "Record", local_experts: int, chunk_bytes: int):
@@ -402,22 +429,39 @@ class MOLECore:
         F = self._ffn_dim()
         if M % 128 or F % 128:
             return None
-        key = (W, L, Cs, M, dtype)
-        if self._peer is None or self._peer.key != key:
-            try:
-                self._peer = PeerExchange(W, MOLEDist._instance.rank, L, Cs, M, dtype, device,
-                                          MOLEDist._instance.MOLE_group)
-            except Exception as e:      # no peer mapping on this system: keep the all-to-all
-                import warnings
-                warnings.warn(f"push-style exchange unavailable ({e}); using the all-to-all")
-                self._peer_failed = True
-                self._peer = None
+        key = (W, L, M, dtype)
+        peer = self._peer
+        if peer is not None and peer.key == key and Cs <= peer.cap_Cs:
+            peer.set_stride(Cs)          # shorter batch / other capacity factor: same memory
+            return peer
+        # First use, or the chunks have outgrown the buffers.  Every rank takes this branch in the
+        # same call: the token count per rank (hence Cs) must be equal on all ranks, as the
+        # reference's equal-split exchange requires too (MOLE/cpp/core.cpp:156-161).  The old
+        # buffers go first, collectively: unmap everywhere, barrier, then free.
+        if peer is not None:
+            peer.close(True, MOLEDist._instance.MOLE_group)
+            self._peer = None
+        try:
+            self._peer = PeerExchange(W, MOLEDist._instance.rank, L, Cs, M, dtype, device,
+                                      MOLEDist._instance.MOLE_group)
+        except Exception as e:      # no peer mapping on this system: keep the all-to-all
+            import warnings
+            warnings.warn(f"push-style exchange unavailable ({e}); using the all-to-all")
+            self._peer_failed = True
+            self._peer = None
         return self._peer
+
+    def close_peer_exchange(self) -> None:
+        """Collective teardown of the layer's push-exchange buffers (every rank calls it)."""
+        if self._peer is not None:
+            self._peer.close(True, MOLEDist._instance.MOLE_group)
+            self._peer = None
 
     def forward_peer(self, peer: PeerExchange, requires_grad: bool) -> torch.Tensor:
         """Expert pipeline when the dispatch has already pushed this rank's rows into the owners'
         ``x0`` buffers: barrier, grouped FFN whose FC2 epilogue stores the outputs into the
         source ranks' ``ret`` buffers, barrier.  Returns this rank's ``ret`` ``[E, Cs, M]``."""
+        self._check_fault()
         W, L, Cs, M = peer.world, peer.L, peer.Cs, peer.M
         F = self._ffn_dim()
         records, _ = build_records(self.s_experts, 0, self.ebatch_size, False, 0, 0)
@@ -455,7 +499,7 @@ class MOLECore:
         rec = records[0]
         peer.barrier()                      # every rank's gradient rows have landed in my g
         dx1 = torch.empty(W * L * Cs, F, dtype=self.dtype, device=peer.g.device)
-        accumulate = self.acc_step > 1 and (self.step % self.acc_step) != 0
+        accumulate = self._accumulate()
         w1, _, w2, _, slots, n_slots = self._weights(rec)
         desc = self._desc(M, F, W, Cs, rec, n_slots, accumulate, self.s_experts)
         ws = ops.ffn_workspace(desc, peer.g.device)
@@ -463,11 +507,29 @@ class MOLECore:
         ops.ffn_bwd_peer(desc, s.counts, peer.g, s.x0, s.x1, s.h, w1, w2, dx1, peer, grads[0],
                          grads[1], grads[2], grads[3], ws, slots, slots)
         peer.barrier()                      # every owner's dX rows have landed in my dx
+        ops.device_fault_poll()
         self.step += 1
         self._saved = None
         return peer.dx
 
     # -- helpers ---------------------------------------------------------------------------
+    def _accumulate(self) -> bool:
+        """GPU-resident experts' weight gradients: with ``acc_step > 1`` every backward adds to the
+        gradient tensors and whoever steps the optimizer zeroes them (``acc = acc_step > 1``,
+        MOLE/cpp/define.hpp:657; ``+=`` at MOLE/cpp/core.cpp:295-316); with ``acc_step == 1`` each
+        backward overwrites (core.cpp:274-280)."""
+        return self.acc_step > 1
+
+    def _check_fault(self) -> None:
+        """Raises if a kernel of an earlier step recorded that one of its bounded waits ran out
+        (that step's activations and gradients are not to be trusted).  Reads a host copy that
+        ``_poll_fault`` requested behind the previous backward: no device synchronisation."""
+        code = ops.device_fault_peek()
+        if code:
+            raise RuntimeError(
+                f"a grouped-GEMM kernel gave up on a bounded wait (fault code {code}): the results "
+                "of that step are invalid")
+
     def _desc(self, M, F, n_src, Cs, rec: Record, n_slots, accumulate=False, n_grad_slots=0):
         L = self.s_experts + self.d_experts
         return ops.make_ffn_desc(self.dtype, self.act_name, self.gelu_bwd, M, F, L, n_src, Cs,
@@ -502,6 +564,7 @@ class MOLECore:
     def forward(self, dispatched: torch.Tensor, counts: torch.Tensor, requires_grad: bool):
         """``dispatched`` ``[E_total, Cs, M]`` capacity-strided rows, ``counts`` ``[E_total]``
         valid rows per chunk -> expert outputs in the same layout."""
+        self._check_fault()
         E, Cs, M = dispatched.shape
         W = self.world_size
         L = self.s_experts + self.d_experts
@@ -605,7 +668,7 @@ class MOLECore:
             dx_local = torch.empty_like(dout) if input_requires_grad else None
             ret = dx_local
         dx1 = torch.empty(rows_total, F, dtype=dout.dtype, device=dout.device)
-        accumulate = self.acc_step > 1 and (self.step % self.acc_step) != 0
+        accumulate = self._accumulate()
 
         for g in groups:
             for ri in g:
@@ -643,6 +706,7 @@ class MOLECore:
         if self.d_experts > 0:
             check(lib.mole_ctx_synchronize(sctx.handle, 4))     # D2H gradient stores done
             self._finish_grad_accumulate()
+        ops.device_fault_poll()
         self.step += 1
         self.unset_lazy_zero()
         self._saved = None

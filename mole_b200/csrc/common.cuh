@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -53,11 +54,27 @@ void profile_end(cudaStream_t st);
 int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t* slot,
                             const float* dlogits, const void* wg, int64_t T, int M, int E, int k,
                             int C, int Cs, void* dx, cudaStream_t st);
-int launch_gate_wgrad_mma(const float* dlogits, const void* x, int64_t T, int M, int E, float* dwg,
-                          cudaStream_t st);
+int launch_gate_wgrad_mma(const float* dlogits, const void* x, int64_t T, int M, int E, int chunk,
+                          int n_chunks, float* partial, cudaStream_t st);
 
 // device-side fault word: kernels with bounded waits record where they gave up
-int32_t* device_fault_word();   // lazily allocated once per process (4 bytes), zeroed
+int32_t* device_fault_word();   // of the current device; allocated at its first use (256 bytes), zeroed
+
+// Per-device host state.  cudaFuncSetAttribute, occupancy figures and the SM count belong to a
+// device, not to the process: a process that drives several GPUs needs them once per device.
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
+// One int per device, 0 until set.  Racing setters write the same value, so plain atomics do.
+struct PerDeviceInt {
+  std::atomic<int64_t> v[kMaxDevices];
+  int64_t get(int dev) const { return v[dev].load(std::memory_order_acquire); }
+  void set(int dev, int64_t x) { v[dev].store(x, std::memory_order_release); }
+};
+int sm_count();                 // multiprocessors of the current device
 
 // ---- element types ---------------------------------------------------------------
 template <typename T> struct Elem;

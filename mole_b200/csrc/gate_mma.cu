@@ -189,11 +189,12 @@ int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t
   const size_t ops = (size_t)(2 * kGmTok * (EP + 8) + EP * kGmLdb) * 2;
   const size_t ctile = (size_t)kGmTok * (kGmCols + 4) * 4;
   const size_t smem = ops > ctile ? ops : ctile;
-  static size_t configured = 0;
-  if (smem > configured) {
+  static PerDeviceInt configured;      // per device; the attribute only ever needs to grow
+  const int dev_ = current_device();
+  if ((int64_t)smem > configured.get(dev_)) {
     MOLE_CUDA_OK(cudaFuncSetAttribute(dispatch_bwd_mma_kernel,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+    configured.set(dev_, (int64_t)smem);
   }
   dim3 grid(M / kGmCols, (unsigned)((T + kGmTok - 1) / kGmTok));
   dispatch_bwd_mma_kernel<<<grid, 256, smem, st>>>(
@@ -203,16 +204,16 @@ int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t
   return MOLE_OK;
 }
 
-// ---- dWg += dlogits^T @ x -------------------------------------------------------------------
-// Block: 8 warps, all experts x 128 columns, `chunk` tokens in sub-chunks of 64; partial sums
-// go to the fp32 accumulator with atomics (split over tokens).  The chunk is sized for about two
-// blocks per SM: every block ends with E x 128 atomics, so fewer, longer blocks cost less.  Warp w: columns 64 (w >> 2) ..,
+// ---- partial[chunk] = dlogits[chunk]^T @ x[chunk] ---------------------------------------------
+// Block: 8 warps, all experts x 128 columns, `chunk` tokens in sub-chunks of 64; the block's
+// partial product goes to partial[blockIdx.y] (the caller adds the chunks in a fixed order, so the
+// gradient is bit-reproducible).  The chunk is sized for about two blocks per SM.  Warp w: columns 64 (w >> 2) ..,
 // expert tiles (w & 3) + 4 i.  Both operands sit in shared memory token-major ([k][m], [k][n]),
 // so both fragments come from transposing ldmatrix loads.
 template <int MT>                       // expert tiles of 16 per warp: EP <= 64 * MT
 __global__ void __launch_bounds__(256)
 gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ x,
-                      int64_t Ttok, int M, int E, int EP, int chunk, float* __restrict__ dwg) {
+                      int64_t Ttok, int M, int E, int EP, int chunk, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lda = EP + 8;
   __nv_bfloat16* a_hi = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [64 tok][lda]
@@ -304,40 +305,34 @@ gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __
       for (int j = 0; j < 4; ++j) {
         const int e = (mg + 4 * a) * 16 + g + (j >> 1) * 8;
         const int m = col0 + nh * 64 + i * 8 + 2 * q + (j & 1);
-        if (e < E) atomicAdd(&dwg[(int64_t)e * M + m], acc[a][i][j]);
+        if (e < E) partial[((int64_t)blockIdx.y * E + e) * M + m] = acc[a][i][j];
       }
 }
 
 template <int MT>
 static int launch_wgrad_mma_t(const float* dlogits, const void* x, int64_t T, int M, int E, int EP,
-                              float* dwg, cudaStream_t st) {
+                              int chunk, int n_chunks, float* partial, cudaStream_t st) {
   const size_t smem = (size_t)(2 * kGmTok * (EP + 8) + kGmTok * kGmLdb) * 2;
   auto kern = gate_wgrad_mma_kernel<MT>;
-  static size_t configured = 0;
-  if (smem > configured) {
+  static PerDeviceInt configured;      // per device; the attribute only ever needs to grow
+  const int dev_ = current_device();
+  if ((int64_t)smem > configured.get(dev_)) {
     MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+    configured.set(dev_, (int64_t)smem);
   }
-  int dev = 0, sms = 0;
-  MOLE_CUDA_OK(cudaGetDevice(&dev));
-  MOLE_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int col_blocks = M / kGmCols;
-  const int64_t want = (2 * sms + col_blocks - 1) / col_blocks;          // token chunks wanted
-  int64_t chunk = ((T + want - 1) / want + kGmTok - 1) / kGmTok * kGmTok;
-  if (chunk < 256) chunk = 256;
-  dim3 grid(col_blocks, (unsigned)((T + chunk - 1) / chunk));
-  kern<<<grid, 256, smem, st>>>(dlogits, static_cast<const __nv_bfloat16*>(x), T, M, E, EP,
-                                (int)chunk, dwg);
+  dim3 grid(M / kGmCols, (unsigned)n_chunks);
+  kern<<<grid, 256, smem, st>>>(dlogits, static_cast<const __nv_bfloat16*>(x), T, M, E, EP, chunk,
+                                partial);
   MOLE_LAUNCH_OK();
   return MOLE_OK;
 }
 
-int launch_gate_wgrad_mma(const float* dlogits, const void* x, int64_t T, int M, int E, float* dwg,
-                          cudaStream_t st) {
+int launch_gate_wgrad_mma(const float* dlogits, const void* x, int64_t T, int M, int E, int chunk,
+                          int n_chunks, float* partial, cudaStream_t st) {
   const int EP = (E + 15) / 16 * 16;
-  if (EP <= 64) return launch_wgrad_mma_t<1>(dlogits, x, T, M, E, EP, dwg, st);
-  if (EP <= 128) return launch_wgrad_mma_t<2>(dlogits, x, T, M, E, EP, dwg, st);
-  return launch_wgrad_mma_t<4>(dlogits, x, T, M, E, EP, dwg, st);
+  if (EP <= 64) return launch_wgrad_mma_t<1>(dlogits, x, T, M, E, EP, chunk, n_chunks, partial, st);
+  if (EP <= 128) return launch_wgrad_mma_t<2>(dlogits, x, T, M, E, EP, chunk, n_chunks, partial, st);
+  return launch_wgrad_mma_t<4>(dlogits, x, T, M, E, EP, chunk, n_chunks, partial, st);
 }
 
 }  // namespace mole

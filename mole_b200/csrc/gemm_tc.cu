@@ -64,23 +64,43 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait.  `abort_flag` lives in shared memory: once any wait of this CTA has run out,
-// later waits return at once so the kernel drains quickly.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+// Bounded wait; false when it gave up.  `abort_flag` lives in shared memory: once any wait of
+// this CTA has run out, later waits return false at once.  A role that sees false leaves its
+// work loop: it issues no further TMA load or MMA and stores nothing more, so an output that
+// the accumulator never reached is not written (the fault word tells the host that the step's
+// results are not to be used).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int32_t* fault, int code) {
-  if (mbar_try_wait(bar, parity)) return;
-  if (*abort_flag) return;
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
   const uint64_t t0 = globaltimer_ns();
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 0x3ff) == 0) {
-      if (*abort_flag) return;
+      if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > 2000000000ull) {     // 2 s
         *abort_flag = 1;
         atomicCAS(fault, 0, code);
-        return;
+        return false;
       }
     }
+  }
+  return true;
+}
+// After an abort: what this CTA has already issued (TMA loads into its shared memory, MMAs that
+// read it) gets a bounded time to land before the CTA frees its TMEM and exits.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity, uint64_t deadline_ns) {
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity))
+    if ((++polls & 0xff) == 0 && globaltimer_ns() > deadline_ns) return;
+}
+// Producer side of the drain: stage s of a ring of `stages` has been armed
+// n_s = issued / stages + (s < issued % stages) times; the parity of its last phase is (n_s - 1) & 1.
+__device__ __forceinline__ void drain_loads(uint32_t full0, int stages, uint32_t issued) {
+  const uint64_t deadline = globaltimer_ns() + 200000000ull;      // 0.2 s for all of them
+  for (int s = 0; s < stages; ++s) {
+    const uint32_t n_s = issued / stages + ((uint32_t)s < issued % stages ? 1u : 0u);
+    if (n_s > 0) mbar_drain(full0 + 8 * s, (n_s - 1) & 1u, deadline);
   }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -574,7 +594,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
   __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
@@ -585,10 +605,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
   const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+  const uint32_t drain0 = smem_u32(&bars[2 * STAGES + 4]);      // used only after an abort
   const uint32_t smem_base = smem_u32(smem);
 
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
+    mbar_init(drain0, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
@@ -613,15 +635,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------- TMA producer -------------------------------------
     if (lane == 0) {
       int stage = 0;
-      uint32_t phase = 0;
-      for (int item = blockIdx.x;; item += gridDim.x) {
+      uint32_t phase = 0, issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok; item += gridDim.x) {
         const WorkItem w = decode_item<MODE, BN>(p, item);
         if (!w.valid) break;
         const int slot = p.slot.s[p.e_begin + w.el];
         if (MODE == TC_ROWS) {
           const int nkb = p.K / kBK;
           for (int kb = 0; kb < nkb; ++kb) {
-            mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1);
+            if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1))) break;
             const uint32_t bar = full0 + 8 * stage;
             const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
             mbar_expect_tx(bar, kStageBytes);
@@ -633,17 +656,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               for (int i = 0; i < BN / 64; ++i)
                 tma_load_3d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, kb * kBK, slot);
             }
+            ++issued;
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         } else {
           // K runs over the expert's rows, tile by tile, and stops at each tile's valid rows
           // (64-row blocks here, 16-row MMA steps in the issuer): with ~256 rows per expert the
           // zero rows up to the next multiple of 128 would be a fifth of the work.
-          for (int t = w.t0; t < w.t1; ++t) {
+          for (int t = w.t0; t < w.t1 && ok; ++t) {
             const int trow = p.tile_row0[t];
             const int halves = p.tile_rows[t] > kBK ? 2 : 1;
             for (int hf = 0; hf < halves; ++hf) {
-              mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1);
+              if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1))) break;
               const uint32_t bar = full0 + 8 * stage;
               const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
               const int row = trow + hf * kBK;
@@ -654,27 +678,30 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
               for (int i = 0; i < BN / 64; ++i)
                 tma_load_2d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, row);
+              ++issued;
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           }
         }
       }
+      if (*abort_flag) drain_loads(full0, STAGES, issued);
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------------
     if (lane == 0) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      for (int item = blockIdx.x;; item += gridDim.x) {
+      bool ok = true;
+      for (int item = blockIdx.x; ok; item += gridDim.x) {
         const WorkItem w = decode_item<MODE, BN>(p, item);
         if (!w.valid) break;
         if (MODE == TC_WGRAD && w.t1 == w.t0) continue;      // empty expert: epilogue writes zeros
-        mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 2);
+        if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 2))) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         // one shared-memory stage: `ksteps` MMAs of K = 16
         auto issue_stage = [&](int ksteps, bool first) {
-          mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 3);
+          if (!ok || !(ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 3))) return;
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
 #pragma unroll
@@ -705,8 +732,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           }
         }
+        if (!ok) break;                               // gave up: this accumulator is never published
         tcgen05_commit(tfull0 + 8 * acc);             // accumulator ready for the epilogue
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (*abort_flag) {                              // MMAs already issued retire before the TMEM goes
+        tcgen05_commit(drain0);
+        mbar_drain(drain0, 0, globaltimer_ns() + 200000000ull);
       }
     }
   } else {
@@ -750,7 +782,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t pre[NSTEPS][8];
       epilogue_prefetch<EV, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (BN / 4), pre);
       if (!empty) {
-        mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4);
+        // warp-uniform: the epilogue's tcgen05.ld and shuffles need all 32 lanes
+        if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 4)))
+          break;                                      // nothing is stored for this tile
         tcgen05_fence_after();
       }
       using Ev = EvTraits<EV>;
@@ -897,7 +931,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
   __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
@@ -910,11 +944,13 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const bool leader = rank == 0;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
   const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+  const uint32_t drain0 = smem_u32(&bars[2 * STAGES + 4]);      // used only after an abort
   const uint32_t smem_base = smem_u32(smem);
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
+    mbar_init(drain0, 1);          // the drain commit is multicast like the others: one arrival per CTA
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);               // the even CTA's arrive.expect_tx
       mbar_init(empty0 + 8 * s, 1);              // one multicast commit
@@ -940,8 +976,9 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------- TMA producer (both CTAs) -------------------------
     if (lane == 0) {
       int stage = 0;
-      uint32_t phase = 0;
-      for (int item = cluster_id;; item += n_clusters) {
+      uint32_t phase = 0, issued = 0;
+      bool ok = true;
+      for (int item = cluster_id; ok; item += n_clusters) {
         const PairItem w = decode_pair<MODE>(p, item);
         if (!w.valid) break;
         const int slot = p.slot.s[p.e_begin + w.el];
@@ -953,7 +990,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (MODE == TC_ROWS) {
           const int nkb = p.K / kBK;
           for (int kb = 0; kb < nkb; ++kb) {
-            mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11);
+            if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11))) break;
             const uint32_t bar = (full0 + 8 * stage) & kPeerMask;     // the even CTA's barrier
             const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
             if (leader) mbar_expect_tx(full0 + 8 * stage, tx);
@@ -965,14 +1002,15 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               for (int i = 0; i < 2; ++i)
                 tma2_load_3d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, kb * kBK, slot);
             }
+            ++issued;
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         } else {
-          for (int t = w.t0; t < w.t1; ++t) {            // K stops at each tile's valid rows
+          for (int t = w.t0; t < w.t1 && ok; ++t) {      // K stops at each tile's valid rows
             const int trow = p.tile_row0[t];
             const int halves = p.tile_rows[t] > kBK ? 2 : 1;
             for (int hf = 0; hf < halves; ++hf) {
-              mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11);
+              if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11))) break;
               const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
               const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
               const int row = trow + hf * kBK;
@@ -983,26 +1021,31 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
               for (int i = 0; i < 2; ++i)
                 tma2_load_2d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, row);
+              ++issued;
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           }
         }
       }
+      // both CTAs' loads complete on the even CTA's barriers: it waits for the pair (the odd CTA
+      // stays until the cluster barrier at the end, which the even CTA reaches after this)
+      if (leader && *abort_flag) drain_loads(full0, STAGES, issued);
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (even CTA only) -----------------------
     if (lane == 0 && leader) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      for (int item = cluster_id;; item += n_clusters) {
+      bool ok = true;
+      for (int item = cluster_id; ok; item += n_clusters) {
         const PairItem w = decode_pair<MODE>(p, item);
         if (!w.valid) break;
         if (MODE == TC_WGRAD && w.t1 == w.t0) continue;
-        mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12);
+        if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12))) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN2;
         auto issue_stage = [&](int ksteps, bool first) {
-          mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 13);
+          if (!ok || !(ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 13))) return;
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
 #pragma unroll
@@ -1033,8 +1076,13 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             }
           }
         }
+        if (!ok) break;
         tcgen05_commit2(tfull0 + 8 * acc);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (*abort_flag) {                      // MMAs already issued retire before the TMEM goes
+        tcgen05_commit2(drain0);
+        mbar_drain(drain0, 0, globaltimer_ns() + 200000000ull);
       }
     }
   } else {
@@ -1080,7 +1128,8 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         epilogue_prefetch<EV, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (kBN2 / 4), pre);
       }
       if (!empty) {
-        mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14);
+        if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14)))
+          break;                                      // nothing is stored for this tile
         tcgen05_fence_after();
       }
       if (r0 >= 0)
@@ -1193,17 +1242,6 @@ static int encode_map(CUtensorMap* m, const void* base, int rank, const uint64_t
   return MOLE_OK;
 }
 
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
 bool tc_supported(int M, int F) { return M % 128 == 0 && F % 128 == 0 && M >= 128 && F >= 128; }
 
 template <int MODE, bool B_KMAJOR, int BN, int EV>
@@ -1212,10 +1250,11 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   constexpr int STAGES = BN == 256 ? 4 : 6;
   constexpr size_t smem = (size_t)STAGES * (kABytes + BN * kBK * 2) + 1024;
   auto kern = tc_gemm_kernel<MODE, B_KMAJOR, BN, STAGES, EV>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceInt configured;          // the attribute belongs to a device
+  const int dev = current_device();
+  if (!configured.get(dev)) {
     MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set(dev, 1);
   }
   int grid = sm_count();
   if (max_items < grid) grid = max_items;
@@ -1234,7 +1273,9 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
   constexpr int STAGES = 6;
   constexpr size_t smem = (size_t)STAGES * kStage2Bytes + 1024;
   auto kern = tc2_gemm_kernel<MODE, B_KMAJOR, STAGES, EV>;
-  static int max_clusters = 0;
+  static PerDeviceInt max_clusters_of;     // attribute and occupancy belong to a device
+  const int dev = current_device();
+  int max_clusters = (int)max_clusters_of.get(dev);
   if (max_clusters == 0) {
     MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg = {};
@@ -1252,6 +1293,7 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
       n = sm_count() / 2;
     }
     max_clusters = n;
+    max_clusters_of.set(dev, n);
   }
   int clusters = max_clusters < max_items ? max_clusters : max_items;
   if (clusters <= 0) return MOLE_OK;

@@ -470,23 +470,26 @@ gate_bwd_kernel(const float* __restrict__ scores, const int32_t* __restrict__ id
   }
 }
 
-// dWg[e, m] += sum_t dlogits[t, e] * x[t, m].  Block: 128 tokens x 64 columns, all experts.
+// dWg[e, m] += sum_t dlogits[t, e] * x[t, m], in two stages so that the sum has one fixed order
+// (bit-reproducible from run to run): block (column block, token chunk) writes its partial
+// [E, 64 columns] product into partial[chunk], gate_wgrad_reduce_kernel then adds the chunks to
+// dWg in chunk order.  Block: `chunk` tokens x 64 columns, all experts.
 constexpr int kWgTok = 128, kWgCols = 64, kWgKC = 32;
 template <typename T, int EJ>
 __global__ void __launch_bounds__(256)
 gate_wgrad_kernel(const float* __restrict__ dlogits, const T* __restrict__ x, int64_t Ttok, int M,
-                  int E, float* __restrict__ dwg) {
+                  int E, int chunk, float* __restrict__ partial) {
   __shared__ float dl_s[kWgKC][EJ * 16 + 1];
   __shared__ float x_s[kWgKC][kWgCols + 1];
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;   // ty: expert group, tx: columns
   const int col0 = blockIdx.x * kWgCols;
-  const int64_t tok0 = (int64_t)blockIdx.y * kWgTok;
+  const int64_t tok0 = (int64_t)blockIdx.y * chunk;
   float acc[EJ][4];
 #pragma unroll
   for (int j = 0; j < EJ; ++j)
 #pragma unroll
     for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
-  for (int t0 = 0; t0 < kWgTok; t0 += kWgKC) {
+  for (int t0 = 0; t0 < chunk && tok0 + t0 < Ttok; t0 += kWgKC) {
     for (int i = tid; i < kWgKC * EJ * 16; i += 256) {
       const int tl = i / (EJ * 16), e = i - tl * (EJ * 16);
       const int64_t t = tok0 + t0 + tl;
@@ -517,8 +520,17 @@ gate_wgrad_kernel(const float* __restrict__ dlogits, const T* __restrict__ x, in
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int e = ty + 16 * j, m = col0 + tx + 16 * c;
-      if (e < E && m < M) atomicAdd(&dwg[(int64_t)e * M + m], acc[j][c]);
+      if (e < E && m < M) partial[((int64_t)blockIdx.y * E + e) * M + m] = acc[j][c];
     }
+}
+
+__global__ void gate_wgrad_reduce_kernel(const float* __restrict__ partial, int n_chunks, int64_t n,
+                                         float* __restrict__ dwg) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = dwg[i];
+  for (int c = 0; c < n_chunks; ++c) s += partial[(int64_t)c * n + i];
+  dwg[i] = s;
 }
 
 // ---- host side ---------------------------------------------------------------------
@@ -589,10 +601,11 @@ static int launch_gate_mma(const void* x, const void* wg, const float* bias, int
   const size_t tail = (size_t)kGateTok * (E + 1) * 4 + (size_t)k * E * 4;
   const size_t smem = tiles > tail ? tiles : tail;
   auto kern = gate_topk_mma_kernel<NT>;
-  static size_t configured = 0;             // the attribute only ever needs to grow
-  if (smem > configured) {
+  static PerDeviceInt configured;      // per device; the attribute only ever needs to grow
+  const int dev_ = current_device();
+  if ((int64_t)smem > configured.get(dev_)) {
     MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+    configured.set(dev_, (int64_t)smem);
   }
   kern<<<nb, kGateThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
                                        static_cast<const __nv_bfloat16*>(wg), bias, Ttok, M, E, k,
@@ -622,6 +635,27 @@ static int dispatch_gate(int E, const void* x, const void* wg, const float* bias
   return launch_gate<T, 16>(x, wg, bias, Ttok, M, E, k, normalize, scores, idx, gates, w, st);
 }
 
+// Gate kernel by element type and alignment, then the routing-index build, over the scratch `w`
+// (a caller workspace or the library's built-in array).
+static int gate_route_on(RouteWs w, const void* x, const void* wg, const float* logit_bias, int64_t T,
+                         int M, int E, int k, int C, int normalize_gate, int dtype, float* scores,
+                         int32_t* idx, int32_t* slot, float* gates, int32_t* counts,
+                         int32_t* offsets, int32_t* perm, int32_t* first_hist, float* l_aux,
+                         cudaStream_t st) {
+  int rc;
+  if (dtype == MOLE_F32)
+    rc = dispatch_gate<float>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else if (dtype == MOLE_BF16 && M % kMmaKC == 0 &&
+           ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg)) & 15) == 0)
+    rc = dispatch_gate_mma(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else if (dtype == MOLE_BF16)     // odd M or unaligned rows: CUDA-core gate
+    rc = dispatch_gate<__nv_bfloat16>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
+  else
+    return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
+  if (rc) return rc;
+  return route_tail(w, T, E, k, C, idx, slot, gates, counts, offsets, perm, first_hist, l_aux, st);
+}
+
 }  // namespace mole
 
 using namespace mole;
@@ -648,18 +682,8 @@ extern "C" int mole_gate_route_fwd(const void* x, const void* wg, const float* l
                (long long)workspace_bytes, (long long)route_ws_bytes(T, E, k));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   RouteWs w = carve(workspace, T, E, k);
-  int rc;
-  if (dtype == MOLE_F32)
-    rc = dispatch_gate<float>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
-  else if (dtype == MOLE_BF16 && M % kMmaKC == 0 &&
-           ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg)) & 15) == 0)
-    rc = dispatch_gate_mma(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
-  else if (dtype == MOLE_BF16)     // odd M or unaligned rows: CUDA-core gate
-    rc = dispatch_gate<__nv_bfloat16>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
-  else
-    return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
-  if (rc) return rc;
-  return route_tail(w, T, E, k, C, idx, slot, gates, counts, offsets, perm, first_hist, l_aux, st);
+  return gate_route_on(w, x, wg, logit_bias, T, M, E, k, C, normalize_gate, dtype, scores, idx, slot,
+                       gates, counts, offsets, perm, first_hist, l_aux, st);
 }
 
 // ---- the same gate + routing build for callers that cannot hand over a workspace -------------
@@ -672,7 +696,6 @@ static __device__ __align__(256) unsigned char g_route_scratch[kStaticScratchByt
 // address each device gave the array is looked up once per device (with that device current)
 // and cached.
 static int static_scratch(void** out) {
-  constexpr int kMaxDevices = 64;
   static void* ptrs[kMaxDevices] = {};
   static std::mutex mu;
   int dev = -1;
@@ -710,18 +733,8 @@ extern "C" int mole_gate_route_fwd_static(const void* x, const void* wg, const f
   // every scratch entry the scan reads is written by the gate kernel of this call first, so
   // nothing has to be cleared although the array keeps the previous call's contents
   RouteWs w = carve(scratch, T, E, k);
-  int rc;
-  if (dtype == MOLE_F32)
-    rc = dispatch_gate<float>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
-  else if (dtype == MOLE_BF16 && M % kMmaKC == 0 &&
-           ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg)) & 15) == 0)
-    rc = dispatch_gate_mma(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
-  else if (dtype == MOLE_BF16)
-    rc = dispatch_gate<__nv_bfloat16>(E, x, wg, logit_bias, T, M, k, normalize_gate, scores, idx, gates, w, st);
-  else
-    return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
-  if (rc) return rc;
-  return route_tail(w, T, E, k, C, idx, slot, gates, counts, offsets, perm, first_hist, l_aux, st);
+  return gate_route_on(w, x, wg, logit_bias, T, M, E, k, C, normalize_gate, dtype, scores, idx, slot,
+                       gates, counts, offsets, perm, first_hist, l_aux, st);
 }
 
 extern "C" int mole_route_from_scores(const float* scores, int64_t T, int32_t E, int32_t k,
@@ -758,29 +771,71 @@ extern "C" int mole_gate_bwd(const float* scores, const int32_t* idx, const int3
   return MOLE_OK;
 }
 
+// Token chunks of the gate weight gradient: about two blocks per SM, at least 256 tokens each
+// (multiples of 128), the same split for the CUDA-core and the mma.sync kernel.
+static void wgrad_split(int64_t T, int M, int col_width, int* chunk, int* n_chunks) {
+  const int col_blocks = (M + col_width - 1) / col_width;
+  const int64_t want = (2 * sm_count() + col_blocks - 1) / col_blocks;
+  int64_t c = ((T + want - 1) / want + kWgTok - 1) / kWgTok * kWgTok;
+  if (c < 256) c = 256;
+  *chunk = (int)c;
+  *n_chunks = (int)((T + c - 1) / c);
+}
+static bool wgrad_uses_mma(const void* x, int M, int dtype) {
+  return dtype == MOLE_BF16 && M % 128 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+}
+
 template <typename T>
-static int launch_wgrad(const float* dlogits, const void* x, int64_t Ttok, int M, int E, float* dwg,
-                        cudaStream_t st) {
-  dim3 grid((M + kWgCols - 1) / kWgCols, (unsigned)((Ttok + kWgTok - 1) / kWgTok));
+static int launch_wgrad(const float* dlogits, const void* x, int64_t Ttok, int M, int E, int chunk,
+                        int n_chunks, float* partial, cudaStream_t st) {
+  dim3 grid((M + kWgCols - 1) / kWgCols, (unsigned)n_chunks);
   const int ej = (E + 15) / 16;
   const T* xp = static_cast<const T*>(x);
-  if (ej <= 1) gate_wgrad_kernel<T, 1><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
-  else if (ej <= 2) gate_wgrad_kernel<T, 2><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
-  else if (ej <= 4) gate_wgrad_kernel<T, 4><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
-  else if (ej <= 8) gate_wgrad_kernel<T, 8><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
-  else gate_wgrad_kernel<T, 16><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, dwg);
+  if (ej <= 1) gate_wgrad_kernel<T, 1><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, chunk, partial);
+  else if (ej <= 2) gate_wgrad_kernel<T, 2><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, chunk, partial);
+  else if (ej <= 4) gate_wgrad_kernel<T, 4><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, chunk, partial);
+  else if (ej <= 8) gate_wgrad_kernel<T, 8><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, chunk, partial);
+  else gate_wgrad_kernel<T, 16><<<grid, 256, 0, st>>>(dlogits, xp, Ttok, M, E, chunk, partial);
   MOLE_LAUNCH_OK();
   return MOLE_OK;
 }
 
-extern "C" int mole_gate_wgrad(const float* dlogits, const void* x, int64_t T, int32_t M,
-                               int32_t E, int32_t dtype, float* dwg32, void* stream) {
+extern "C" int mole_gate_wgrad_workspace_bytes(int64_t T, int32_t M, int32_t E, int32_t dtype,
+                                               int64_t* bytes) {
+  MOLE_REQUIRE(bytes != nullptr, "bytes is null");
   if (int rc = check_route_args(T, E, 1, 1)) return rc;
-  MOLE_REQUIRE(dlogits && x && dwg32, "null pointer argument");
+  MOLE_REQUIRE(M >= 1, "M=%d", M);
+  int chunk, n_chunks;
+  // the larger of the two kernels' splits, so that the size does not depend on the alignment of x
+  wgrad_split(T, M, kWgCols, &chunk, &n_chunks);
+  int64_t n = n_chunks;
+  if (dtype == MOLE_BF16 && M % 128 == 0) {
+    wgrad_split(T, M, 128, &chunk, &n_chunks);
+    if (n_chunks > n) n = n_chunks;
+  }
+  *bytes = n * (int64_t)E * M * 4;
+  return MOLE_OK;
+}
+
+extern "C" int mole_gate_wgrad(const float* dlogits, const void* x, int64_t T, int32_t M,
+                               int32_t E, int32_t dtype, float* dwg32, void* workspace,
+                               int64_t workspace_bytes, void* stream) {
+  if (int rc = check_route_args(T, E, 1, 1)) return rc;
+  MOLE_REQUIRE(dlogits && x && dwg32 && workspace, "null pointer argument");
+  MOLE_REQUIRE(dtype == MOLE_F32 || dtype == MOLE_BF16, "dtype %d", dtype);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == MOLE_BF16 && M % 128 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
-    return launch_gate_wgrad_mma(dlogits, x, T, M, E, dwg32, st);
-  if (dtype == MOLE_F32) return launch_wgrad<float>(dlogits, x, T, M, E, dwg32, st);
-  if (dtype == MOLE_BF16) return launch_wgrad<__nv_bfloat16>(dlogits, x, T, M, E, dwg32, st);
-  return fail(MOLE_ERR_UNSUPPORTED, "dtype %d", dtype);
+  const bool mma = wgrad_uses_mma(x, M, dtype);
+  int chunk, n_chunks;
+  wgrad_split(T, M, mma ? 128 : kWgCols, &chunk, &n_chunks);
+  MOLE_REQUIRE(workspace_bytes >= (int64_t)n_chunks * E * M * 4, "workspace too small");
+  float* partial = static_cast<float*>(workspace);
+  int rc;
+  if (mma) rc = launch_gate_wgrad_mma(dlogits, x, T, M, E, chunk, n_chunks, partial, st);
+  else if (dtype == MOLE_F32) rc = launch_wgrad<float>(dlogits, x, T, M, E, chunk, n_chunks, partial, st);
+  else rc = launch_wgrad<__nv_bfloat16>(dlogits, x, T, M, E, chunk, n_chunks, partial, st);
+  if (rc) return rc;
+  const int64_t n = (int64_t)E * M;
+  gate_wgrad_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partial, n_chunks, n, dwg32);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
 }

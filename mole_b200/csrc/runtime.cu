@@ -22,14 +22,44 @@ char* last_error_buffer() {
   return buf;
 }
 
+// One fault word per device (256 bytes of device memory, allocated at the device's first use).
+struct FaultSlot {
+  int32_t* word = nullptr;        // device
+  int32_t* host = nullptr;        // pinned: where mole_device_fault_poll copies the word
+  cudaEvent_t polled = nullptr;   // recorded behind the last poll's copy
+  bool poll_pending = false;
+};
+static FaultSlot g_fault[kMaxDevices];
+static std::mutex g_fault_mu;
+static FaultSlot* fault_slot() {
+  const int dev = current_device();
+  std::lock_guard<std::mutex> lock(g_fault_mu);
+  FaultSlot& f = g_fault[dev];
+  if (!f.word) {
+    if (cudaMalloc(&f.word, 256) != cudaSuccess) { f.word = nullptr; return nullptr; }
+    cudaMemset(f.word, 0, 256);
+    if (cudaMallocHost(&f.host, 64) != cudaSuccess) f.host = nullptr;
+    else *f.host = 0;
+    if (cudaEventCreateWithFlags(&f.polled, cudaEventDisableTiming) != cudaSuccess) f.polled = nullptr;
+  }
+  return &f;
+}
 int32_t* device_fault_word() {
-  static int32_t* word = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    if (cudaMalloc(&word, 256) == cudaSuccess) cudaMemset(word, 0, 256);
-    else word = nullptr;
-  });
-  return word;
+  FaultSlot* f = fault_slot();
+  return f ? f->word : nullptr;
+}
+
+int sm_count() {
+  static PerDeviceInt n;
+  const int dev = current_device();
+  int64_t v = n.get(dev);
+  if (v == 0) {
+    int a = 0;
+    cudaDeviceGetAttribute(&a, cudaDevAttrMultiProcessorCount, dev);
+    v = a > 0 ? a : 148;
+    n.set(dev, v);
+  }
+  return (int)v;
 }
 
 static std::atomic<int64_t> g_launches{0};
@@ -92,6 +122,34 @@ extern "C" int mole_device_fault(void* stream, int32_t* fault) {
   MOLE_CUDA_OK(cudaMemcpyAsync(fault, w, 4, cudaMemcpyDeviceToHost, st));
   MOLE_CUDA_OK(cudaStreamSynchronize(st));
   if (*fault != 0) MOLE_CUDA_OK(cudaMemsetAsync(w, 0, 4, st));
+  return MOLE_OK;
+}
+// The same check without a host wait: poll enqueues a copy of the word into pinned host memory
+// behind the work already on `stream`; peek returns the last copy that has landed.
+extern "C" int mole_device_fault_poll(void* stream) {
+  FaultSlot* f = fault_slot();
+  if (!f || !f->host || !f->polled) return fail(MOLE_ERR_CUDA, "fault word not allocated");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (f->poll_pending && cudaEventQuery(f->polled) != cudaSuccess) {
+    cudaGetLastError();           // the previous poll's copy is still in flight: keep that one
+    return MOLE_OK;
+  }
+  MOLE_CUDA_OK(cudaMemcpyAsync(f->host + 1, f->word, 4, cudaMemcpyDeviceToHost, st));
+  MOLE_CUDA_OK(cudaEventRecord(f->polled, st));
+  f->poll_pending = true;
+  return MOLE_OK;
+}
+extern "C" int mole_device_fault_peek(int32_t* fault) {
+  MOLE_REQUIRE(fault != nullptr, "fault is null");
+  FaultSlot* f = fault_slot();
+  if (!f || !f->host || !f->polled) return fail(MOLE_ERR_CUDA, "fault word not allocated");
+  if (f->poll_pending && cudaEventQuery(f->polled) == cudaSuccess) {
+    f->host[0] = f->host[1];
+    f->poll_pending = false;
+  } else {
+    cudaGetLastError();
+  }
+  *fault = f->host[0];
   return MOLE_OK;
 }
 

@@ -72,6 +72,9 @@ class Dispatch(torch.autograd.Function):
     def backward(ctx, ddisp):
         M, dtype, device = ctx.meta
         h = ctx.holder
+        if h is not None and h.get("tap") is not None:
+            peer = h.get("peer")
+            h["tap"]["dx_rows"] = peer.dx if peer is not None else ddisp
         if h is not None and h.get("gate_needs_x_grad") and not h.get("gate_backward_done"):
             # the gate's backward is still to come and will emit the fused gradient of x
             h["pending_ddisp"] = ddisp.contiguous()

@@ -124,6 +124,10 @@ class MOLEModule(torch.nn.Module):
         self.l_aux = None
         self._route_counts = None
         self.last_plan = None
+        # A dict here makes every step leave references to the expert pipeline's output rows
+        # ("rows", [E, Cs, M], what combine reads) and to the gradient rows that come back from it
+        # ("dx_rows"), so that a checker can compare them with a reference after the step.
+        self.parity_tap = None
 
         self.moe_id = len(MOLEModule._instance)
         MOLEModule._instance.append(self)
@@ -247,6 +251,7 @@ class MOLEModule(torch.nn.Module):
         # (dispatch -> owners, FC2 -> sources, and the mirror in backward) instead of all-to-alls
         peer = self.MOLECore.peer_for(plan.Cs, self.embed_dim, self.dtype, resized_input.device)
         holder["peer"] = peer
+        holder["tap"] = self.parity_tap
         dispatched_input = Dispatch.apply(resized_input, plan, holder)
 
         self._route_counts = plan.counts
@@ -254,6 +259,8 @@ class MOLEModule(torch.nn.Module):
         experts_output = BatchFusedFWD.apply(dispatched_input, self, self.dummy_param, time_it, prefetch)
         self._route_counts = None
         self._peer_exchange = None
+        if self.parity_tap is not None:
+            self.parity_tap["rows"] = experts_output
 
         expert_output = Combine.apply(experts_output, gates, plan, peer)
         out = expert_output.reshape(original_shape).to(original_dtype)

@@ -152,7 +152,11 @@ def gate_wgrad(dlogits: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     T, M = x.shape
     E = dlogits.shape[1]
     dwg = torch.zeros(E, M, dtype=torch.float32, device=x.device)
-    check(lib.mole_gate_wgrad(_ptr(dlogits), _ptr(x), T, M, E, _dt(x), _ptr(dwg), _stream()))
+    n = C.c_int64()
+    check(lib.mole_gate_wgrad_workspace_bytes(T, M, E, _dt(x), C.byref(n)))
+    ws = torch.empty(n.value, dtype=torch.uint8, device=x.device)
+    check(lib.mole_gate_wgrad(_ptr(dlogits), _ptr(x), T, M, E, _dt(x), _ptr(dwg), _ptr(ws),
+                              ws.numel(), _stream()))
     return dwg
 
 
@@ -270,6 +274,18 @@ def ffn_bwd_peer(desc: FfnDesc, counts, dout, x, x1, h, w1, w2, dx1, peer, gw1, 
                                 _ptr(x1), _ptr(h), _ptr(w1), _ptr(w2), _ptr(dx1), peer.table["dx"],
                                 peer.rank, _ptr(gw1), _ptr(gb1), _ptr(gw2), _ptr(gb2), _ptr(ws),
                                 ws.numel(), _stream()))
+
+
+def device_fault_poll() -> None:
+    """Enqueues a copy of the fault word behind the current stream's work (no host wait)."""
+    check(lib.mole_device_fault_poll(_stream()))
+
+
+def device_fault_peek() -> int:
+    """Value of the last polled copy that has landed (0 before the first)."""
+    f = C.c_int32()
+    check(lib.mole_device_fault_peek(C.byref(f)))
+    return f.value
 
 
 def device_fault() -> int:

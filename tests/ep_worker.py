@@ -36,22 +36,25 @@ def main():
     mine = per_rank[rank]
     # "records": two records per rank, NCCL all-to-all per record.  "push": one record, rows
     # stored straight into the consuming rank's memory (dispatch / FC2 / combine bwd / dX).
+    # "push_pair": the same with the CTA-pair kernel forced, so that its row map / peer scatter runs
+    # on several ranks (by default this small shape picks the one-CTA kernel).
     mode = sys.argv[1] if len(sys.argv) > 1 else "records"
-    ebatch = L if mode == "push" else max(1, L // 2)
+    push = mode.startswith("push")
+    ebatch = L if push else max(1, L // 2)
     m = MOLEModule(0, E, M, F, -1, k, ebatch, {"local_rank": local, "world_size": world, "rank": rank},
-                   "gelu", 1, False, False, dtype=dtype)
+                   "gelu", 1, False, False, dtype=dtype, ffn_backend=3 if mode == "push_pair" else 0)
     sl = slice(rank * L, (rank + 1) * L)
     m.set_layer_state({"gate": [mine["wg"], None],
                        "experts": [[mine["w1"][e], mine["b1"][e], mine["w2"][e], mine["b2"][e]]
                                    for e in range(rank * L, (rank + 1) * L)]}, grad=False)
     x = mine["x"].to(dtype).cuda().requires_grad_(True)
-    for _ in range(2 if mode == "push" else 1):      # twice: the push buffers are reused per step
+    for _ in range(2 if push else 1):      # twice: the push buffers are reused per step
         x.grad = None
         m.gate[0].linear.weight.grad = None
         y = m(x, capacity_factor=cf)
         (y.float() * mine["gy"].cuda()).sum().backward()
     torch.cuda.synchronize()
-    if mode == "push":
+    if push:
         assert m.MOLECore._peer is not None, "the push-style exchange was not taken"
     else:
         assert m.MOLECore._peer is None
@@ -78,6 +81,7 @@ def main():
         # rounded to bf16 before this sum, hence the wider tolerance
         want = sum(r[name][sl] for r in refs)
         assert_close(g, want, dtype, f"rank {rank} {name}", scale=2.0)
+    m.MOLECore.close_peer_exchange()
     dist.barrier()
     if rank == 0:
         print("EP_OK", world, mode)

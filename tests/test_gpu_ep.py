@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("mode", ["records", "push"])
+@pytest.mark.parametrize("mode", ["records", "push", "push_pair"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_expert_parallel_layer_matches_oracle(world, mode):
     if torch.cuda.device_count() < world:

@@ -11,9 +11,11 @@ pytestmark = pytest.mark.gpu
 
 
 class Case:
-    def __init__(self, M, F, L, n_src, Cs, counts, dtype, seed=0, bias=True, act="gelu"):
+    def __init__(self, M, F, L, n_src, Cs, counts, dtype, seed=0, bias=True, act="gelu",
+                 gelu_bwd="exact"):
         g = torch.Generator().manual_seed(seed)
         self.M, self.F, self.L, self.n_src, self.Cs, self.dtype, self.act = M, F, L, n_src, Cs, dtype, act
+        self.gelu_bwd = gelu_bwd
         self.counts = torch.tensor(counts, dtype=torch.int32).view(n_src, L)
         self.w1 = (torch.randn(L, F, M, generator=g) * 0.05).to(dtype)
         self.w2 = (torch.randn(L, F, M, generator=g) * 0.05).to(dtype)
@@ -41,7 +43,7 @@ class Case:
         x = self.expert_rows(self.x, l).float()
         dout = self.expert_rows(self.dout, l).float()
         r = O.ffn_explicit(x, self.w1[l].float(), self.b1[l].float(), self.w2[l].float(),
-                           self.b2[l].float(), dout, self.dtype, act=self.act)
+                           self.b2[l].float(), dout, self.dtype, act=self.act, gelu_bwd=self.gelu_bwd)
         return r["out"], r["dx"], [r["gw1"], r["gb1"], r["gw2"], r["gb2"]]
 
 
@@ -52,7 +54,7 @@ def run_gpu(case, e_begin=0, e_end=None, backend=0, accumulate=False, slots=None
     e_end = c.L if e_end is None else e_end
     dev = torch.device("cuda")
     n_slots = c.L if slots is None else max(slots) + 1
-    desc = ops.make_ffn_desc(c.dtype, c.act, "exact", c.M, c.F, c.L, c.n_src, c.Cs, e_begin, e_end,
+    desc = ops.make_ffn_desc(c.dtype, c.act, c.gelu_bwd, c.M, c.F, c.L, c.n_src, c.Cs, e_begin, e_end,
                              n_slots, accumulate, backend, compact=compact)
     ws = ops.ffn_workspace(desc, dev)
     rows = c.n_src * c.L * c.Cs
@@ -208,3 +210,49 @@ def test_ffn_bf16_full_size_spot_check():
         for got, ref in zip(grads, g_ref):
             assert_close(got[l], ref, case.dtype, f"grad {l}")
     assert (grads[0][3] == 0).all() and (grads[2][3] == 0).all()
+
+
+@pytest.mark.parametrize("backend,dtype", [(2, torch.bfloat16), (3, torch.bfloat16), (1, torch.bfloat16),
+                                           (0, torch.float32)],
+                         ids=["tcgen05_one_cta", "tcgen05_cta_pair", "cuda_cores_bf16", "cuda_cores_fp32"])
+def test_ffn_tanh_gelu_derivative(backend, dtype):
+    """The reference's shipped backward: ``USE_MOLE_GELU`` is defined (MOLE/cpp/define.hpp:6), so
+    dX1 is multiplied by the tanh-approximation derivative of MOLE/cpp/gelu.cu:3-14 while the
+    forward stays the exact GELU.  Checked on every back end against the oracle run with the same
+    flag; the pre-activations are spread widely enough that the two derivatives differ by far more
+    than the tolerance, so a kernel that ignored the flag would fail."""
+    case = Case(M=256, F=512, L=8, n_src=1, Cs=256, counts=RAGGED, dtype=dtype, seed=11,
+                gelu_bwd="tanh")
+    out, dx, grads = run_gpu(case, backend=backend)
+    check(case, out, dx, grads, range(8), wscale=4.0 if dtype == torch.float32 else 1.0)
+    exact = Case(M=256, F=512, L=8, n_src=1, Cs=256, counts=RAGGED, dtype=dtype, seed=11)
+    _, dx_exact, _ = run_gpu(exact, backend=backend)
+    l = 6                                        # 256 rows
+    a, b = case.expert_rows(dx, l).float(), case.expert_rows(dx_exact, l).float()
+    assert (a - b).abs().max() > 0, "tanh and exact derivative produced identical dx"
+
+
+def test_ffn_bf16_config3_shape_spot_check():
+    """The headline benchmark's shape on one GPU: M = 2048, F = 8192, 256 +- 16 rows per expert
+    (capacity 320, stride 384), eight experts: tcgen05 path (one-CTA kernel, what the benchmark
+    runs at this shape, and CTA pairs) against the oracle on experts with a ragged third tile,
+    exactly two tiles, and the fullest one."""
+    g = torch.Generator().manual_seed(9)
+    L, M, F, Cs = 8, 2048, 8192, 384
+    counts = torch.randint(240, 273, (L,), generator=g).tolist()
+    counts[1], counts[4], counts[6] = 256, 320, 257
+    case = Case(M, F, L, 1, Cs, counts, torch.bfloat16, seed=10)
+    out, dx, grads = run_gpu(case)                       # backend 0: picks the one-CTA kernel here
+    out3, dx3, grads3 = run_gpu(case, backend=3)
+    valid = torch.zeros(1, L, Cs, dtype=torch.bool)
+    for l in range(L):
+        valid[0, l, :counts[l]] = True
+    assert torch.equal(out[valid], out3[valid]) and torch.equal(dx[valid], dx3[valid])
+    for a, b in zip(grads, grads3):
+        assert torch.equal(a, b)
+    for l in (1, 4, 6):
+        o_ref, dx_ref, g_ref = case.oracle(l)
+        assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
+        assert_close(case.expert_rows(dx, l), dx_ref, case.dtype, f"dx {l}")
+        for got, ref in zip(grads, g_ref):
+            assert_close(got[l], ref, case.dtype, f"grad {l}")

@@ -134,3 +134,31 @@ def test_offloaded_experts_match_resident():
     assert torch.equal(res.FC1_B_GPU.grad_tensors.cpu(), off.FC1_B_CPU.all_tensors.grad_)
     assert torch.equal(res.FC2_B_GPU.grad_tensors.cpu(), off.FC2_B_CPU.all_tensors.grad_)
     mcore.UniMem._instance = None
+
+
+def test_layer_bf16_gradient_accumulation_two_micro_batches():
+    """``acc_step = 2``: every backward adds to the GPU-resident experts' gradient tensors
+    (``acc = acc_step > 1``, MOLE/cpp/define.hpp:657; ``+=`` at MOLE/cpp/core.cpp:295-316) and
+    zeroing is the optimizer's job.  Two micro-batches must leave the sum of their gradients, and
+    after zeroing a third backward leaves just its own."""
+    from mole_b200 import MOLEModule
+    T, M, E, F, k = 1024, 256, 8, 512, 2
+    a = O.make_inputs(T, M, E, F, seed=41)
+    b = O.make_inputs(T, M, E, F, seed=41, token_seed=5)
+    m = MOLEModule(0, E, M, F, -1, k, E, DIST1, "gelu", 2, False, False, dtype=torch.bfloat16)
+    m.set_layer_state({"gate": [a["wg"], None],
+                       "experts": [[a["w1"][e], a["b1"][e], a["w2"][e], a["b2"][e]] for e in range(E)]},
+                      grad=False)
+    refs = []
+    for inp in (a, b):
+        x, y = run_module(m, inp, 1.25, torch.bfloat16)
+        refs.append(run_oracle(inp, k, 1.25, torch.bfloat16, scores=m.last_plan.scores.cpu()))
+    for name, got in (("gw1", m.FC1_W_GPU.grad_tensors), ("gb1", m.FC1_B_GPU.grad_tensors),
+                      ("gw2", m.FC2_W_GPU.grad_tensors), ("gb2", m.FC2_B_GPU.grad_tensors)):
+        # the second backward adds to a bf16-rounded first gradient: one more rounding than the sum
+        assert_close(got, refs[0][name] + refs[1][name], torch.bfloat16, name, scale=2.0)
+    for p in (m.FC1_W_GPU, m.FC1_B_GPU, m.FC2_W_GPU, m.FC2_B_GPU):
+        p.grad_tensors.zero_()
+    x, y = run_module(m, a, 1.25, torch.bfloat16)
+    assert_close(m.FC1_W_GPU.grad_tensors, refs[0]["gw1"], torch.bfloat16, "gw1 after zeroing")
+    assert_close(m.FC2_W_GPU.grad_tensors, refs[0]["gw2"], torch.bfloat16, "gw2 after zeroing")

@@ -124,3 +124,19 @@ def test_gate_backward_matches_autograd():
         dx = ops.dispatch_bwd(None, plan, M, torch.float32, torch.device("cuda"), dlogits, wg.cuda())
         torch.testing.assert_close(dwg.cpu(), wr.grad, rtol=1e-4, atol=1e-5)
         torch.testing.assert_close(dx.cpu(), xr.grad, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gate_weight_gradient_is_bit_reproducible(dtype):
+    """dWg = dlogits^T x is summed over tokens in two stages with a fixed order (no atomics):
+    repeated calls return identical bits, and the value matches a float64 product."""
+    from mole_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    T, M, E = 4096 + 77, 256, 24
+    x = torch.randn(T, M, generator=g).to(dtype).cuda()
+    dl = (torch.randn(T, E, generator=g) * 1e-2).cuda()
+    first = ops.gate_wgrad(dl, x)
+    for _ in range(3):
+        assert torch.equal(ops.gate_wgrad(dl, x), first)
+    ref = (dl.double().t() @ x.double()).float()
+    torch.testing.assert_close(first, ref, rtol=2e-4, atol=2e-4)
