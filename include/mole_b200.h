@@ -273,6 +273,11 @@ int mole_ctx_destroy(mole_ctx* ctx);
 int mole_ctx_stream(mole_ctx* ctx, int32_t idx, void** stream);
 /* make stream `waiter` wait for everything enqueued so far on stream `waited` */
 int mole_ctx_wait(mole_ctx* ctx, void* waiter, void* waited);
+/* per-record edges (comp_event / comm_event / para_event of MOLE/cpp/define.hpp:634-636):
+ * record returns a ticket for the work enqueued on `stream` so far; wait orders `stream` behind
+ * that work only.  The last 1024 tickets stay valid. */
+int mole_ctx_event_record(mole_ctx* ctx, void* stream, int64_t* ticket);
+int mole_ctx_event_wait(mole_ctx* ctx, int64_t ticket, void* stream);
 int mole_ctx_synchronize(mole_ctx* ctx, int32_t idx);
 
 /* ------------------------------------------------------------------------------------
@@ -352,6 +357,26 @@ int mole_pool_abs_slot(mole_pool* pool, int32_t view_slot, int32_t* abs_slot);
  * current work */
 int mole_store_to_host(mole_ctx* ctx, void* host_dst, const void* dev_src, int64_t bytes,
                        void* after_stream);
+
+/* ------------------------------------------------------------------------------------
+ * optimizer step of offloaded experts on the GPU ("instant Adam") and the cross-layer prefetch
+ * assignment.  Replace _MOLECore::adam / instant_adam (MOLE/cpp/define.hpp:543-579,
+ * MOLE/cpp/core.cpp:848-943) and _fast_assign_prefetch (MOLE/cpp/core.cpp:1302-1345).
+ * ---------------------------------------------------------------------------------- */
+/* One fused pass over n elements, in place: p, m, v updated from g (+ g_extra when not NULL: a
+ * gradient accumulated over earlier micro-steps).  t is the step count AFTER this step (the
+ * reference's this->t + 1).  adamw != 0: decoupled weight decay p *= 1 - lam*lr; else g += lam*p.
+ * All five arrays have element type `dtype`; the arithmetic is fp32. */
+int mole_adam_update(void* p, void* m, void* v, const void* g, const void* g_extra, int64_t n,
+                     int32_t dtype, float beta1, float beta2, int32_t t, float lr, float lam,
+                     float eps, int32_t adamw, void* stream);
+/* P free pool slots, n layers, layer i can hide F[i] expert fetches and owns E[i] offloaded
+ * experts.  local[i] = experts layer i prefetches for itself; triples[3j..3j+2] = (lender layer,
+ * borrower layer, count): while the lender runs it also fetches `count` experts of the borrower.
+ * Host-only (no device work).  *n_triples is the number found even when it exceeds capacity. */
+int mole_fast_assign_prefetch(int32_t P, const int32_t* F, const int32_t* E, int32_t n,
+                              int32_t* local, int32_t* triples, int32_t capacity,
+                              int32_t* n_triples);
 
 #ifdef __cplusplus
 }

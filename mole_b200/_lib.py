@@ -72,6 +72,8 @@ SIGNATURES = {
     "mole_ctx_destroy": (C.c_int, [_p]),
     "mole_ctx_stream": (C.c_int, [_p, _i32, C.POINTER(_p)]),
     "mole_ctx_wait": (C.c_int, [_p, _p, _p]),
+    "mole_ctx_event_record": (C.c_int, [_p, _p, _pi64]),
+    "mole_ctx_event_wait": (C.c_int, [_p, _i64, _p]),
     "mole_ctx_synchronize": (C.c_int, [_p, _i32]),
     "mole_comm_unique_id": (C.c_int, [C.POINTER(C.c_uint8)]),
     "mole_comm_create": (C.c_int, [C.POINTER(C.c_uint8), _i32, _i32, _i32, C.POINTER(_p)]),
@@ -104,6 +106,9 @@ SIGNATURES = {
     "mole_pool_log": (C.c_int, [_p, _pi32, _i32, _pi32]),
     "mole_pool_abs_slot": (C.c_int, [_p, _i32, _pi32]),
     "mole_store_to_host": (C.c_int, [_p, _p, _p, _i64, _p]),
+    "mole_adam_update": (C.c_int, [_p, _p, _p, _p, _p, _i64, _i32, C.c_float, C.c_float, _i32,
+                                   C.c_float, C.c_float, C.c_float, _i32, _p]),
+    "mole_fast_assign_prefetch": (C.c_int, [_i32, _pi32, _pi32, _i32, _pi32, _pi32, _i32, _pi32]),
 }
 
 

@@ -18,7 +18,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT_DIR = HERE / "lib"
 LIB = OUT_DIR / "libmole_b200.so"
-SOURCES = ["route.cu", "dispatch.cu", "gate_mma.cu", "gemm_simt.cu", "gemm_tc.cu", "ffn.cu", "runtime.cu"]
+SOURCES = ["route.cu", "dispatch.cu", "gate_mma.cu", "gemm_simt.cu", "gemm_tc.cu", "ffn.cu", "runtime.cu", "adam.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

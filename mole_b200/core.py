@@ -115,6 +115,37 @@ def _get_UniMem() -> UniMem:
     return UniMem._instance
 
 
+def clear_virtual_mem() -> None:
+    """Drops every prefetch reservation of the pool (``clear_virtual_mem`` of the reference's
+    ``core`` module; the scheduler calls it at the start of a step)."""
+    if UniMem._instance is not None and UniMem._instance.handle is not None:
+        UniMem._instance.clear_virtual_mem()
+
+
+def fast_assign_prefetch(P: int, F, E):
+    """``(GPscheme, LPscheme)`` as the reference's binding returns them
+    (MOLE/cpp/core.cpp:1302-1345): ``LPscheme[i]`` experts layer ``i`` prefetches for itself,
+    ``GPscheme[i]`` a list of ``[layer j, count]``: while layer ``i`` runs it also fetches ``count``
+    experts of the later layer ``j`` into spare pool slots."""
+    n = len(E)
+    assert len(F) == n
+    Fa = (C.c_int32 * max(n, 1))(*F)
+    Ea = (C.c_int32 * max(n, 1))(*E)
+    local = (C.c_int32 * max(n, 1))()
+    cap = 4 * max(n, 1) + 8
+    while True:
+        triples = (C.c_int32 * (3 * cap))()
+        nt = C.c_int32()
+        check(lib.mole_fast_assign_prefetch(P, Fa, Ea, n, local, triples, cap, C.byref(nt)))
+        if nt.value <= cap:
+            break
+        cap = nt.value
+    gp = [[] for _ in range(n)]
+    for j in range(nt.value):
+        gp[triples[3 * j]].append([triples[3 * j + 1], triples[3 * j + 2]])
+    return gp, [local[i] for i in range(n)]
+
+
 # --------------------------------------------------------------------------- #
 # records
 # --------------------------------------------------------------------------- #
@@ -326,6 +357,35 @@ class _Saved:
     __slots__ = ("x0", "x1", "h", "counts", "Cs", "n_src", "serial")
 
 
+class _Staging:
+    """One record's worth of device memory for an offloaded batch's backward: the four weight
+    gradients and, when the optimizer step runs on the GPU, the Adam moments (and the host's
+    accumulated gradient).  ``busy`` is recorded on the device-to-host stream behind the last
+    copy that reads the block; the next writer waits for it."""
+
+    def __init__(self, n, M, F, dtype, device):
+        kw = dict(dtype=dtype, device=device)
+        self.shapes = [(n, F, M), (n, F), (n, F, M), (n, M)]
+        self.kw = kw
+        self.grads = [torch.empty(*sh, **kw) for sh in self.shapes]
+        self.m = self.v = self.g_host = None
+        self.busy = None
+
+    def ensure_moments(self, extra_grad: bool) -> None:
+        if self.m is None:
+            self.m = [torch.empty(*sh, **self.kw) for sh in self.shapes]
+            self.v = [torch.empty(*sh, **self.kw) for sh in self.shapes]
+        if extra_grad and self.g_host is None:
+            self.g_host = [torch.empty(*sh, **self.kw) for sh in self.shapes]
+
+    def acquire(self, stream) -> None:
+        if self.busy is not None:
+            ExpertStreamCtx.wait_ticket(stream, self.busy)
+
+    def release(self, back_stream) -> None:
+        self.busy = ExpertStreamCtx.record(back_stream)
+
+
 class MOLECore:
     def __init__(self, use_pool, grad_use_pool, mome_use_pool, vari_use_pool, s_experts, d_experts,
                  ebatch_size, world_size, act, adv_adam, acc_step, step, device, moe_id,
@@ -351,14 +411,20 @@ class MOLECore:
         self.gpu_grads = [None] * 4
         self.cpu_params = [None] * 4
         self.cpu_grads = [None] * 4
+        self.cpu_mome = [None] * 4
+        self.cpu_vari = [None] * 4
         self._saved: Optional[_Saved] = None
         self._records: List[Record] = []
-        self._grad_staging = None
+        self._staging: List["_Staging"] = []
+        self._staging_turn = 0
+        self._pending_acc = []
         self._peer: Optional[PeerExchange] = None
         self._peer_failed = False
-        if adv_adam:
-            raise NotImplementedError(
-                "adv_adam (optimizer step fused after backward) is outside the MoE-layer hot path")
+        # Adam hyper-parameters of the step fused behind backward (``set_adam``); ``t`` counts the
+        # optimizer steps already taken.  ``hybrid_adam_count`` experts (from the front of the
+        # offloaded ones) are updated on the GPU, the rest by the host optimizer.
+        self.adam = dict(beta1=0.9, beta2=0.999, t=0, lr=1e-3, lam=0.0, eps=1e-8, adamW=False)
+        self.hybrid_adam_count = d_experts
 
     # -- parameter cores (MOLE/cpp/uparameter.cpp:13-56) -----------------------------------
     def set_GPUParamCore(self, p_id, all_tensors, grad_tensors, bias):
@@ -366,6 +432,19 @@ class MOLECore:
 
     def set_CPUParamCore(self, p_id, t, grad, mome, vari, bias, p_id2=None):
         self.cpu_params[p_id], self.cpu_grads[p_id] = t, grad
+        self.cpu_mome[p_id], self.cpu_vari[p_id] = mome, vari
+
+    def set_adam(self, beta1, beta2, t, lr, lam, eps, adamW, hybrid_adam_count):
+        """Hyper-parameters of the GPU Adam step for offloaded experts
+        (``_MOLECore::set_adam``, MOLE/cpp/define.hpp:524-541); ``hybrid_adam_count == -1`` means
+        all of them."""
+        self.adam = dict(beta1=float(beta1), beta2=float(beta2), t=int(t), lr=float(lr),
+                         lam=float(lam), eps=float(eps), adamW=bool(adamW))
+        self.hybrid_adam_count = self.d_experts if hybrid_adam_count == -1 else int(hybrid_adam_count)
+
+    def clear_tran_tmp(self):
+        """The reference frees temporaries of its D2H callbacks here (MOLE/cpp/define.hpp:366-378);
+        this pipeline has none: its staging blocks are guarded by events."""
 
     def GPUParamCore_fetch_single(self, p_id, i):
         return self.gpu_params[p_id][i]
@@ -605,16 +684,22 @@ class MOLECore:
         es = dispatched.element_size()
         chunk_bytes = Cs * M * es
 
+        # Edges between the streams are per record, as the reference's comm_event / para_event /
+        # comp_event are (MOLE/cpp/define.hpp:634-636): a record's compute waits for ITS exchange
+        # and fetch, its return exchange for ITS compute, so the exchanges of later records run
+        # beside the compute of earlier ones.
         for g in groups:
+            arrived, computed = {}, {}
             for ri in g:
                 rec = records[ri]
                 if W > 1:       # first exchange of this record's experts, on the comm stream
                     MOLEDist.all2all(x0, dispatched, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
+                    arrived[ri] = ExpertStreamCtx.record(comm)
                 self._fetch_para(rec)
             for ri in g:
                 rec = records[ri]
                 if W > 1:
-                    ExpertStreamCtx.wait(comp, comm)
+                    ExpertStreamCtx.wait_ticket(comp, arrived[ri])
                 if rec.use_cpu_param:
                     pool.wait_fetch(rec.ticket, comp)
                 w1, b1, w2, b2, slots, n_slots = self._weights(rec)
@@ -623,10 +708,12 @@ class MOLECore:
                 ops.ffn_fwd(desc, rcounts, x0, w1, b1, w2, b2, x1, h, out_local, ws, slots)
                 if rec.use_cpu_param:
                     pool.mark_used(rec.view_base, rec.batch_size, comp)
+                if W > 1:
+                    computed[ri] = ExpertStreamCtx.record(comp)
             for ri in g:
                 rec = records[ri]
                 if W > 1:       # return exchange, on the comm stream after this record's compute
-                    ExpertStreamCtx.wait(comm, comp)
+                    ExpertStreamCtx.wait_ticket(comm, computed[ri])
                     MOLEDist.all2all(ret, out_local, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
         if W > 1:
             ExpertStreamCtx.wait(comp, comm)
@@ -670,21 +757,29 @@ class MOLECore:
         dx1 = torch.empty(rows_total, F, dtype=dout.dtype, device=dout.device)
         accumulate = self._accumulate()
 
+        instant = self.adv_adam and (self.step + 1) % self.acc_step == 0
         for g in groups:
+            arrived, computed = {}, {}
             for ri in g:
                 rec = records[ri]
                 if W > 1:
                     MOLEDist.all2all(g_local, dout, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
+                    arrived[ri] = ExpertStreamCtx.record(comm)
                 self._fetch_para(rec)          # weights are fetched again for backward
             for ri in g:
                 rec = records[ri]
                 if W > 1:
-                    ExpertStreamCtx.wait(comp, comm)
+                    ExpertStreamCtx.wait_ticket(comp, arrived[ri])
                 if rec.use_cpu_param:
                     pool.wait_fetch(rec.ticket, comp)
                 w1, _, w2, _, slots, n_slots = self._weights(rec)
+                stage = None
                 if rec.use_cpu_param:
-                    grads, gslots, g_slots_n = self._staging_grads(rec, M, F, dout)
+                    stage = self._take_staging(M, F, dout, comp)
+                    grads, g_slots_n = stage.grads, self.ebatch_size
+                    gslots = [0] * L
+                    for i in range(rec.batch_size):
+                        gslots[rec.base_in_all + i] = i
                     acc = False
                 else:
                     grads, gslots, g_slots_n = self.gpu_grads, slots, self.s_experts
@@ -695,16 +790,25 @@ class MOLECore:
                             grads[0], grads[1], grads[2], grads[3], ws, slots, gslots)
                 if rec.use_cpu_param:
                     pool.mark_used(rec.view_base, rec.batch_size, comp)
-                    self._store_grad(rec, grads, comp)
+                    # the optimizer step of this batch right behind its backward, on the GPU
+                    # (MOLE/cpp/core.cpp:1216-1227), or the gradients back to the host
+                    n_adam = min(rec.batch_size, self.hybrid_adam_count - rec.batch_base) if instant else 0
+                    if n_adam > 0:
+                        self._instant_adam(rec, n_adam, stage, comp)
+                    if n_adam < rec.batch_size:
+                        self._store_grad(rec, grads, comp, first=max(n_adam, 0))
+                    stage.release(sctx.tran_back_stream())
+                if W > 1:
+                    computed[ri] = ExpertStreamCtx.record(comp)
             for ri in g:
                 rec = records[ri]
                 if W > 1 and input_requires_grad:
-                    ExpertStreamCtx.wait(comm, comp)
+                    ExpertStreamCtx.wait_ticket(comm, computed[ri])
                     MOLEDist.all2all(ret, dx_local, *exchange_geometry(rec, L, chunk_bytes), stream=comm)
         if W > 1:
             ExpertStreamCtx.wait(comp, comm)
         if self.d_experts > 0:
-            check(lib.mole_ctx_synchronize(sctx.handle, 4))     # D2H gradient stores done
+            check(lib.mole_ctx_synchronize(sctx.handle, 4))     # D2H stores done
             self._finish_grad_accumulate()
         ops.device_fault_poll()
         self.step += 1
@@ -713,28 +817,26 @@ class MOLECore:
         return ret
 
     # -- offloaded-expert gradients (MOLE/cpp/core.cpp:77-103, uparameter.cpp:68-83) ---------
-    def _staging_grads(self, rec: Record, M, F, like):
-        n = self.ebatch_size
-        if self._grad_staging is None:
-            kw = dict(dtype=like.dtype, device=like.device)
-            self._grad_staging = [torch.empty(n, F, M, **kw), torch.empty(n, F, **kw),
-                                  torch.empty(n, F, M, **kw), torch.empty(n, M, **kw)]
-            self._pending_acc = []
-        L = self.s_experts + self.d_experts
-        gslots = [0] * L
-        for i in range(rec.batch_size):
-            gslots[rec.base_in_all + i] = i
-        # the staging block is reused by the next record: order it after the previous D2H
-        sctx = ExpertStreamCtx.get(like.device)
-        ExpertStreamCtx.wait(torch.cuda.current_stream(), sctx.tran_back_stream())
-        return self._grad_staging, gslots, n
+    def _take_staging(self, M, F, like, comp) -> "_Staging":
+        """Device block that receives one record's weight gradients (and, for the GPU optimizer
+        step, its Adam moments).  Two blocks alternate, each guarded by an event: the compute of
+        record i+1 writes the other block while record i's block is still travelling to the host,
+        and waits only for the device-to-host copies of record i-1."""
+        if not self._staging:
+            self._staging = [_Staging(self.ebatch_size, M, F, like.dtype, like.device) for _ in range(2)]
+        st = self._staging[self._staging_turn]
+        self._staging_turn ^= 1
+        st.acquire(comp)
+        return st
 
-    def _store_grad(self, rec: Record, grads, comp) -> None:
+    def _store_grad(self, rec: Record, grads, comp, first: int = 0) -> None:
+        """Gradients of the record's experts ``[first, batch_size)`` to the pinned host arrays on
+        the device-to-host stream (``store_grad``, MOLE/cpp/core.cpp:77-103)."""
         sctx = ExpertStreamCtx.get(grads[0].device)
         lazy = getattr(self.cpu_grads[0], "lazy_zero", True)
         for p_id in range(4):
-            host = self.cpu_grads[p_id][rec.batch_base:rec.batch_base + rec.batch_size]
-            dev = grads[p_id][:rec.batch_size]
+            host = self.cpu_grads[p_id][rec.batch_base + first:rec.batch_base + rec.batch_size]
+            dev = grads[p_id][first:rec.batch_size]
             nbytes = host.numel() * host.element_size()
             if self.acc_step > 1 and not lazy:
                 stage = torch.empty_like(host).pin_memory()
@@ -747,8 +849,57 @@ class MOLECore:
                                              C.c_void_p(dev.data_ptr()), nbytes,
                                              C.c_void_p(comp.cuda_stream)))
 
+    def _instant_adam(self, rec: Record, n: int, stage: "_Staging", comp) -> None:
+        """Adam step of the record's first ``n`` experts on the GPU, right behind their backward
+        (``_MOLECore::instant_adam``, MOLE/cpp/core.cpp:848-943): the moments come in on the
+        host-to-device stream behind the compute, one fused kernel per parameter kind updates the
+        weights where they lie in the pool slots, and parameters and moments go back to the
+        pinned host arrays on the device-to-host stream.  With ``acc_step > 1`` the gradient the
+        host has accumulated over the earlier micro-steps is brought in and added
+        (core.cpp:906-918)."""
+        pool = _get_UniMem()
+        sctx = ExpertStreamCtx.get(stage.grads[0].device)
+        tran, back = sctx.tran_stream(), sctx.tran_back_stream()
+        a = self.adam
+        base = rec.batch_base
+        lazy = getattr(self.cpu_grads[0], "lazy_zero", True)
+        extra = self.acc_step > 1 and not lazy
+        stage.ensure_moments(extra)
+        ExpertStreamCtx.wait(tran, comp)            # gradients written, weights no longer read
+        a0 = rec.slots[0]
+        with torch.cuda.stream(tran):
+            for k in range(4):
+                stage.m[k][:n].copy_(self.cpu_mome[k][base:base + n], non_blocking=True)
+                stage.v[k][:n].copy_(self.cpu_vari[k][base:base + n], non_blocking=True)
+                if extra:
+                    stage.g_host[k][:n].copy_(self.cpu_grads[k][base:base + n], non_blocking=True)
+            for k in range(4):
+                per = stage.grads[k][0].numel()
+                es = stage.grads[k].element_size()
+                p_ptr = pool.bases[k] + a0 * per * es
+                check(lib.mole_adam_update(
+                    C.c_void_p(p_ptr), C.c_void_p(stage.m[k].data_ptr()),
+                    C.c_void_p(stage.v[k].data_ptr()), C.c_void_p(stage.grads[k].data_ptr()),
+                    C.c_void_p(stage.g_host[k].data_ptr()) if extra else None, n * per,
+                    ops._DTYPES[self.dtype], a["beta1"], a["beta2"], a["t"] + 1, a["lr"], a["lam"],
+                    a["eps"], int(a["adamW"]), C.c_void_p(tran.cuda_stream)))
+        for k in range(4):
+            per = stage.grads[k][0].numel()
+            es = stage.grads[k].element_size()
+            nbytes = n * per * es
+            for host, dev_ptr in ((self.cpu_params[k], pool.bases[k] + a0 * per * es),
+                                  (self.cpu_mome[k], stage.m[k].data_ptr()),
+                                  (self.cpu_vari[k], stage.v[k].data_ptr())):
+                check(lib.mole_store_to_host(sctx.handle, C.c_void_p(host[base:base + n].data_ptr()),
+                                             C.c_void_p(dev_ptr), nbytes,
+                                             C.c_void_p(tran.cuda_stream)))
+        # a later fetch into these slots waits until the updated weights have left them
+        pool.mark_used(rec.view_base, rec.batch_size, back)
+        # the next host-to-device copy into this block's moments must not overtake these stores
+        ExpertStreamCtx.wait(tran, back)
+
     def _finish_grad_accumulate(self) -> None:
-        for host, stage in getattr(self, "_pending_acc", []):
+        for host, stage in self._pending_acc:
             host += stage
         self._pending_acc = []
 

@@ -156,12 +156,16 @@ extern "C" int mole_device_fault_peek(int32_t* fault) {
 // ---- streams --------------------------------------------------------------------------
 constexpr int kStreams = 16;
 constexpr int kEventRing = 64;
+constexpr int kTicketRing = 1024;
 struct mole_ctx {
   int device;
   int single;
   cudaStream_t streams[kStreams];
   cudaEvent_t ring[kEventRing];
   int ring_pos;
+  cudaEvent_t tickets[kTicketRing];     // per-record edges (mole_ctx_event_record / _wait)
+  int64_t ticket_serial[kTicketRing];   // which record call last used the slot
+  int64_t next_ticket;
 };
 
 static cudaEvent_t next_event(mole_ctx* c) {
@@ -183,6 +187,11 @@ extern "C" int mole_ctx_create(int32_t device, int32_t single_stream, mole_ctx**
   }
   for (int i = 0; i < kEventRing; ++i)
     MOLE_CUDA_OK(cudaEventCreateWithFlags(&c->ring[i], cudaEventDisableTiming));
+  for (int i = 0; i < kTicketRing; ++i) {
+    MOLE_CUDA_OK(cudaEventCreateWithFlags(&c->tickets[i], cudaEventDisableTiming));
+    c->ticket_serial[i] = -1;
+  }
+  c->next_ticket = 0;
   *out = c;
   return MOLE_OK;
 }
@@ -191,6 +200,7 @@ extern "C" int mole_ctx_destroy(mole_ctx* c) {
   for (int i = 0; i < kStreams; ++i)
     if (c->streams[i]) cudaStreamDestroy(c->streams[i]);
   for (int i = 0; i < kEventRing; ++i) cudaEventDestroy(c->ring[i]);
+  for (int i = 0; i < kTicketRing; ++i) cudaEventDestroy(c->tickets[i]);
   delete c;
   return MOLE_OK;
 }
@@ -206,6 +216,29 @@ extern "C" int mole_ctx_wait(mole_ctx* c, void* waiter, void* waited) {
   cudaEvent_t e = next_event(c);
   MOLE_CUDA_OK(cudaEventRecord(e, static_cast<cudaStream_t>(waited)));
   MOLE_CUDA_OK(cudaStreamWaitEvent(static_cast<cudaStream_t>(waiter), e, 0));
+  return MOLE_OK;
+}
+// Per-record edges: what the reference keeps as comp_event / comm_event / para_event in every
+// _BatchRecord (MOLE/cpp/define.hpp:634-636, recorded at MOLE/cpp/core.cpp:177).  A ticket names
+// the work enqueued on `stream` up to the record call; a later wait orders another stream behind
+// exactly that work, not behind everything the first stream has been given since.
+extern "C" int mole_ctx_event_record(mole_ctx* c, void* stream, int64_t* ticket) {
+  MOLE_REQUIRE(c && ticket, "null argument");
+  const int64_t t = c->next_ticket++;
+  const int slot = (int)(t % kTicketRing);
+  MOLE_CUDA_OK(cudaEventRecord(c->tickets[slot], static_cast<cudaStream_t>(stream)));
+  c->ticket_serial[slot] = t;
+  *ticket = t;
+  return MOLE_OK;
+}
+extern "C" int mole_ctx_event_wait(mole_ctx* c, int64_t ticket, void* stream) {
+  MOLE_REQUIRE(c != nullptr, "ctx is null");
+  MOLE_REQUIRE(ticket >= 0 && ticket < c->next_ticket, "ticket %lld was never issued", (long long)ticket);
+  const int slot = (int)(ticket % kTicketRing);
+  if (c->ticket_serial[slot] != ticket)
+    return fail(MOLE_ERR_STATE, "ticket %lld is older than the last %d records and has been reused",
+                (long long)ticket, kTicketRing);
+  MOLE_CUDA_OK(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), c->tickets[slot], 0));
   return MOLE_OK;
 }
 extern "C" int mole_ctx_synchronize(mole_ctx* c, int32_t idx) {

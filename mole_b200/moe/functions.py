@@ -16,6 +16,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..utils.Utimer import UATimer
 
 
 class GateRoute(torch.autograd.Function):
@@ -119,6 +120,12 @@ class BatchFusedFWD(torch.autograd.Function):
         ctx.dummy_shape = dummy_param.shape
         timer = module.timer if time_it and hasattr(module, "timer") else None
         ctx.peer = getattr(module, "_peer_exchange", None)
+        ctx.time_it = bool(time_it)
+        ctx.moe_id = getattr(module, "moe_id", 0)
+        if time_it:
+            # the gap since the step began (or since the previous MoE layer finished) is the time
+            # this layer's experts could have been travelling: the scheduler sizes prefetches by it
+            UATimer.track_fwd_end()
         if timer:
             timer.start_fwd()
         if ctx.peer is not None:
@@ -127,16 +134,31 @@ class BatchFusedFWD(torch.autograd.Function):
             out = core.forward(dispatched_input.contiguous(), counts, True)
         if timer:
             timer.stop_fwd()
+        if time_it:
+            last = len(type(module)._instance) - 1
+            if ctx.moe_id >= last:
+                UATimer.track_bwd_start()       # next: the gap in front of the last layer's backward
+            else:
+                UATimer.track_fwd_start()
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
+        if ctx.time_it:
+            UATimer.track_bwd_end()
+        dx = BatchFusedFWD._backward(ctx, grad_out)
+        if ctx.time_it and ctx.moe_id > 0:
+            UATimer.track_bwd_start()
+        dummy_grad = torch.zeros(ctx.dummy_shape, device=grad_out.device, dtype=grad_out.dtype)
+        return dx, None, dummy_grad, None, None
+
+    @staticmethod
+    def _backward(ctx, grad_out):
         if ctx.peer is not None:
             dx = ctx.core.backward_peer(ctx.peer, ctx.input_requires_grad)
         else:
             dx = ctx.core.backward(grad_out.contiguous(), ctx.counts, ctx.input_requires_grad)
-        dummy_grad = torch.zeros(ctx.dummy_shape, device=grad_out.device, dtype=grad_out.dtype)
-        return dx, None, dummy_grad, None, None
+        return dx
 
 
 class pfetchbwd(torch.autograd.Function):

@@ -61,7 +61,17 @@ class UnifiedCPUTensor(object):
         for kind in ("param", "grad", "momentum", "variance"):
             inst.blocks[kind] = _pinned_zeros(inst.numel, dtype)
             inst.offset[kind] = 0
+        # the whole block is one optimizer parameter (Uparam.py:136-138)
+        inst.blocks["param"].grad_ = inst.blocks["grad"]
+        inst.blocks["param"].momentum = inst.blocks["momentum"]
+        inst.blocks["param"].variance = inst.blocks["variance"]
+        inst.blocks["grad"].lazy_zero = True
         inst.inited = True
+
+    @staticmethod
+    def get_cpu_experts():
+        inst = UnifiedCPUTensor._instance
+        return [inst.blocks["param"]] if inst is not None and inst.inited and inst.numel > 0 else []
 
     @staticmethod
     def _carve(kind, size, count):

@@ -91,3 +91,17 @@ class ExpertStreamCtx(object):
         inst = ExpertStreamCtx._instance
         check(lib.mole_ctx_wait(inst.handle, C.c_void_p(waiter.cuda_stream),
                                 C.c_void_p(waited.cuda_stream)))
+
+    @staticmethod
+    def record(stream: torch.cuda.Stream) -> int:
+        """Ticket for the work enqueued on ``stream`` so far (a per-record event)."""
+        inst = ExpertStreamCtx._instance
+        t = C.c_int64()
+        check(lib.mole_ctx_event_record(inst.handle, C.c_void_p(stream.cuda_stream), C.byref(t)))
+        return t.value
+
+    @staticmethod
+    def wait_ticket(waiter: torch.cuda.Stream, ticket: int) -> None:
+        """``waiter`` waits for the work named by ``ticket`` only."""
+        inst = ExpertStreamCtx._instance
+        check(lib.mole_ctx_event_wait(inst.handle, ticket, C.c_void_p(waiter.cuda_stream)))
