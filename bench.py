@@ -983,6 +983,23 @@ def run_ours(args):
         out["hbm_kernels"] = hbm_kernel_report(m, x, gy, cf, pk)
     if rank == 0 and world == 1 and not args.no_kernel_report and not cfg.get("offload"):
         out["stock_torch_gpu"] = stock_torch_gpu(m, x, gy, k, cf)
+    if world == 1 and not args.no_kernel_report and not cfg.get("offload"):
+        # the combine fused into the FC2 epilogue against the separate combine kernel, same box,
+        # alternating (device-resident steps)
+        keep = m.fuse_combine
+        ab = {True: [], False: []}
+        for _ in range(3):
+            for fused in (True, False):
+                m.fuse_combine = fused
+                for _ in range(3):
+                    step()
+                t, _ = hs.timed(step, 20)
+                ab[fused].append(t / 20)
+        m.fuse_combine = keep
+        out["combine_fusion"] = {"fused_ms_per_step": statistics.median(ab[True]),
+                                 "separate_ms_per_step": statistics.median(ab[False]),
+                                 "default": "separate kernel (fuse_combine=True selects the fused epilogue)",
+                                 "note": "whole fwd+bwd step, 3 x 20 steps each way, alternating"}
     check_fault("after the kernel reports")
     hs.barrier()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -234,6 +234,19 @@ int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts, const int32_t* s
                  void* x1, void* h, void* out,
                  void* workspace, int64_t workspace_bytes, void* stream);
 
+/* mole_ffn_fwd with the gate-weighted combine (fast_decode, MOLE/moe/layer.py:456-458) fused into
+ * the second GEMM's epilogue: besides storing out, FC2 adds gates[pair] * out[row] into
+ * y[token] ([T, M], zeroed by the caller) for every valid row, row (e, s) being pair
+ * perm[offsets[e] + s] = token * k + choice (the arrays of mole_gate_route_fwd).  bf16, one
+ * source rank, k <= 2 (two addends commute: the result does not depend on the order in which
+ * the reductions land); other cases get MOLE_ERR_UNSUPPORTED and use mole_combine_fwd. */
+int mole_ffn_fwd_combine(const mole_ffn_desc* d, const int32_t* counts,
+                         const int32_t* slot_of_expert, const void* x, const void* w1,
+                         const void* b1, const void* w2, const void* b2, void* x1, void* h,
+                         void* out, const int32_t* offsets, const int32_t* perm,
+                         const float* gates, int32_t k, void* y,
+                         void* workspace, int64_t workspace_bytes, void* stream);
+
 /* dout rows -> dx rows (NULL to skip) and weight grads gw1,gw2 [n_slots,F,M], gb1 [n_slots,F],
  * gb2 [n_slots,M].  dx1 [.., F] is caller-provided scratch. */
 int mole_ffn_bwd(const mole_ffn_desc* d, const int32_t* counts, const int32_t* slot_of_expert,
@@ -310,6 +323,14 @@ int mole_peer_export(void* ptr, uint8_t* handle64);
 int mole_peer_open(const uint8_t* handle64, void** ptr);
 int mole_peer_close(void* ptr);
 int mole_barrier(mole_comm* comm, void* scratch, void* stream);
+/* the same barrier through flags in peer-visible memory instead of NCCL: peer_flags[q] is rank q's
+ * int32 [world] array (mole_peer_alloc'ed, zeroed) mapped into this process; `seq` is the
+ * barrier's sequence number, 1, 2, 3, ... identical on every rank.  One tiny kernel stores seq
+ * into entry `rank` of every peer's array and waits, at most limit_ns, until its own array shows
+ * seq (or more) from every peer; when the wait runs out it records 40 + the missing rank in the
+ * device fault word (mole_device_fault) and returns -- nothing hangs. */
+int mole_peer_barrier(void* const* peer_flags, int32_t world, int32_t rank, int32_t seq,
+                      int64_t limit_ns, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * (e) offloaded experts.  Replaces _UniMem (MOLE/cpp/define.hpp:143-193,

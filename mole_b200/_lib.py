@@ -66,6 +66,8 @@ SIGNATURES = {
     "mole_ffn_workspace_bytes": (C.c_int, [C.POINTER(FfnDesc), _pi64]),
     "mole_ffn_fwd": (C.c_int, [C.POINTER(FfnDesc), _p, _pi32, _p, _p, _p, _p, _p, _p, _p, _p,
                                _p, _i64, _p]),
+    "mole_ffn_fwd_combine": (C.c_int, [C.POINTER(FfnDesc), _p, _pi32, _p, _p, _p, _p, _p, _p, _p, _p,
+                                       _p, _p, _p, _i32, _p, _p, _i64, _p]),
     "mole_ffn_bwd": (C.c_int, [C.POINTER(FfnDesc), _p, _pi32, _pi32, _p, _p, _p, _p, _p, _p,
                                _p, _p, _p, _p, _p, _p, _p, _i64, _p]),
     "mole_ctx_create": (C.c_int, [_i32, _i32, C.POINTER(_p)]),
@@ -93,6 +95,7 @@ SIGNATURES = {
     "mole_peer_open": (C.c_int, [C.POINTER(C.c_uint8), C.POINTER(_p)]),
     "mole_peer_close": (C.c_int, [_p]),
     "mole_barrier": (C.c_int, [_p, _p, _p]),
+    "mole_peer_barrier": (C.c_int, [C.POINTER(_p), _i32, _i32, _i32, _i64, _p]),
     "mole_pool_create": (C.c_int, [_p, _i32, _i32, _i32, _i32, C.POINTER(_p)]),
     "mole_pool_destroy": (C.c_int, [_p]),
     "mole_pool_base": (C.c_int, [_p, _i32, C.POINTER(_p)]),

@@ -189,7 +189,8 @@ class PeerExchange:
     (``mole_barrier``): every reader of a buffer has finished before the barrier that precedes
     its next writer, see ``MOLECore.forward_peer`` / ``backward_peer``."""
 
-    KINDS = ("x0", "ret", "g", "dx", "counts")
+    KINDS = ("x0", "ret", "g", "dx", "counts", "flags")
+    BARRIER_LIMIT_NS = 2_000_000_000      # a rank that never arrives costs its peers two seconds
 
     def __init__(self, world, rank, L, Cs, M, dtype, device, group):
         import torch.distributed as dist
@@ -200,7 +201,7 @@ class PeerExchange:
         es = torch.empty(0, dtype=dtype).element_size()
         row_bytes = world * L * Cs * M * es
         sizes = {"x0": row_bytes, "ret": row_bytes, "g": row_bytes, "dx": row_bytes,
-                 "counts": max(256, world * L * 4)}
+                 "counts": max(256, world * L * 4), "flags": 256}
         self.sizes = sizes
         # Every rank takes the same decision: each phase ends in a collective that carries the
         # ranks' success flags, and one failure anywhere makes all of them give the buffers up
@@ -250,6 +251,9 @@ class PeerExchange:
         self.Cs = None
         self.set_stride(Cs)
         self.scratch = torch.zeros(8 * world, dtype=torch.uint8, device=device)
+        self.barrier_seq = 0     # flag barriers taken so far (the same number on every rank)
+        import os
+        self.flag_barrier = os.environ.get("MOLE_FLAG_BARRIER", "1") != "0"
         self.serial = 0          # forward passes so far: backward checks that its buffers are still its own
         dist.barrier(group=group)
 
@@ -278,8 +282,16 @@ class PeerExchange:
         self.counts = view("counts", torch.int32, (world * L,))
 
     def barrier(self):
-        check(lib.mole_barrier(MOLEDist._instance.comm, C.c_void_p(self.scratch.data_ptr()),
-                               C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        """Every rank has finished what it enqueued so far on the current stream: flags stored
+        into the peers' mapped memory with a bounded wait (``MOLE_FLAG_BARRIER=0``: a 4-byte
+        grouped NCCL send/recv instead)."""
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        if self.flag_barrier:
+            self.barrier_seq += 1
+            check(lib.mole_peer_barrier(self.table["flags"], self.world, self.rank, self.barrier_seq,
+                                        self.BARRIER_LIMIT_NS, stream))
+        else:
+            check(lib.mole_barrier(MOLEDist._instance.comm, C.c_void_p(self.scratch.data_ptr()), stream))
 
     def close(self, barrier=False, group=None):
         """Unmaps the peers' buffers, then frees this rank's own.  ``barrier=True`` (then every
@@ -640,9 +652,19 @@ class MOLECore:
         rec.slots = [pool.abs_slot(rec.view_base + i) for i in range(rec.batch_size)]
 
     # -- forward pipeline (MOLE/cpp/core.cpp:991-1131) -------------------------------------
-    def forward(self, dispatched: torch.Tensor, counts: torch.Tensor, requires_grad: bool):
+    def can_fuse_combine(self, plan, M: int) -> bool:
+        """Whether FC2's epilogue can also do the gate-weighted combine for this batch: one rank,
+        bf16 on the one-CTA tensor-core kernel (fewer than 12 row tiles per expert), top-1 / top-2."""
+        F = self._ffn_dim()
+        return (self.world_size == 1 and self.dtype == torch.bfloat16 and self.ffn_backend in (0, 2)
+                and plan.k <= 2 and plan.Cs // 128 < 12 and M % 128 == 0 and F % 128 == 0)
+
+    def forward(self, dispatched: torch.Tensor, counts: torch.Tensor, requires_grad: bool,
+                combine=None):
         """``dispatched`` ``[E_total, Cs, M]`` capacity-strided rows, ``counts`` ``[E_total]``
-        valid rows per chunk -> expert outputs in the same layout."""
+        valid rows per chunk -> expert outputs in the same layout.  ``combine = (plan, gates, y)``
+        makes the second GEMM's epilogue add ``gates * row`` into the zeroed ``y [T, M]`` as well
+        (``can_fuse_combine`` says when that is possible)."""
         self._check_fault()
         E, Cs, M = dispatched.shape
         W = self.world_size
@@ -705,7 +727,12 @@ class MOLECore:
                 w1, b1, w2, b2, slots, n_slots = self._weights(rec)
                 desc = self._desc(M, F, W, Cs, rec, n_slots)
                 ws = ops.ffn_workspace(desc, dispatched.device)
-                ops.ffn_fwd(desc, rcounts, x0, w1, b1, w2, b2, x1, h, out_local, ws, slots)
+                if combine is not None:
+                    plan, gates, y = combine
+                    ops.ffn_fwd_combine(desc, rcounts, x0, w1, b1, w2, b2, x1, h, out_local, plan,
+                                        gates, y, ws, slots)
+                else:
+                    ops.ffn_fwd(desc, rcounts, x0, w1, b1, w2, b2, x1, h, out_local, ws, slots)
                 if rec.use_cpu_param:
                     pool.mark_used(rec.view_base, rec.batch_size, comp)
                 if W > 1:

@@ -123,10 +123,17 @@ static int peers_for_ffn(const mole_ffn_desc* d, void* const* peer_rows, int ran
   return MOLE_OK;
 }
 
+struct CombineArgs {
+  const int32_t* offsets;
+  const int32_t* perm;
+  const float* gates;
+  int k;
+  void* y;
+};
 static int ffn_fwd_impl(const mole_ffn_desc* d, const int32_t* counts,
                         const int32_t* slot_of_expert, const void* x, const void* w1,
                         const void* b1, const void* w2, const void* b2, void* x1, void* h,
-                        void* out, const PeerMap* peers, void* workspace,
+                        void* out, const PeerMap* peers, const CombineArgs* comb, void* workspace,
                         int64_t workspace_bytes, void* stream);
 
 extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
@@ -134,8 +141,29 @@ extern "C" int mole_ffn_fwd(const mole_ffn_desc* d, const int32_t* counts,
                             const void* b1, const void* w2, const void* b2, void* x1, void* h,
                             void* out, void* workspace, int64_t workspace_bytes, void* stream) {
   MOLE_REQUIRE(out != nullptr, "null pointer argument");
-  return ffn_fwd_impl(d, counts, slot_of_expert, x, w1, b1, w2, b2, x1, h, out, nullptr, workspace,
-                      workspace_bytes, stream);
+  return ffn_fwd_impl(d, counts, slot_of_expert, x, w1, b1, w2, b2, x1, h, out, nullptr, nullptr,
+                      workspace, workspace_bytes, stream);
+}
+
+// FC2's epilogue also adds gates[pair] * row into y[token] (bf16 reductions at L2; the caller
+// zeroes y first): the combine needs no pass of its own over the expert outputs.  The rows are
+// still stored, backward reads them for the gate gradient.
+extern "C" int mole_ffn_fwd_combine(const mole_ffn_desc* d, const int32_t* counts,
+                                    const int32_t* slot_of_expert, const void* x, const void* w1,
+                                    const void* b1, const void* w2, const void* b2, void* x1,
+                                    void* h, void* out, const int32_t* offsets,
+                                    const int32_t* perm, const float* gates, int32_t k, void* y,
+                                    void* workspace, int64_t workspace_bytes, void* stream) {
+  if (int rc = check_desc(d)) return rc;
+  MOLE_REQUIRE(out && offsets && perm && gates && y, "null pointer argument");
+  MOLE_REQUIRE(k >= 1 && k <= 2, "the fused combine covers top-1 and top-2 (k=%d): with more addends "
+               "per token the order of the reductions would show in the result", k);
+  if (!(use_tc(d) && d->n_src == 1 && single_cta(d)))
+    return fail(MOLE_ERR_UNSUPPORTED, "the fused combine needs bf16 on the one-CTA tensor-core kernel "
+                "(fewer than 12 row tiles per expert) and one source rank");
+  CombineArgs c{offsets, perm, gates, k, y};
+  return ffn_fwd_impl(d, counts, slot_of_expert, x, w1, b1, w2, b2, x1, h, out, nullptr, &c,
+                      workspace, workspace_bytes, stream);
 }
 
 extern "C" int mole_ffn_fwd_peer(const mole_ffn_desc* d, const int32_t* counts,
@@ -146,14 +174,14 @@ extern "C" int mole_ffn_fwd_peer(const mole_ffn_desc* d, const int32_t* counts,
   if (int rc = check_desc(d)) return rc;
   PeerMap pm;
   if (int rc = peers_for_ffn(d, peer_out, rank, pm)) return rc;
-  return ffn_fwd_impl(d, counts, slot_of_expert, x, w1, b1, w2, b2, x1, h, nullptr, &pm, workspace,
-                      workspace_bytes, stream);
+  return ffn_fwd_impl(d, counts, slot_of_expert, x, w1, b1, w2, b2, x1, h, nullptr, &pm, nullptr,
+                      workspace, workspace_bytes, stream);
 }
 
 static int ffn_fwd_impl(const mole_ffn_desc* d, const int32_t* counts,
                         const int32_t* slot_of_expert, const void* x, const void* w1,
                         const void* b1, const void* w2, const void* b2, void* x1, void* h,
-                        void* out, const PeerMap* peers, void* workspace,
+                        void* out, const PeerMap* peers, const CombineArgs* comb, void* workspace,
                         int64_t workspace_bytes, void* stream) {
   if (int rc = check_desc(d)) return rc;
   MOLE_REQUIRE(counts && x && w1 && b1 && w2 && b2 && x1 && h && (out || peers) && workspace,
@@ -193,6 +221,10 @@ static int ffn_fwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   a.out0 = out; a.out1 = nullptr; a.epi = EPI_BIAS;
   a.rowmap = compact ? wk.rowmap : nullptr;          // back to the (source, expert) chunks
   if (peers) { a.peers = *peers; a.peer_Cs = d->Cs; }
+  if (comb) {
+    a.c_perm = comb->perm; a.c_offsets = comb->offsets; a.c_counts = counts; a.c_gates = comb->gates;
+    a.c_y = comb->y; a.c_k = comb->k; a.c_Cs = d->Cs;
+  }
   return row_gemm(d, a, st);
 }
 

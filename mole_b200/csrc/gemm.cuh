@@ -33,6 +33,13 @@ struct RowGemmArgs {
   const int32_t* rowmap;    // tensor cores, FC2 / dX: scatter output rows (-1 = drop), or null
   PeerMap peers;            // with rowmap: the scattered rows go to their source ranks (n > 0)
   int peer_Cs;              // rows per chunk of the receive buffers
+  // FC2 with the gate-weighted combine in its epilogue (c_y != null): y[t] += gates[pair] * out[row]
+  const int32_t* c_perm;
+  const int32_t* c_offsets;
+  const int32_t* c_counts;
+  const float* c_gates;
+  void* c_y;
+  int c_k, c_Cs;
   Schedule sched;
   SlotMap wslot;
 };

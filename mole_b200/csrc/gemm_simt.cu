@@ -335,11 +335,18 @@ colsum_kernel(const __grid_constant__ ColsumArgs a) {
   if (col < a.N) {
     for (int t = t0; t < t1; ++t) {
       const T* base = A + ((int64_t)a.sched.tile_row0[t] + rl) * a.N + col;
-#pragma unroll
-      for (int r0 = 0; r0 < kTileRows; r0 += 32) {          // rows rl + {0, 8, 16, 24} + r0
+      const int valid = a.sched.tile_rows[t];               // rows beyond it may never have been written
+      for (int r0 = 0; r0 < valid; r0 += 32) {              // rows rl + {0, 8, 16, 24} + r0
         float v[4][V];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) Vec16<T>::load(base + (int64_t)(r0 + 8 * u) * a.N, v[u]);
+        for (int u = 0; u < 4; ++u) {
+          if (r0 + 8 * u + rl < valid) {
+            Vec16<T>::load(base + (int64_t)(r0 + 8 * u) * a.N, v[u]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < V; ++c) v[u][c] = 0.f;
+          }
+        }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
 #pragma unroll

@@ -29,10 +29,13 @@ namespace mole {
 
 constexpr int kBM = 128;          // rows of one UMMA (cta_group::1)
 constexpr int kBK = 64;           // K elements per stage = one 128-byte swizzle span of bf16
+// Weight-gradient mode: K runs over an expert's rows, a stage holds kWBK of them.  (32-row stages
+// in a ring twice as deep were measured: 19-33 % slower -- twice the TMA requests and stage
+// hand-shakes per output tile; the weight-gradient launch is sensitive to both.)
+constexpr int kWBK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kEpiWarps = 16;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
-constexpr uint32_t kABytes = kBM * kBK * 2;
 
 enum TcMode : int { TC_ROWS = 0, TC_WGRAD = 1 };
 
@@ -254,7 +257,24 @@ struct TcParams {
   __nv_bfloat16* out1;
   int32_t* fault;
   SlotMap slot;
+  // gate-weighted combine fused into the FC2 epilogue (one-CTA kernel, one source rank):
+  // row (e, s) belongs to pair perm[offsets[e] + s] = t * k + j; y[t] += gates[pair] * out
+  const int32_t* c_perm;
+  const int32_t* c_offsets;
+  const int32_t* c_counts;
+  const float* c_gates;
+  __nv_bfloat16* c_y;          // null: no fused combine
+  int c_k, c_Cs;
 };
+
+// y[0..7] (eight bf16 pairs = 16 columns) += v, as two 16-byte reductions at L2.  With k <= 2 a
+// token's row receives at most two addends, whose sum does not depend on their order.
+__device__ __forceinline__ void red_add_bf16x16(__nv_bfloat16* y, const uint32_t (&v)[8]) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+               ::"l"(y), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+               ::"l"(y + 8), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
 
 struct WorkItem {
   int valid;
@@ -398,7 +418,8 @@ template <int EPI, int ACT, int GBWD, bool HAS_BIAS, bool ACCUM, int NSTEPS>
 __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr, bool empty,
                                               bool valid, __nv_bfloat16* sout, int64_t obase,
                                               const float* bias_s, int c_begin,
-                                              uint32_t (&pre)[NSTEPS][8], uint8_t* strip) {
+                                              uint32_t (&pre)[NSTEPS][8], uint8_t* strip,
+                                              __nv_bfloat16* yrow = nullptr, float gate = 0.f) {
   const bool remote = (EPI == EPI_BIAS || EPI == EPI_STORE) && p.peer_n > 0;
   uint32_t keep[NSTEPS][8];       // remote rows: the whole slice first, then whole-line stores
   {
@@ -455,6 +476,12 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
         } else if (valid) {
           st_v8(sout + obase + c, o);
         }
+        if (yrow != nullptr) {       // fused combine: the stored (rounded) row times its gate weight
+          uint32_t gv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gv[i] = pack_bf16(gate * bf16_lo(o[i]), gate * bf16_hi(o[i]));
+          red_add_bf16x16(yrow + c, gv);
+        }
       } else if (EPI == EPI_DACT) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -470,6 +497,12 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
           for (int i = 0; i < 8; ++i) keep[step][i] = o[i];
         } else if (valid) {
           st_v8(sout + obase + c, o);
+        }
+        if (yrow != nullptr) {
+          uint32_t gv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gv[i] = pack_bf16(gate * bf16_lo(o[i]), gate * bf16_hi(o[i]));
+          red_add_bf16x16(yrow + c, gv);
         }
       }
     }
@@ -582,7 +615,10 @@ template <int MODE, bool B_KMAJOR, int BN, int STAGES, int EV>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ TcParams p) {
-  constexpr uint32_t kBBytes = BN * kBK * 2;
+  constexpr int KR = MODE == TC_WGRAD ? kWBK : kBK;       // K extent of one shared-memory stage
+  constexpr uint32_t kBoxBytes = 128 * KR;                // one 64-element-wide MN-major TMA box
+  constexpr uint32_t kABytes = kBM * KR * 2;
+  constexpr uint32_t kBBytes = BN * KR * 2;
   constexpr uint32_t kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN;     // two accumulator stages (256 or 512 columns)
   constexpr bool A_MN = (MODE == TC_WGRAD);
@@ -633,7 +669,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------
-    if (lane == 0) {
+    // Rows mode: one lane issues the stage's loads (two large boxes with K-major weights).
+    // Weight-gradient mode: a stage is six boxes of 8 KB (both operands MN-major, 64 columns per
+    // box); the whole warp runs the loop and lanes 0..5 issue one box each, so the requests of a
+    // stage leave together instead of one after the other from a single thread.
+    if (MODE == TC_WGRAD || lane == 0) {
       int stage = 0;
       uint32_t phase = 0, issued = 0;
       bool ok = true;
@@ -654,7 +694,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             } else {
 #pragma unroll
               for (int i = 0; i < BN / 64; ++i)
-                tma_load_3d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, kb * kBK, slot);
+                tma_load_3d(sb + i * kBoxBytes, &tmap_b, bar, w.n0 + 64 * i, kb * kBK, slot);
             }
             ++issued;
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -663,28 +703,30 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // K runs over the expert's rows, tile by tile, and stops at each tile's valid rows
           // (64-row blocks here, 16-row MMA steps in the issuer): with ~256 rows per expert the
           // zero rows up to the next multiple of 128 would be a fifth of the work.
+          constexpr int kBoxesA = kBM / 64, kBoxes = kBoxesA + BN / 64;
           for (int t = w.t0; t < w.t1 && ok; ++t) {
             const int trow = p.tile_row0[t];
-            const int halves = p.tile_rows[t] > kBK ? 2 : 1;
+            const int halves = (p.tile_rows[t] + KR - 1) / KR;
             for (int hf = 0; hf < halves; ++hf) {
-              if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1))) break;
+              // every lane waits (the same barrier, the same answer up to the moment of a time-out)
+              ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 1));
+              if (!ok) break;
               const uint32_t bar = full0 + 8 * stage;
-              const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
-              const int row = trow + hf * kBK;
-              mbar_expect_tx(bar, kStageBytes);
-#pragma unroll
-              for (int i = 0; i < kBM / 64; ++i)
-                tma_load_2d(sa + i * 8192, &tmap_a, bar, w.row0 + 64 * i, row);
-#pragma unroll
-              for (int i = 0; i < BN / 64; ++i)
-                tma_load_2d(sb + i * 8192, &tmap_b, bar, w.n0 + 64 * i, row);
+              const uint32_t sa = smem_base + stage * kStageBytes;
+              const int row = trow + hf * KR;
+              if (lane == 0) mbar_expect_tx(bar, kStageBytes);
+              __syncwarp();                   // the expectation is armed before any box can complete
+              if (lane < kBoxesA)
+                tma_load_2d(sa + lane * kBoxBytes, &tmap_a, bar, w.row0 + 64 * lane, row);
+              else if (lane < kBoxes)
+                tma_load_2d(sa + lane * kBoxBytes, &tmap_b, bar, w.n0 + 64 * (lane - kBoxesA), row);
               ++issued;
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           }
         }
       }
-      if (*abort_flag) drain_loads(full0, STAGES, issued);
+      if (lane == 0 && *abort_flag) drain_loads(full0, STAGES, issued);
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------------
@@ -705,11 +747,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
 #pragma unroll
-          for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
+          for (int ks = 0; ks < KR / kUmmaK; ++ks) {
             if (ks < ksteps) {
-              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
+              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024)
                                        : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
-              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
+              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024)
                                        : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
               tcgen05_mma_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
             }
@@ -724,10 +766,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           bool first = true;
           for (int t = w.t0; t < w.t1; ++t) {
             const int v = p.tile_rows[t];
-            const int halves = v > kBK ? 2 : 1;
+            const int halves = (v + KR - 1) / KR;
             for (int hf = 0; hf < halves; ++hf) {
-              const int left = v - hf * kBK;
-              issue_stage(left >= kBK ? kBK / kUmmaK : (left + kUmmaK - 1) / kUmmaK, first);
+              const int left = v - hf * KR;
+              issue_stage(left >= KR ? KR / kUmmaK : (left + kUmmaK - 1) / kUmmaK, first);
               first = false;
             }
           }
@@ -780,6 +822,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           (MODE == TC_ROWS && p.bias) ? p.bias + (int64_t)slot * p.N + w.n0 : nullptr;
       constexpr int NSTEPS = BN / 4 / kEpiStep;
       uint32_t pre[NSTEPS][8];
+      // fused combine (FC2, rows not scattered): where this thread's row goes, with which gate weight
+      __nv_bfloat16* yrow = nullptr;
+      float gate = 0.f;
+      if (MODE == TC_ROWS && EvTraits<EV>::scatter && p.c_y != nullptr) {
+        const int srow = w.row0 + lrow - e * p.c_Cs;
+        if (srow < p.c_counts[e]) {
+          const int pair = p.c_perm[p.c_offsets[e] + srow];
+          gate = p.c_gates[pair];
+          yrow = p.c_y + (int64_t)(pair / p.c_k) * p.N + w.n0;
+        }
+      }
       epilogue_prefetch<EV, NSTEPS>(p, obase, bias, bias_strip[ew], cq * (BN / 4), pre);
       if (!empty) {
         // warp-uniform: the epilogue's tcgen05.ld and shuffles need all 32 lanes
@@ -795,7 +848,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       else
         epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
             p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, empty, valid, sout, obase,
-            bias_strip[ew], cq * (BN / 4), pre, scatter_strip[ew]);
+            bias_strip[ew], cq * (BN / 4), pre, scatter_strip[ew], yrow, gate);
       if (!empty) {
         tcgen05_fence_before();
         __syncwarp();
@@ -831,8 +884,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // to both CTAs' barriers; the odd CTA's epilogue releases the accumulator with a remote arrive.
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared::cluster address
 constexpr int kBN2 = 256;
-constexpr uint32_t kBHalfBytes = (kBN2 / 2) * kBK * 2;
-constexpr uint32_t kStage2Bytes = kABytes + kBHalfBytes;
+template <int KR> struct Pair2 {
+  static constexpr uint32_t kBoxBytes = 128 * KR;
+  static constexpr uint32_t kABytes = kBM * KR * 2;
+  static constexpr uint32_t kBHalfBytes = (kBN2 / 2) * KR * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBHalfBytes;
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -922,6 +979,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ TcParams p) {
   constexpr uint32_t kTmemCols = 2 * kBN2;
+  constexpr int KR = MODE == TC_WGRAD ? kWBK : kBK;
+  constexpr uint32_t kBoxBytes = Pair2<KR>::kBoxBytes;
+  constexpr uint32_t kABytes = Pair2<KR>::kABytes;
+  constexpr uint32_t kBHalfBytes = Pair2<KR>::kBHalfBytes;
+  constexpr uint32_t kStage2Bytes = Pair2<KR>::kStageBytes;
   constexpr bool A_MN = (MODE == TC_WGRAD);
   constexpr bool B_MN = (MODE == TC_WGRAD) || !B_KMAJOR;
   constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
@@ -1000,7 +1062,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             } else {
 #pragma unroll
               for (int i = 0; i < 2; ++i)
-                tma2_load_3d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, kb * kBK, slot);
+                tma2_load_3d(sb + i * kBoxBytes, &tmap_b, bar, nh + 64 * i, kb * kBK, slot);
             }
             ++issued;
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -1008,19 +1070,19 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         } else {
           for (int t = w.t0; t < w.t1 && ok; ++t) {      // K stops at each tile's valid rows
             const int trow = p.tile_row0[t];
-            const int halves = p.tile_rows[t] > kBK ? 2 : 1;
+            const int halves = (p.tile_rows[t] + KR - 1) / KR;
             for (int hf = 0; hf < halves; ++hf) {
               if (!(ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 11))) break;
               const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
               const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
-              const int row = trow + hf * kBK;
+              const int row = trow + hf * KR;
               if (leader) mbar_expect_tx(full0 + 8 * stage, tx);
 #pragma unroll
               for (int i = 0; i < 2; ++i)
-                tma2_load_2d(sa + i * 8192, &tmap_a, bar, w.row0[rank] + 64 * i, row);
+                tma2_load_2d(sa + i * kBoxBytes, &tmap_a, bar, w.row0[rank] + 64 * i, row);
 #pragma unroll
               for (int i = 0; i < 2; ++i)
-                tma2_load_2d(sb + i * 8192, &tmap_b, bar, nh + 64 * i, row);
+                tma2_load_2d(sb + i * kBoxBytes, &tmap_b, bar, nh + 64 * i, row);
               ++issued;
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -1049,11 +1111,11 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
 #pragma unroll
-          for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
+          for (int ks = 0; ks < KR / kUmmaK; ++ks) {
             if (ks < ksteps) {
-              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), 8192, 1024)
+              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024)
                                        : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
-              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), 8192, 1024)
+              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024)
                                        : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
               tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
             }
@@ -1068,10 +1130,10 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           bool first = true;
           for (int t = w.t0; t < w.t1; ++t) {
             const int v = p.tile_rows[t];
-            const int halves = v > kBK ? 2 : 1;
+            const int halves = (v + KR - 1) / KR;
             for (int hf = 0; hf < halves; ++hf) {
-              const int left = v - hf * kBK;
-              issue_stage(left >= kBK ? kBK / kUmmaK : (left + kUmmaK - 1) / kUmmaK, first);
+              const int left = v - hf * KR;
+              issue_stage(left >= KR ? KR / kUmmaK : (left + kUmmaK - 1) / kUmmaK, first);
               first = false;
             }
           }
@@ -1247,8 +1309,9 @@ bool tc_supported(int M, int F) { return M % 128 == 0 && F % 128 == 0 && M >= 12
 template <int MODE, bool B_KMAJOR, int BN, int EV>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_items,
                      cudaStream_t st) {
-  constexpr int STAGES = BN == 256 ? 4 : 6;
-  constexpr size_t smem = (size_t)STAGES * (kABytes + BN * kBK * 2) + 1024;
+  constexpr int KR = MODE == TC_WGRAD ? kWBK : kBK;
+  constexpr int STAGES = (BN == 256 ? 4 : 6) * (kBK / KR);      // the same bytes in flight either way
+  constexpr size_t smem = (size_t)STAGES * (kBM * KR * 2 + BN * KR * 2) + 1024;
   auto kern = tc_gemm_kernel<MODE, B_KMAJOR, BN, STAGES, EV>;
   static PerDeviceInt configured;          // the attribute belongs to a device
   const int dev = current_device();
@@ -1270,8 +1333,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
 template <int MODE, bool B_KMAJOR, int EV>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int max_items,
                       cudaStream_t st) {
-  constexpr int STAGES = 6;
-  constexpr size_t smem = (size_t)STAGES * kStage2Bytes + 1024;
+  constexpr int KR = MODE == TC_WGRAD ? kWBK : kBK;
+  constexpr int STAGES = 6 * (kBK / KR);
+  constexpr size_t smem = (size_t)STAGES * Pair2<KR>::kStageBytes + 1024;
   auto kern = tc2_gemm_kernel<MODE, B_KMAJOR, STAGES, EV>;
   static PerDeviceInt max_clusters_of;     // attribute and occupancy belong to a device
   const int dev = current_device();
@@ -1358,12 +1422,16 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   p.peer_L = a.peers.L;
   p.peer_Cs = a.peer_Cs;
   for (int q = 0; q < kMaxPeers; ++q) p.peer_base[q] = a.peers.base[q];
+  p.c_perm = a.c_perm; p.c_offsets = a.c_offsets; p.c_counts = a.c_counts; p.c_gates = a.c_gates;
+  p.c_y = static_cast<__nv_bfloat16*>(a.c_y); p.c_k = a.c_k; p.c_Cs = a.c_Cs;
   MOLE_REQUIRE(a.peers.n == 0 || a.rowmap != nullptr, "peer scatter needs the row map");
   MOLE_REQUIRE(a.rowmap == nullptr || a.epi == EPI_BIAS || a.epi == EPI_STORE,
                "only FC2 / dX outputs can be scattered");
   const int max_items = a.sched.max_tiles * (a.N / BN);
   for (const void* q : {a.bias, a.aux, (const void*)a.out0, (const void*)a.out1})
     MOLE_REQUIRE((reinterpret_cast<uintptr_t>(q) & 31) == 0, "epilogue operand %p not 32-byte aligned", q);
+  MOLE_REQUIRE(a.c_y == nullptr || (!pair && a.rowmap == nullptr && (a.epi == EPI_BIAS || a.epi == EPI_STORE)),
+               "the fused combine needs the one-CTA kernel and rows that are not scattered");
   // one kernel per (operand layout, tile shape, epilogue variant)
 #define MOLE_ROWS(KM, EV)                                                                    \
   return pair ? launch_tc2<TC_ROWS, KM, EV>(ma, mb, p, max_items, st)                        \
@@ -1393,7 +1461,7 @@ int tc_wgrad(const WgradArgs& a, cudaStream_t st) {
   if (a.n_experts <= 0) return MOLE_OK;
   const int BN = a.Q % 256 == 0 ? 256 : 128;
   CUtensorMap ma, mb;
-  const uint32_t box[2] = {64, kBK};
+  const uint32_t box[2] = {64, kWBK};
   {
     const uint64_t dims[2] = {(uint64_t)a.P, (uint64_t)a.total_rows};
     if (int rc = make_map(&ma, a.A, 2, dims, box)) return rc;

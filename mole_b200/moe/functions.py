@@ -85,10 +85,12 @@ class Dispatch(torch.autograd.Function):
 
 class Combine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, rows, gates, plan, peer=None):
+    def forward(ctx, rows, gates, plan, peer=None, fused_y=None):
         ctx.plan = plan
         ctx.peer = peer
         ctx.save_for_backward(rows, gates)
+        if fused_y is not None:        # already produced by the expert pipeline's last epilogue
+            return fused_y
         return ops.combine(rows, plan, gates)
 
     @staticmethod
@@ -96,9 +98,9 @@ class Combine(torch.autograd.Function):
         rows, gates = ctx.saved_tensors
         if ctx.peer is not None:        # row gradients go straight to the experts' owners
             dgates = ops.combine_bwd_peer(dy.contiguous(), rows, ctx.plan, gates, ctx.peer)
-            return dy.new_zeros(1).expand_as(rows), dgates, None, None
+            return dy.new_zeros(1).expand_as(rows), dgates, None, None, None
         drows, dgates = ops.combine_bwd(dy.contiguous(), rows, ctx.plan, gates)
-        return drows, dgates, None, None
+        return drows, dgates, None, None, None
 
 
 class BatchFusedFWD(torch.autograd.Function):
@@ -131,7 +133,15 @@ class BatchFusedFWD(torch.autograd.Function):
         if ctx.peer is not None:
             out = core.forward_peer(ctx.peer, True)
         else:
-            out = core.forward(dispatched_input.contiguous(), counts, True)
+            # the layer may ask for the combine to be fused into the second GEMM's epilogue
+            fuse = getattr(module, "_fuse", None)
+            combine = None
+            if fuse is not None:
+                plan, gates = fuse["plan"], fuse["gates"]
+                y = torch.zeros(plan.T, M, dtype=dispatched_input.dtype, device=dispatched_input.device)
+                fuse["y"] = y
+                combine = (plan, gates.detach(), y)
+            out = core.forward(dispatched_input.contiguous(), counts, True, combine=combine)
         if timer:
             timer.stop_fwd()
         if time_it:

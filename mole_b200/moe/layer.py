@@ -42,12 +42,17 @@ class MOLEModule(torch.nn.Module):
                  ebatch_size, dist, act, acc_step, adv_adam, use_pool,
                  pool_for_extra=[False, False, False], overlap=True, gate_control_by_umoe=True,
                  hybrid_adam=False, device_s_experts=-1, *, dtype=torch.float32,
-                 normalize_gate=False, gelu_bwd="exact", ffn_backend=0):
+                 normalize_gate=False, gelu_bwd="exact", ffn_backend=0, fuse_combine=None):
         super().__init__()
         self.acc_step = acc_step
         self.topk = topk
         self.dtype = dtype
         self.normalize_gate = normalize_gate
+        # True: the gate-weighted combine runs inside the second GEMM's epilogue (one rank, bf16,
+        # top-1 / top-2; an error where that is not possible).  None / False: the separate combine
+        # kernel -- measured equally fast on the benchmark shape, and it sums a token's rows in
+        # fp32 before the one rounding, as the reference's decode does.
+        self.fuse_combine = fuse_combine
 
         self.local_rank = dist["local_rank"]
         self.world_size = dist["world_size"]
@@ -256,13 +261,21 @@ class MOLEModule(torch.nn.Module):
 
         self._route_counts = plan.counts
         self._peer_exchange = peer
+        # the combine as part of the second GEMM's epilogue where that is possible
+        can_fuse = peer is None and self.MOLECore.can_fuse_combine(plan, self.embed_dim)
+        if self.fuse_combine and not can_fuse:
+            raise RuntimeError("fuse_combine=True needs one rank, bf16, top-1/top-2 and the default FFN backend")
+        fuse = {"plan": plan, "gates": gates} if (can_fuse and self.fuse_combine) else None
+        self._fuse = fuse
         experts_output = BatchFusedFWD.apply(dispatched_input, self, self.dummy_param, time_it, prefetch)
         self._route_counts = None
         self._peer_exchange = None
+        self._fuse = None
         if self.parity_tap is not None:
             self.parity_tap["rows"] = experts_output
 
-        expert_output = Combine.apply(experts_output, gates, plan, peer)
+        expert_output = Combine.apply(experts_output, gates, plan, peer,
+                                      fuse["y"] if fuse is not None else None)
         out = expert_output.reshape(original_shape).to(original_dtype)
 
         if prefetch:

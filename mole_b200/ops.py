@@ -228,6 +228,16 @@ def ffn_fwd(desc: FfnDesc, counts, x, w1, b1, w2, b2, x1, h, out, ws,
                            _ptr(out), _ptr(ws), ws.numel(), _stream()))
 
 
+def ffn_fwd_combine(desc: FfnDesc, counts, x, w1, b1, w2, b2, x1, h, out, plan: RoutePlan, gates, y,
+                    ws, slot_of_expert: Optional[Sequence[int]] = None) -> None:
+    """``ffn_fwd`` whose second GEMM also adds ``gates * out_row`` into ``y[token]`` (``y`` zeroed
+    by the caller): the combine fused into the W2 epilogue."""
+    check(lib.mole_ffn_fwd_combine(C.byref(desc), _ptr(counts), _slot_array(slot_of_expert, desc.L),
+                                   _ptr(x), _ptr(w1), _ptr(b1), _ptr(w2), _ptr(b2), _ptr(x1), _ptr(h),
+                                   _ptr(out), _ptr(plan.offsets), _ptr(plan.perm), _ptr(gates), plan.k,
+                                   _ptr(y), _ptr(ws), ws.numel(), _stream()))
+
+
 def ffn_bwd(desc: FfnDesc, counts, dout, x, x1, h, w1, w2, dx1, dx, gw1, gb1, gw2, gb2, ws,
             slot_of_expert: Optional[Sequence[int]] = None,
             grad_slot_of_expert: Optional[Sequence[int]] = None) -> None:
