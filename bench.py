@@ -451,6 +451,7 @@ def parity_check(m, cfg, x, gy, y, world, rank, device, dtype):
             continue
         l = e - rank * L
         X, DO, OUT, DX = [], [], [], []
+        packed_base = 0
         for w in range(world):
             sel = (idxs[w] == e) & (slots[w] < Cap)
             tok, j = sel.nonzero(as_tuple=True)
@@ -463,7 +464,11 @@ def parity_check(m, cfg, x, gy, y, world, rank, device, dtype):
             assert n == tok.numel()
             OUT.append(all_rows[w][si, :n].float().cpu())
             DX.append(all_dx[w][si, :n].float().cpu())
-            if peer is not None:
+            if peer is not None and peer.packed:      # one run per expert, sources in rank order
+                run = peer.x0.view(L, world * Cs, M)[l]
+                x0_exact = x0_exact and torch.equal(run[packed_base:packed_base + n], xr)
+                packed_base += n
+            elif peer is not None:
                 x0_exact = x0_exact and torch.equal(peer.x0[w, l, :n], xr)
         X, DO, OUT, DX = (torch.cat(t) for t in (X, DO, OUT, DX))
         w1, b1, w2, b2 = (p.fetch_single(l).float().cpu()

@@ -166,17 +166,28 @@ int mole_combine_bwd(const void* dy, const void* rows, const float* gates,
  * rank q's buffer [W, L, Cs, M] mapped into this process, peer_counts[q] its int32 [W * L] count
  * array; row (e, s) of this rank lands in chunk (rank, e % L) of rank e / L.  No pad rows are
  * written: the receiver packs rows by count.  Replaces fast_encode + _BatchRecord::first_a2a
- * (MOLE/moe/layer.py:448-449, MOLE/cpp/core.cpp:144-179) and the backward mirror. */
+ * (MOLE/moe/layer.py:448-449, MOLE/cpp/core.cpp:144-179) and the backward mirror.
+ *
+ * Packed form (all_counts != NULL): all_counts is this rank's copy of every rank's counts,
+ * int32 [W][E] (mole_peer_put_i32 + a barrier distribute it before the call).  The receive buffer
+ * is then [L][W * Cs][M], one run per local expert, and the sender puts its rows straight at
+ * their final place in the run, behind the rows of the lower ranks: the receiver has nothing to
+ * gather (mole_ffn_*_peer with desc.compact = 3).  peer_counts is not used in this form. */
 int mole_dispatch_fwd_peer(const void* x, const int32_t* counts, const int32_t* offsets,
                            const int32_t* perm, int64_t T, int32_t M, int32_t E, int32_t k,
                            int32_t Cs, int32_t dtype, void* const* peer_rows,
-                           int32_t* const* peer_counts, int32_t n_peers, int32_t rank,
-                           void* stream);
+                           int32_t* const* peer_counts, const int32_t* all_counts,
+                           int32_t n_peers, int32_t rank, void* stream);
 int mole_combine_bwd_peer(const void* dy, const void* rows, const float* gates,
                           const int32_t* counts, const int32_t* offsets, const int32_t* perm,
                           int64_t T, int32_t M, int32_t E, int32_t k, int32_t Cs, int32_t dtype,
-                          void* const* peer_rows, int32_t n_peers, int32_t rank, float* dgates,
-                          void* stream);
+                          void* const* peer_rows, const int32_t* all_counts, int32_t n_peers,
+                          int32_t rank, float* dgates, void* stream);
+/* src[0..n) of this rank into slot `rank` of every rank's int32 [world][n] table (peer_tables[q]
+ * = rank q's table mapped into this process, this rank's own for q == rank).  Used to tell every
+ * rank every rank's per-expert row counts; follow it with a barrier before reading the table. */
+int mole_peer_put_i32(const int32_t* src, int32_t n, void* const* peer_tables, int32_t world,
+                      int32_t rank, void* stream);
 /* backward of dispatch fused with the gate's input gradient:
  * dx[t] = sum_j kept * ddisp[idx*Cs + slot] + dlogits[t,:] @ wg
  * (ddisp may be NULL: gate term only; dlogits and wg may both be NULL: dispatch term only) */
@@ -215,7 +226,11 @@ typedef struct {
   int32_t accumulate;     /* backward: weight grads += instead of = (core.cpp:457-514) */
   int32_t compact;        /* 0: with n_src > 1 the tensor-core path packs each expert's rows of all
                              sources into one run before the GEMMs (x1, h, dx1 are then in that
-                             layout); 2: never pack */
+                             layout); 2: never pack; 3: x and dout already ARE packed,
+                             [L][n_src * Cs][M] with expert l's rows of all sources in source order
+                             at the front of its run (the packed form of mole_dispatch_fwd_peer /
+                             mole_combine_bwd_peer): nothing is gathered, the call writes the pad
+                             rows of x (forward) and dout (backward) in place */
   int32_t backend;        /* 0: tensor cores for bf16 (CTA pairs, cta_group::2, where the shape
                              allows), CUDA cores for fp32 (the fp32 layer needs fp32-exact
                              products); 1: CUDA-core kernels also for bf16, used to bisect

@@ -86,9 +86,10 @@ SIGNATURES = {
     "mole_ffn_bwd_peer": (C.c_int, [C.POINTER(FfnDesc), _p, _pi32, _pi32, _p, _p, _p, _p, _p, _p, _p,
                                     C.POINTER(_p), _i32, _p, _p, _p, _p, _p, _i64, _p]),
     "mole_dispatch_fwd_peer": (C.c_int, [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32,
-                                         C.POINTER(_p), C.POINTER(_p), _i32, _i32, _p]),
+                                         C.POINTER(_p), C.POINTER(_p), _p, _i32, _i32, _p]),
     "mole_combine_bwd_peer": (C.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32,
-                                        C.POINTER(_p), _i32, _i32, _p, _p]),
+                                        C.POINTER(_p), _p, _i32, _i32, _p, _p]),
+    "mole_peer_put_i32": (C.c_int, [_p, _i32, C.POINTER(_p), _i32, _i32, _p]),
     "mole_peer_alloc": (C.c_int, [_i64, C.POINTER(_p)]),
     "mole_peer_free": (C.c_int, [_p]),
     "mole_peer_export": (C.c_int, [_p, C.POINTER(C.c_uint8)]),

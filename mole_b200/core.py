@@ -189,7 +189,7 @@ class PeerExchange:
     (``mole_barrier``): every reader of a buffer has finished before the barrier that precedes
     its next writer, see ``MOLECore.forward_peer`` / ``backward_peer``."""
 
-    KINDS = ("x0", "ret", "g", "dx", "counts", "flags")
+    KINDS = ("x0", "ret", "g", "dx", "counts", "flags", "allcounts")
     BARRIER_LIMIT_NS = 2_000_000_000      # a rank that never arrives costs its peers two seconds
 
     def __init__(self, world, rank, L, Cs, M, dtype, device, group):
@@ -201,7 +201,8 @@ class PeerExchange:
         es = torch.empty(0, dtype=dtype).element_size()
         row_bytes = world * L * Cs * M * es
         sizes = {"x0": row_bytes, "ret": row_bytes, "g": row_bytes, "dx": row_bytes,
-                 "counts": max(256, world * L * 4), "flags": 256}
+                 "counts": max(256, world * L * 4), "flags": 256,
+                 "allcounts": max(256, world * world * L * 4)}
         self.sizes = sizes
         # Every rank takes the same decision: each phase ends in a collective that carries the
         # ranks' success flags, and one failure anywhere makes all of them give the buffers up
@@ -254,6 +255,10 @@ class PeerExchange:
         self.barrier_seq = 0     # flag barriers taken so far (the same number on every rank)
         import os
         self.flag_barrier = os.environ.get("MOLE_FLAG_BARRIER", "1") != "0"
+        # packed: every rank first learns every rank's counts, then stores its rows at their
+        # final place in the owner's per-expert run; the owner gathers nothing
+        # (MOLE_PACKED_PUSH=0: chunks per source rank, packed by the owner before its GEMMs)
+        self.packed = os.environ.get("MOLE_PACKED_PUSH", "1") != "0"
         self.serial = 0          # forward passes so far: backward checks that its buffers are still its own
         dist.barrier(group=group)
 
@@ -275,8 +280,10 @@ class PeerExchange:
 
         E = world * L
         self.Cs = Cs
+        # chunks [W][L][Cs] or, packed, one run per local expert [L][W * Cs]: the same memory
         self.x0 = view("x0", dtype, (world, L, Cs, M))
         self.g = view("g", dtype, (world, L, Cs, M))
+        self.allcounts = view("allcounts", torch.int32, (world, world * L))
         self.ret = view("ret", dtype, (E, Cs, M))
         self.dx = view("dx", dtype, (E, Cs, M))
         self.counts = view("counts", torch.int32, (world * L,))
@@ -307,7 +314,7 @@ class PeerExchange:
         for p in self.own.values():
             lib.mole_peer_free(C.c_void_p(p))
         self.own = {}
-        for name in ("x0", "g", "ret", "dx", "counts"):
+        for name in ("x0", "g", "ret", "dx", "counts", "allcounts"):
             self.__dict__.pop(name, None)
 
     def __del__(self):
@@ -563,13 +570,17 @@ class MOLECore:
         x1 = torch.empty(rows_total, F, dtype=self.dtype, device=peer.x0.device)
         h = torch.empty(rows_total, F, dtype=self.dtype, device=peer.x0.device)
         w1, b1, w2, b2, slots, n_slots = self._weights(rec)
-        desc = self._desc(M, F, W, Cs, rec, n_slots)
+        if peer.packed:       # rows are where the GEMMs want them; counts of my experts from the table
+            rcounts = peer.allcounts[:, peer.rank * L:(peer.rank + 1) * L].contiguous().view(-1)
+        else:
+            rcounts = peer.counts
+        desc = self._desc(M, F, W, Cs, rec, n_slots, compact=3 if peer.packed else 0)
         ws = ops.ffn_workspace(desc, peer.x0.device)
-        ops.ffn_fwd_peer(desc, peer.counts, peer.x0, w1, b1, w2, b2, x1, h, peer, ws, slots)
+        ops.ffn_fwd_peer(desc, rcounts, peer.x0, w1, b1, w2, b2, x1, h, peer, ws, slots)
         peer.barrier()                      # every owner's output rows have landed in my ret
         if requires_grad:
             s = _Saved()
-            s.x0, s.x1, s.h, s.counts, s.Cs, s.n_src = peer.x0, x1, h, peer.counts, Cs, W
+            s.x0, s.x1, s.h, s.counts, s.Cs, s.n_src = peer.x0, x1, h, rcounts, Cs, W
             s.serial = peer.serial
             self._saved = s
         return peer.ret
@@ -592,7 +603,8 @@ class MOLECore:
         dx1 = torch.empty(W * L * Cs, F, dtype=self.dtype, device=peer.g.device)
         accumulate = self._accumulate()
         w1, _, w2, _, slots, n_slots = self._weights(rec)
-        desc = self._desc(M, F, W, Cs, rec, n_slots, accumulate, self.s_experts)
+        desc = self._desc(M, F, W, Cs, rec, n_slots, accumulate, self.s_experts,
+                          compact=3 if peer.packed else 0)
         ws = ops.ffn_workspace(desc, peer.g.device)
         grads = self.gpu_grads
         ops.ffn_bwd_peer(desc, s.counts, peer.g, s.x0, s.x1, s.h, w1, w2, dx1, peer, grads[0],
@@ -621,11 +633,12 @@ class MOLECore:
                 f"a grouped-GEMM kernel gave up on a bounded wait (fault code {code}): the results "
                 "of that step are invalid")
 
-    def _desc(self, M, F, n_src, Cs, rec: Record, n_slots, accumulate=False, n_grad_slots=0):
+    def _desc(self, M, F, n_src, Cs, rec: Record, n_slots, accumulate=False, n_grad_slots=0,
+              compact=0):
         L = self.s_experts + self.d_experts
         return ops.make_ffn_desc(self.dtype, self.act_name, self.gelu_bwd, M, F, L, n_src, Cs,
                                  rec.base_in_all, rec.base_in_all + rec.batch_size, n_slots,
-                                 accumulate, self.ffn_backend, n_grad_slots)
+                                 accumulate, self.ffn_backend, n_grad_slots, compact)
 
     def _weights(self, rec: Record):
         """(w1, b1, w2, b2, slot map, n_slots) for a record."""

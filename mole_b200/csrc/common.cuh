@@ -163,10 +163,21 @@ struct PeerMap {
   int32_t* counts[kMaxPeers];     // rank q's [W * L] valid-row counts (dispatch only), or null
   int n;                          // ranks; 0: no peers, rows stay local
   int rank, L;
+  // Packed layout: when every rank knows every rank's counts ([W][E] table, local copy here), a
+  // sender puts its rows straight at their final place in the owner's per-expert run
+  // [L][W * Cs]: behind the rows of the lower ranks.  Null: chunk layout [W][L][Cs].
+  const int32_t* all_counts;
+  int E;
 };
 __device__ __forceinline__ int64_t peer_row(const PeerMap& pm, int e, int s, int Cs, int* owner) {
   *owner = e / pm.L;
-  return ((int64_t)pm.rank * pm.L + (e - *owner * pm.L)) * Cs + s;
+  const int l = e - *owner * pm.L;
+  if (pm.all_counts != nullptr) {
+    int base = 0;
+    for (int w = 0; w < pm.rank; ++w) base += min(pm.all_counts[w * pm.E + e], Cs);
+    return (int64_t)l * pm.n * Cs + base + s;
+  }
+  return ((int64_t)pm.rank * pm.L + l) * Cs + s;
 }
 
 struct Schedule {

@@ -33,7 +33,7 @@ dispatch_fwd_kernel(const T* __restrict__ x, const int32_t* __restrict__ counts,
     // there), and the count itself
     int owner;
     const int64_t prow = peer_row(pm, e, s, Cs, &owner);
-    if (s == 0 && lane == 0) pm.counts[owner][prow / Cs] = cnt;
+    if (pm.all_counts == nullptr && s == 0 && lane == 0) pm.counts[owner][prow / Cs] = cnt;
     if (s >= cnt) return;
     dst = reinterpret_cast<uint4*>(static_cast<T*>(pm.base[owner]) + prow * M);
   } else {
@@ -311,7 +311,7 @@ extern "C" int mole_dispatch_fwd(const void* x, const int32_t* counts, const int
 }
 
 static int fill_peer_map(PeerMap& pm, void* const* rows, int32_t* const* counts, int n_peers,
-                         int rank, int E) {
+                         int rank, int E, const int32_t* all_counts = nullptr) {
   MOLE_REQUIRE(rows != nullptr, "null peer table");
   MOLE_REQUIRE(n_peers >= 2 && n_peers <= kMaxPeers, "peer count %d not in [2, %d]", n_peers, kMaxPeers);
   MOLE_REQUIRE(rank >= 0 && rank < n_peers, "rank %d outside the %d peers", rank, n_peers);
@@ -328,18 +328,45 @@ static int fill_peer_map(PeerMap& pm, void* const* rows, int32_t* const* counts,
   pm.n = n_peers;
   pm.rank = rank;
   pm.L = E / n_peers;
+  pm.all_counts = all_counts;
+  pm.E = E;
+  return MOLE_OK;
+}
+
+// n int32 values of this rank into slot `rank` of every rank's table (peer_tables[q] is rank q's
+// [world][n] table mapped into this process): how the ranks tell each other their per-expert row
+// counts before a packed dispatch.  One block per destination, plain stores over NVLink.
+__global__ void peer_put_kernel(const int32_t* __restrict__ src, int n, const __grid_constant__ PeerMap pm) {
+  int32_t* dst = static_cast<int32_t*>(pm.base[blockIdx.x]) + (int64_t)pm.rank * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int mole_peer_put_i32(const int32_t* src, int32_t n, void* const* peer_tables,
+                                 int32_t world, int32_t rank, void* stream) {
+  MOLE_REQUIRE(src && peer_tables && n >= 1, "bad argument");
+  MOLE_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "rank %d / world %d", rank, world);
+  PeerMap pm{};
+  for (int q = 0; q < world; ++q) {
+    MOLE_REQUIRE(peer_tables[q] != nullptr, "null table of rank %d", q);
+    pm.base[q] = peer_tables[q];
+  }
+  pm.n = world;
+  pm.rank = rank;
+  peer_put_kernel<<<world, 256, 0, static_cast<cudaStream_t>(stream)>>>(src, n, pm);
+  MOLE_LAUNCH_OK();
   return MOLE_OK;
 }
 
 extern "C" int mole_dispatch_fwd_peer(const void* x, const int32_t* counts, const int32_t* offsets,
                                       const int32_t* perm, int64_t T_, int32_t M, int32_t E,
                                       int32_t k, int32_t Cs, int32_t dtype, void* const* peer_rows,
-                                      int32_t* const* peer_counts, int32_t n_peers, int32_t rank,
-                                      void* stream) {
+                                      int32_t* const* peer_counts, const int32_t* all_counts,
+                                      int32_t n_peers, int32_t rank, void* stream) {
   if (int rc = check_rows(T_, M, E, k, Cs, dtype)) return rc;
-  MOLE_REQUIRE(x && counts && offsets && perm && peer_counts, "null pointer argument");
+  MOLE_REQUIRE(x && counts && offsets && perm && (peer_counts || all_counts), "null pointer argument");
   PeerMap pm;
-  if (int rc = fill_peer_map(pm, peer_rows, peer_counts, n_peers, rank, E)) return rc;
+  if (int rc = fill_peer_map(pm, peer_rows, all_counts ? nullptr : peer_counts, n_peers, rank, E, all_counts))
+    return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)(((int64_t)E * Cs + kRowWarps - 1) / kRowWarps);
   MOLE_BY_DTYPE(dtype, dispatch_fwd_kernel<T><<<grid, kRowWarps * 32, 0, st>>>(
@@ -384,11 +411,12 @@ extern "C" int mole_combine_bwd_peer(const void* dy, const void* rows, const flo
                                      const int32_t* counts, const int32_t* offsets,
                                      const int32_t* perm, int64_t T_, int32_t M, int32_t E,
                                      int32_t k, int32_t Cs, int32_t dtype, void* const* peer_rows,
-                                     int32_t n_peers, int32_t rank, float* dgates, void* stream) {
+                                     const int32_t* all_counts, int32_t n_peers, int32_t rank,
+                                     float* dgates, void* stream) {
   if (int rc = check_rows(T_, M, E, k, Cs, dtype)) return rc;
   MOLE_REQUIRE(dy && rows && gates && counts && offsets && perm && dgates, "null pointer argument");
   PeerMap pm;
-  if (int rc = fill_peer_map(pm, peer_rows, nullptr, n_peers, rank, E)) return rc;
+  if (int rc = fill_peer_map(pm, peer_rows, nullptr, n_peers, rank, E, all_counts)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MOLE_CUDA_OK(cudaMemsetAsync(dgates, 0, (size_t)T_ * k * 4, st));
   const unsigned grid = (unsigned)(((int64_t)E * Cs + kRowWarps - 1) / kRowWarps);

@@ -56,6 +56,10 @@ static int single_cta(const mole_ffn_desc* d) {
 // layout, FC2 / dX scatter their output rows back to the (source, expert) chunks.  `desc.compact`
 // = 2 switches it off (comparisons).
 static bool compacting(const mole_ffn_desc* d) { return use_tc(d) && d->n_src > 1 && d->compact != 2; }
+// compact == 3: the caller's row buffers (x, dout) already are in the packed layout -- the senders
+// of the push-style exchange put every row at its final place -- so nothing is gathered: the
+// call only builds the row map and zeroes the pad rows of those buffers, in place.
+static bool prepacked(const mole_ffn_desc* d) { return compacting(d) && d->compact == 3; }
 
 struct Workspace {
   Schedule sched;
@@ -68,7 +72,8 @@ static int64_t workspace_bytes_of(const mole_ffn_desc* d) {
   int64_t b = align256(schedule_bytes(d->L, d->n_src, d->Cs));
   if (compacting(d)) {
     const int64_t rows = (int64_t)d->L * d->n_src * d->Cs;
-    b += align256(rows * 4) + 2 * align256(rows * d->M * 2);
+    b += align256(rows * 4);
+    if (!prepacked(d)) b += 2 * align256(rows * d->M * 2);
   }
   return b;
 }
@@ -194,9 +199,14 @@ static int ffn_fwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   const bool compact = compacting(d);
   if (compact) {
     if (int rc = build_schedule_compact(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
-    if (int rc = compact_gather(d->dtype, x, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, d->M,
-                                wk.buf_a, wk.rowmap, st)) return rc;
-    x = wk.buf_a;
+    if (prepacked(d)) {
+      if (int rc = compact_gather(d->dtype, nullptr, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end,
+                                  d->M, const_cast<void*>(x), wk.rowmap, st)) return rc;
+    } else {
+      if (int rc = compact_gather(d->dtype, x, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, d->M,
+                                  wk.buf_a, wk.rowmap, st)) return rc;
+      x = wk.buf_a;
+    }
   } else {
     if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
   }
@@ -276,12 +286,17 @@ static int ffn_bwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   const bool compact = compacting(d);
   if (compact) {      // x1, h come compacted from forward; x and dout are packed the same way here
     if (int rc = build_schedule_compact(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
-    if (int rc = compact_gather(d->dtype, x, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, d->M,
-                                wk.buf_a, wk.rowmap, st)) return rc;
-    if (int rc = compact_gather(d->dtype, dout, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end,
-                                d->M, wk.buf_b, nullptr, st)) return rc;
-    x = wk.buf_a;
-    dout = wk.buf_b;
+    if (prepacked(d)) {      // x was prepared by forward; dout's pad rows are zeroed here
+      if (int rc = compact_gather(d->dtype, nullptr, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end,
+                                  d->M, const_cast<void*>(dout), wk.rowmap, st)) return rc;
+    } else {
+      if (int rc = compact_gather(d->dtype, x, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, d->M,
+                                  wk.buf_a, wk.rowmap, st)) return rc;
+      if (int rc = compact_gather(d->dtype, dout, counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end,
+                                  d->M, wk.buf_b, nullptr, st)) return rc;
+      x = wk.buf_a;
+      dout = wk.buf_b;
+    }
   } else {
     if (int rc = build_schedule(counts, d->L, d->n_src, d->Cs, d->e_begin, d->e_end, s, st)) return rc;
   }

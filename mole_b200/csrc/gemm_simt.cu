@@ -126,7 +126,9 @@ schedule_compact_kernel(const int32_t* __restrict__ counts, int L, int n_src, in
 }
 
 // One warp per row of the compacted layout: finds the (source, slot) the row comes from, records
-// it in rowmap (when given) and copies the row; pad rows are zeroed and mapped to -1.
+// it in rowmap (when given) and copies the row; pad rows are zeroed and mapped to -1.  With
+// src == nullptr the rows are already where they belong (the senders packed them): only the row
+// map is written and the pad rows are zeroed.
 template <typename T>
 __global__ void __launch_bounds__(256)
 compact_gather_kernel(const T* __restrict__ src, const int32_t* __restrict__ counts, int L,
@@ -156,7 +158,7 @@ compact_gather_kernel(const T* __restrict__ src, const int32_t* __restrict__ cou
   const int nvec = width / Vec16<T>::N;
   if (srow < 0) {
     for (int i = lane; i < nvec; i += 32) d4[i] = make_uint4(0, 0, 0, 0);
-  } else {
+  } else if (src != nullptr) {
     const uint4* s4 = reinterpret_cast<const uint4*>(src + srow * width);
     for (int i = lane; i < nvec; i += 32) d4[i] = __ldg(s4 + i);
   }

@@ -252,9 +252,18 @@ def dispatch_peer(x: torch.Tensor, plan: RoutePlan, peer) -> None:
     """Dispatch whose rows (and per-expert counts) land in the receive buffers of the experts'
     owners; ``peer`` is a ``core.PeerExchange``."""
     T, M = x.shape
+    all_counts = None
+    if peer.packed:
+        # every rank learns every rank's counts first, so that rows can go straight to their final
+        # place in the owner's per-expert run
+        check(lib.mole_peer_put_i32(_ptr(plan.counts), plan.E, peer.table["allcounts"], peer.world,
+                                    peer.rank, _stream()))
+        peer.barrier()
+        all_counts = peer.allcounts
     check(lib.mole_dispatch_fwd_peer(_ptr(x), _ptr(plan.counts), _ptr(plan.offsets), _ptr(plan.perm),
                                      T, M, plan.E, plan.k, plan.Cs, _dt(x), peer.table["x0"],
-                                     peer.table["counts"], peer.world, peer.rank, _stream()))
+                                     peer.table["counts"], _ptr(all_counts), peer.world, peer.rank,
+                                     _stream()))
 
 
 def combine_bwd_peer(dy: torch.Tensor, rows: torch.Tensor, plan: RoutePlan, gates: torch.Tensor,
@@ -264,8 +273,9 @@ def combine_bwd_peer(dy: torch.Tensor, rows: torch.Tensor, plan: RoutePlan, gate
     dgates = torch.empty(plan.T, plan.k, dtype=torch.float32, device=rows.device)
     check(lib.mole_combine_bwd_peer(_ptr(dy), _ptr(rows), _ptr(gates), _ptr(plan.counts),
                                     _ptr(plan.offsets), _ptr(plan.perm), plan.T, M, plan.E, plan.k,
-                                    plan.Cs, _dt(rows), peer.table["g"], peer.world, peer.rank,
-                                    _ptr(dgates), _stream()))
+                                    plan.Cs, _dt(rows), peer.table["g"],
+                                    _ptr(peer.allcounts) if peer.packed else None, peer.world,
+                                    peer.rank, _ptr(dgates), _stream()))
     return dgates
 
 

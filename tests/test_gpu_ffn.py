@@ -256,3 +256,53 @@ def test_ffn_bf16_config3_shape_spot_check():
         assert_close(case.expert_rows(dx, l), dx_ref, case.dtype, f"dx {l}")
         for got, ref in zip(grads, g_ref):
             assert_close(got[l], ref, case.dtype, f"grad {l}")
+
+
+@pytest.mark.parametrize("backend", [2, 3])
+def test_ffn_bf16_rows_packed_by_the_senders(backend):
+    """``desc.compact = 3``: x and dout arrive already packed -- expert l's rows of all four source
+    ranks in source order at the front of its run ``[l][n_src * Cs]``, pad rows holding garbage --
+    as the packed form of the push-style dispatch leaves them.  The call gathers nothing, zeroes
+    the pad rows in place and scatters out / dx back to the (source, expert) chunks; results must
+    equal the same call on chunked inputs bit for bit (same packed layout inside) and the oracle."""
+    from mole_b200 import ops
+    counts = [100, 0, 256, 1, 7, 128,
+              30, 0, 129, 0, 250, 128,
+              0, 0, 5, 200, 255, 128,
+              127, 0, 1, 56, 3, 128]            # [n_src=4][L=6]
+    case = Case(M=256, F=512, L=6, n_src=4, Cs=256, counts=counts, dtype=torch.bfloat16, seed=7)
+    out_c, dx_c, grads_c = run_gpu(case, backend=backend)          # chunked inputs, packed by the call
+    c = case
+    dev = torch.device("cuda")
+    run = c.n_src * c.Cs
+    xp = torch.full((c.L, run, c.M), float("nan"), dtype=c.dtype)
+    dp = torch.full((c.L, run, c.M), float("nan"), dtype=c.dtype)
+    for l in range(c.L):
+        xp[l, :c.expert_rows(c.x, l).shape[0]] = c.expert_rows(c.x, l)
+        dp[l, :c.expert_rows(c.dout, l).shape[0]] = c.expert_rows(c.dout, l)
+    desc = ops.make_ffn_desc(c.dtype, c.act, "exact", c.M, c.F, c.L, c.n_src, c.Cs, 0, c.L, c.L,
+                             False, backend, compact=3)
+    ws = ops.ffn_workspace(desc, dev)
+    rows = c.L * run
+    x, dout = xp.view(rows, c.M).cuda(), dp.view(rows, c.M).cuda()
+    w1, b1, w2, b2 = (t.cuda() for t in (c.w1, c.b1, c.w2, c.b2))
+    nan = float("nan")
+    x1 = torch.full((rows, c.F), nan, dtype=c.dtype, device=dev)
+    h = torch.full((rows, c.F), nan, dtype=c.dtype, device=dev)
+    out = torch.full((rows, c.M), nan, dtype=c.dtype, device=dev)
+    cnt = c.counts.flatten().cuda()
+    ops.ffn_fwd(desc, cnt, x, w1, b1, w2, b2, x1, h, out, ws)
+    dx1 = torch.full((rows, c.F), nan, dtype=c.dtype, device=dev)
+    dx = torch.full((rows, c.M), nan, dtype=c.dtype, device=dev)
+    grads = [torch.full_like(t, nan) for t in (w1, b1, w2, b2)]
+    ops.ffn_bwd(desc, cnt, dout, x, x1, h, w1, w2, dx1, dx, grads[0], grads[1], grads[2], grads[3], ws)
+    assert ops.device_fault() == 0
+    torch.cuda.synchronize()
+    shape = (c.n_src, c.L, c.Cs)
+    out, dx = out.view(*shape, c.M).cpu(), dx.view(*shape, c.M).cpu()
+    for l in range(c.L):
+        assert torch.equal(c.expert_rows(out, l), c.expert_rows(out_c, l)), f"out {l}"
+        assert torch.equal(c.expert_rows(dx, l), c.expert_rows(dx_c, l)), f"dx {l}"
+    for a, b in zip(grads, grads_c):
+        assert torch.equal(a.cpu(), b)
+    check(case, out, dx, [g.cpu() for g in grads], range(c.L))
