@@ -38,7 +38,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // Second half of the gate kernel, also used on caller-provided scores.
 // ls: [kGateTok][E + 1] fp32 in shared memory holding logits (softmax_needed) or scores.
-__device__ void softmax_topk_block(float* ls, int* hist_s, int64_t tok0, int64_t T, int E, int k,
+// kPerLane = experts a lane holds (ceil(E / 32), rounded up to 1, 2, 4 or 8): the loops over a
+// lane's experts are unrolled to exactly that, not to the largest expert count the library takes.
+template <int kPerLane>
+__device__ void softmax_topk_lanes(float* ls, int* hist_s, int64_t tok0, int64_t T, int E, int k,
                                    int normalize, bool softmax_needed, float* scores,
                                    int32_t* idx, float* gates, int32_t* hist, float* me_part,
                                    int nblk) {
@@ -47,7 +50,7 @@ __device__ void softmax_topk_block(float* ls, int* hist_s, int64_t tok0, int64_t
   for (int i = tid; i < k * E; i += kGateThreads) hist_s[i] = 0;
   __syncthreads();
 
-  constexpr int kPerLane = kMaxExperts / 32;
+  static_assert(kPerLane * 32 <= kMaxExperts, "more experts per lane than the library takes");
   for (int tt = 0; tt < kGateTok / 8; ++tt) {
     const int tl = warp * (kGateTok / 8) + tt;
     const int64_t t = tok0 + tl;
@@ -128,6 +131,20 @@ __device__ void softmax_topk_block(float* ls, int* hist_s, int64_t tok0, int64_t
     for (int tl = 0; tl < nvalid; ++tl) s += ls[tl * ldl + e];
     me_part[(int64_t)e * nblk + blk] = s;
   }
+}
+
+__device__ __forceinline__ void softmax_topk_block(float* ls, int* hist_s, int64_t tok0, int64_t T,
+                                                   int E, int k, int normalize, bool softmax_needed,
+                                                   float* scores, int32_t* idx, float* gates,
+                                                   int32_t* hist, float* me_part, int nblk) {
+  if (E <= 32)
+    softmax_topk_lanes<1>(ls, hist_s, tok0, T, E, k, normalize, softmax_needed, scores, idx, gates, hist, me_part, nblk);
+  else if (E <= 64)
+    softmax_topk_lanes<2>(ls, hist_s, tok0, T, E, k, normalize, softmax_needed, scores, idx, gates, hist, me_part, nblk);
+  else if (E <= 128)
+    softmax_topk_lanes<4>(ls, hist_s, tok0, T, E, k, normalize, softmax_needed, scores, idx, gates, hist, me_part, nblk);
+  else
+    softmax_topk_lanes<kMaxExperts / 32>(ls, hist_s, tok0, T, E, k, normalize, softmax_needed, scores, idx, gates, hist, me_part, nblk);
 }
 
 template <typename T, int EJ>
