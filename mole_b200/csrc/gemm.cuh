@@ -30,6 +30,8 @@ struct RowGemmArgs {
   int epi, act, gelu_bwd;
   int e_begin, n_experts;   // experts covered by the schedule
   int single_cta;           // tensor cores: keep to the one-CTA kernel (A/B comparisons)
+  int panel;                // tensor cores: every expert's rows are one contiguous run and the panel
+                            // kernel may take the launch (outputs in place, no fused combine)
   const int32_t* rowmap;    // tensor cores, FC2 / dX: scatter output rows (-1 = drop), or null
   PeerMap peers;            // with rowmap: the scattered rows go to their source ranks (n > 0)
   int peer_Cs;              // rows per chunk of the receive buffers
@@ -55,6 +57,8 @@ struct WgradArgs {
   int accumulate;
   int e_begin, n_experts;
   int single_cta;
+  int resident;               // tensor cores: the resident-operand kernel may take the launch
+  int max_tiles_per_expert;   // bound on an expert's 128-row tiles (sizes the resident operand)
   Schedule sched;
   SlotMap gslot;
 };

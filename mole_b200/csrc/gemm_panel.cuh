@@ -1,0 +1,561 @@
+// Panel kernel: the rows-mode grouped GEMM with the operand roles swapped.  Included by
+// gemm_tc.cu (it uses that file's PTX wrappers, TcParams and epilogue traits).
+//
+// The tile kernels put 128 rows of an expert on the M side of the MMA: an expert with 264 rows
+// pays for 384.  Here the WEIGHTS are the M operand -- a CTA pair (cta_group::2) takes 256 output
+// features of one expert, 128 per SM, always full -- and the expert's rows are the N operand,
+// whose extent can be any multiple of 16 up to 256: D^T[feature][row] = W[feature][k] * X[row][k].
+// An expert's rows are cut into ceil(rows / 256) panels of equal size (rounded up to 16), so 264
+// rows cost 288 and every weight element crosses shared memory once per panel instead of once
+// per 128-row tile.  Each CTA stages its 128 features of W and half of the panel's rows; the
+// accumulator (128 lanes = features, N columns = rows) is double-buffered in TMEM.
+//
+// The accumulator comes out transposed: a thread of the epilogue owns one feature and reads 16
+// rows of it per tcgen05.ld, and a warp's store instruction writes 32 neighbouring features of
+// one row (64 contiguous bytes).  Bias is one scalar per thread.
+//
+// Needs every expert's rows in one contiguous run (one source rank, or the compacted layout)
+// and outputs that stay in place (no row map).
+#pragma once
+
+constexpr int kPanelStages = 6;
+constexpr uint32_t kPanelABytes = 128 * kBK * 2;      // 128 features x 64 K
+constexpr uint32_t kPanelBBytes = 128 * kBK * 2;      // up to 128 rows x 64 K per CTA
+constexpr uint32_t kPanelStageBytes = kPanelABytes + kPanelBBytes;
+
+struct PanelMaps {
+  CUtensorMap w;        // weights: box 64 K x 128 features (K-major) or 64 features x 64 K (N-major)
+  CUtensorMap x[4];     // rows [total_rows][K]: boxes of 64 K x {64, 32, 16, 8} rows
+};
+
+struct PanelItem {
+  int valid;
+  int el;          // expert relative to e_begin
+  int n0;          // first of the pair's 256 output features
+  int row0;        // first row of the panel
+  int n;           // rows of the panel, a multiple of 16 (0: nothing to do)
+};
+
+__device__ __forceinline__ PanelItem decode_panel(const TcParams& p, const int* start, const int* pstart, int item) {
+  PanelItem w;
+  w.valid = 0;
+  const int nb = p.N / 256;
+  if (item >= pstart[p.n_experts] * nb) return w;
+  int lo = 0, hi = p.n_experts;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (pstart[mid] * nb <= item) lo = mid; else hi = mid;
+  }
+  // expert_pair_start is the prefix of ceil(tiles / 2) = ceil(rows / 256): the panels per expert
+  const int ps = pstart[lo], np = pstart[lo + 1] - ps;
+  const int local = item - ps * nb;
+  const int pan = local % np;            // panels of a feature block are neighbours: they share W through L2
+  const int ts = start[lo], te = start[lo + 1];
+  const int rows = (te - ts - 1) * kTileRows + p.tile_rows[te - 1];
+  const int per = (((rows + np - 1) / np) + 15) & ~15;
+  const int left = rows - pan * per;
+  w.valid = 1;
+  w.el = lo;
+  w.n0 = (local / np) * 256;
+  w.row0 = p.tile_row0[ts] + pan * per;
+  w.n = left <= 0 ? 0 : min(per, (left + 15) & ~15);
+  return w;
+}
+
+__device__ __forceinline__ uint16_t bf16_bits(float v) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ void st_b16(__nv_bfloat16* p, uint16_t v) {
+  asm volatile("st.global.b16 [%0], %1;" ::"l"(p), "h"(v) : "memory");
+}
+
+template <bool W_KMAJOR, int EV>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant__ TcParams p) {
+  constexpr int STAGES = kPanelStages;
+  constexpr uint32_t kTmemCols = 512;                   // two accumulators of up to 256 columns
+  constexpr uint32_t kBoxBytes = 128 * kBK;             // one 64-feature box of N-major weights
+  // f32 accumulate, bf16 operands, A (weights) K-major or MN-major, B (rows) K-major, M = 256
+  constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((W_KMAJOR ? 0u : 1u) << 15) |
+                                  ((uint32_t)(256 >> 4) << 24);
+  using Ev = EvTraits<EV>;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag_s;
+  __shared__ int start_s[kMaxLocalExperts + 1], pstart_s[kMaxLocalExperts + 1];    // see decode_item
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+  const uint32_t drain0 = smem_u32(&bars[2 * STAGES + 4]);      // used only after an abort
+  const uint32_t smem_base = smem_u32(smem);
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int nkb = p.K / kBK;
+
+  for (int i = threadIdx.x; i <= p.n_experts; i += kThreads) {
+    start_s[i] = p.expert_tile_start[i];
+    pstart_s[i] = p.expert_pair_start[i];
+  }
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    mbar_init(drain0, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);               // the even CTA's arrive.expect_tx
+      mbar_init(empty0 + 8 * s, 1);              // one multicast commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 2 * kEpiWarps); // epilogue warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  cluster_sync_all();                            // peer barriers initialised, TMEM address published
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs, whole warp) --------------
+    // A stage is one or two weight boxes and the CTA's half of the panel's rows, cut into boxes
+    // of 64, 32, 16 and 8 rows; each box is issued by its own lane so they leave together.
+    int stage = 0;
+    uint32_t phase = 0, issued = 0;
+    bool ok = true;
+    for (int item = cluster_id; ok; item += n_clusters) {
+      const PanelItem w = decode_panel(p, start_s, pstart_s, item);
+      if (!w.valid) break;
+      if (w.n == 0) continue;
+      const int slot = p.slot.s[p.e_begin + w.el];
+      const int half = w.n >> 1;                       // rows this CTA stages (a multiple of 8)
+      const uint32_t tx = 2u * (kPanelABytes + (uint32_t)half * 128u);
+      const int f0 = w.n0 + 128 * (int)rank;           // this CTA's features
+      const int r0 = w.row0 + half * (int)rank;        // this CTA's rows
+      // what this lane loads in every stage of the item
+      int kind = -1, off = 0;                          // kind 0..3: row box of 64 >> kind rows at row offset `off`
+      const int n64 = half >> 6, rem = half & 63;
+      if (lane >= 2 && lane < 4) { if (lane - 2 < n64) { kind = 0; off = 64 * (lane - 2); } }
+      else if (lane == 4) { if (rem & 32) { kind = 1; off = 64 * n64; } }
+      else if (lane == 5) { if (rem & 16) { kind = 2; off = 64 * n64 + (rem & 32); } }
+      else if (lane == 6) { if (rem & 8) { kind = 3; off = 64 * n64 + (rem & 48); } }
+      for (int kb = 0; kb < nkb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 21));
+        if (!ok) break;
+        const uint32_t bar = (full0 + 8 * stage) & kPeerMask;     // the even CTA's barrier
+        const uint32_t sa = smem_base + stage * kPanelStageBytes, sb = sa + kPanelABytes;
+        if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, tx);
+        if (W_KMAJOR) {
+          if (lane == 0) tma2_load_3d(sa, &maps.w, bar, kb * kBK, f0, slot);
+        } else {
+          if (lane < 2) tma2_load_3d(sa + lane * kBoxBytes, &maps.w, bar, f0 + 64 * lane, kb * kBK, slot);
+        }
+        if (kind >= 0) tma2_load_2d(sb + off * 128, &maps.x[kind], bar, kb * kBK, r0 + off);
+        ++issued;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    // both CTAs' loads complete on the even CTA's barriers: it waits for the pair
+    if (leader && lane == 0 && *abort_flag) drain_loads(full0, STAGES, issued);
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (even CTA only) -----------------------
+    if (lane == 0 && leader) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = cluster_id; ok; item += n_clusters) {
+        const PanelItem w = decode_panel(p, start_s, pstart_s, item);
+        if (!w.valid) break;
+        if (w.n == 0) continue;
+        if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 22))) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        const uint32_t idesc = kIdescBase | ((uint32_t)(w.n >> 3) << 17);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!(ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 23))) break;
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kPanelStageBytes, sb = sa + kPanelABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
+            const uint64_t ad = W_KMAJOR ? make_desc(sa + ks * (kUmmaK * 2), 16, 1024)
+                                         : make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024);
+            const uint64_t bd = make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
+            tcgen05_mma2_bf16(d_tmem, ad, bd, idesc, (kb | ks) ? 1u : 0u);
+          }
+          tcgen05_commit2(empty0 + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tcgen05_commit2(tfull0 + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (*abort_flag) {                      // MMAs already issued retire before the TMEM goes
+        tcgen05_commit2(drain0);
+        mbar_drain(drain0, 0, globaltimer_ns() + 200000000ull);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs) -----------------------------
+    // warp -> 32 features (the TMEM lanes it may read) and every fourth chunk of 16 rows
+    const int quarter = warp & 3;
+    const int grp = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int item = cluster_id;; item += n_clusters) {
+      const PanelItem w = decode_panel(p, start_s, pstart_s, item);
+      if (!w.valid) break;
+      if (w.n == 0) continue;
+      const int slot = p.slot.s[p.e_begin + w.el];
+      const int f = w.n0 + 128 * (int)rank + 32 * quarter + lane;
+      const int64_t obase = (int64_t)w.row0 * p.N + f;         // element (row0, f) of the outputs
+      float bias = 0.f;
+      if (Ev::bias) bias = __bfloat162float(p.bias[(int64_t)slot * p.N + f]);
+      // dX2: the pre-activations of this thread's (feature, rows), fetched before the wait
+      uint32_t pre[4][8];
+      if (Ev::epi == EPI_DACT) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int c0 = (grp + 4 * jj) * 16;
+          if (c0 < w.n) {
+            const uint16_t* src = reinterpret_cast<const uint16_t*>(p.aux) + obase + (int64_t)c0 * p.N;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t lo = src[(int64_t)(2 * i) * p.N], hi = src[(int64_t)(2 * i + 1) * p.N];
+              pre[jj][i] = lo | (hi << 16);
+            }
+          }
+        }
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 24)))
+        break;                                        // nothing is stored for this item
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int c0 = (grp + 4 * jj) * 16;
+        if (c0 < w.n) {                               // warp-uniform
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+          __nv_bfloat16* o0 = p.out0 + obase + (int64_t)c0 * p.N;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float v = __uint_as_float(r[i]);
+            if (Ev::epi == EPI_FC1) {
+              const uint16_t x1 = bf16_bits(v + bias);
+              st_b16(o0 + (int64_t)i * p.N, x1);
+              // the activation is taken of the rounded pre-activation, as backward sees it
+              st_b16(p.out1 + obase + (int64_t)(c0 + i) * p.N,
+                     bf16_bits(act_fwd_t<Ev::act>(__uint_as_float((uint32_t)x1 << 16))));
+            } else if (Ev::epi == EPI_DACT) {
+              const uint32_t pw = pre[jj][i >> 1];
+              const float x1 = (i & 1) ? bf16_hi(pw) : bf16_lo(pw);
+              st_b16(o0 + (int64_t)i * p.N, bf16_bits(v * act_grad_t<Ev::act, Ev::gbwd>(x1)));
+            } else {
+              st_b16(o0 + (int64_t)i * p.N, bf16_bits(v + bias));
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster((tempty0 + 8 * acc) & kPeerMask);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tcgen05_fence_before();
+  cluster_sync_all();          // nobody leaves while the peer may still touch its smem or barriers
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols) : "memory");
+  }
+}
+
+// =========================================================================================
+// Weight gradient with one operand resident in shared memory.
+//
+// gW_e[p, q] = sum_r A[r, p] * B[r, q] over the rows r of expert e: the reduction is short (an
+// expert's few hundred rows) and the output large ([F, M] per expert), so the tile kernels load
+// (128 + 256) x rows operand elements for every 128 x 256 outputs -- three times the bytes they
+// write -- and run at the rate shared memory can be filled through L2, not at the rate HBM takes
+// the gradient.  Here a CTA pair takes (expert, 256 columns q) and keeps B[:, q-block] -- all
+// rows of the expert, 128 columns per CTA -- in shared memory while it walks down the expert's
+// p-blocks of 256, streaming only A: operand bytes per output tile drop from 240 KB to ~85 KB.
+//
+//   shared memory per CTA: RES resident stages of 64 rows x 128 q (16 KB each) + a ring of
+//   12 - RES stages of 64 rows x 128 p (16 KB each); an expert may have at most RES 64-row
+//   stages (the host checks the bound and falls back to the tile kernel beyond it).
+//
+// Barriers as in tc2_gemm_kernel, plus bfull (resident operand landed; armed by the even CTA,
+// completed by both CTAs' loads) and bfree (every MMA that reads the resident operand has
+// retired; a multicast commit).
+// One lane polls, the warp gets the answer.
+__device__ __forceinline__ bool warp_wait(bool one, uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* fault, int code) {
+  if (!one) return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, fault, code));
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, fault, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+constexpr int kResTotalStages = 12;
+constexpr uint32_t kResStageBytes = 128 * kWBK * 2;      // 16 KB: 64 rows x 128 columns, two boxes
+
+struct ResUnit {
+  int valid;
+  int el;
+  int q0;            // first of the pair's 256 output columns
+  int pb0, pb1;      // p-blocks (of 256 rows of the output) this unit walks
+  int row0, rows;    // the expert's rows: one contiguous run (0 rows: the gradient is zero)
+};
+// Stage s of an expert covers rows [row0 + 64 s, ...): its number of 16-row MMA steps
+__device__ __forceinline__ int res_ksteps(int rows, int s) {
+  const int left = rows - s * kWBK;
+  return left >= kWBK ? kWBK / kUmmaK : (left + kUmmaK - 1) / kUmmaK;
+}
+
+__device__ __forceinline__ ResUnit decode_res(const TcParams& p, int unit, int split) {
+  ResUnit w;
+  w.valid = 0;
+  const int qb = p.N / 256, pb = p.P / 256;
+  if (unit >= p.n_experts * qb * split) return w;
+  w.valid = 1;
+  w.el = unit / (qb * split);
+  const int r = unit - w.el * qb * split;
+  // the q-blocks of one range of p are neighbours: they stream the same A through L2
+  w.q0 = (r % qb) * 256;
+  const int sp = r / qb;
+  w.pb0 = (int)((int64_t)pb * sp / split);
+  w.pb1 = (int)((int64_t)pb * (sp + 1) / split);
+  const int t0 = p.expert_tile_start[w.el], t1 = p.expert_tile_start[w.el + 1];
+  w.rows = t1 > t0 ? (t1 - t0 - 1) * kTileRows + p.tile_rows[t1 - 1] : 0;
+  w.row0 = t1 > t0 ? p.tile_row0[t0] : 0;
+  return w;
+}
+
+template <int RES, int EV>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ TcParams p, const int split) {
+  constexpr int STAGES = kResTotalStages - RES;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kBoxBytes = 128 * kWBK;            // one box: 64 columns x 64 rows
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
+                              ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 7];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag_s;
+  __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+  const uint32_t drain0 = smem_u32(&bars[2 * STAGES + 4]);      // used only after an abort
+  const uint32_t bfull = smem_u32(&bars[2 * STAGES + 5]), bfree = smem_u32(&bars[2 * STAGES + 6]);
+  const uint32_t res_base = smem_u32(smem);                      // resident stages
+  const uint32_t ring_base = res_base + RES * kResStageBytes;    // streamed stages
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    mbar_init(drain0, 1);
+    mbar_init(bfull, 1);
+    mbar_init(bfree, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 2 * kEpiWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  cluster_sync_all();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs, whole warp) --------------
+    int stage = 0;
+    uint32_t phase = 0, issued = 0, unit_phase = 0, res_armed = 0;
+    bool ok = true;
+    for (int unit = cluster_id; ok; unit += n_clusters) {
+      const ResUnit w = decode_res(p, unit, split);
+      if (!w.valid) break;
+      if (w.rows == 0) continue;                       // empty expert: the epilogue writes zeros
+      // resident operand: wait until the previous unit's MMAs are done with it, then load
+      ok = warp_wait(false, bfree, unit_phase ^ 1, abort_flag, p.fault, 31);
+      if (!ok) break;
+      const int ns = (w.rows + kWBK - 1) / kWBK;
+      if (ns > RES) {                                  // the host bounds this; never index past the buffer
+        if (lane == 0) { *abort_flag = 1; atomicCAS(p.fault, 0, 35); }
+        ok = false;
+        break;
+      }
+      if (leader && lane == 0) mbar_expect_tx(bfull, 2u * (uint32_t)ns * kResStageBytes);
+      ++res_armed;
+      __syncwarp();
+      {
+        // boxes 2s and 2s + 1 of the resident operand are issued by lanes 2s and 2s + 1
+        const int qh = w.q0 + 128 * (int)rank;         // this CTA's half of the columns
+        const uint32_t bar = bfull & kPeerMask;
+        const int s = lane >> 1;
+        if (s < ns)
+          tma2_load_2d(res_base + s * kResStageBytes + (lane & 1) * kBoxBytes, &tmap_b, bar,
+                       qh + 64 * (lane & 1), w.row0 + s * kWBK);
+      }
+      // streamed operand: every p-block walks the expert's stages
+      for (int pb = w.pb0; pb < w.pb1 && ok; ++pb) {
+        const int ph = pb * 256 + 128 * (int)rank + 64 * (lane & 1);     // this lane's 64 output rows
+        for (int s = 0; s < ns && ok; ++s) {
+          {
+            ok = warp_wait(false, empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 32);
+            if (ok) {
+              const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
+              const uint32_t sa = ring_base + stage * kResStageBytes;
+              if (p.dbg & 8) {
+                if (leader && lane == 0) mbar_arrive(full0 + 8 * stage);
+              } else {
+                if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, 2u * kResStageBytes);
+                if (lane < 2) tma2_load_2d(sa + lane * kBoxBytes, &tmap_a, bar, ph, w.row0 + s * kWBK);
+              }
+              ++issued;
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          }
+        }
+      }
+      unit_phase ^= 1;
+    }
+    if (leader && lane == 0 && *abort_flag) {
+      drain_loads(full0, STAGES, issued);
+      if (res_armed > 0) mbar_drain(bfull, (res_armed - 1) & 1u, globaltimer_ns() + 200000000ull);
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (even CTA only) -----------------------
+    if (lane == 0 && leader) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0, unit_phase = 0;
+      bool ok = true;
+      for (int unit = cluster_id; ok; unit += n_clusters) {
+        const ResUnit w = decode_res(p, unit, split);
+        if (!w.valid) break;
+        if (w.rows == 0) continue;
+        const int ns = (w.rows + kWBK - 1) / kWBK;
+        if (ns > RES) break;                          // the producer has raised the fault
+        if (!(ok = mbar_wait(bfull, unit_phase, abort_flag, p.fault, 33))) break;
+        tcgen05_fence_after();
+        for (int pb = w.pb0; pb < w.pb1 && ok; ++pb) {
+          if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12))) break;
+          tcgen05_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * 256;
+          for (int s = 0; s < ns && ok; ++s) {
+            {
+              const int ksteps = res_ksteps(w.rows, s);
+              if ((ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 13))) {
+                tcgen05_fence_after();
+                const uint32_t sa = ring_base + stage * kResStageBytes;
+                const uint32_t sb = res_base + s * kResStageBytes;
+#pragma unroll
+                for (int ks = 0; ks < kWBK / kUmmaK; ++ks) {
+                  if (ks < ksteps && !((p.dbg & 2) && !(s == 0 && ks == 0))) {
+                    const uint64_t ad = make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024);
+                    const uint64_t bd = make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024);
+                    tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (s == 0 && ks == 0) ? 0u : 1u);
+                  }
+                }
+                tcgen05_commit2(empty0 + 8 * stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+              }
+            }
+          }
+          if (!ok) break;
+          tcgen05_commit2(tfull0 + 8 * acc);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+        if (!ok) break;
+        tcgen05_commit2(bfree);                       // the resident operand may be replaced
+        unit_phase ^= 1;
+      }
+      if (*abort_flag) {
+        tcgen05_commit2(drain0);
+        mbar_drain(drain0, 0, globaltimer_ns() + 200000000ull);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs) -----------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int cq = ew >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int unit = cluster_id; ok; unit += n_clusters) {
+      const ResUnit w = decode_res(p, unit, split);
+      if (!w.valid) break;
+      const int slot = p.slot.s[p.e_begin + w.el];
+      const bool empty = w.rows == 0;
+      for (int pb = w.pb0; pb < w.pb1; ++pb) {
+        const int lrow = quarter * 32 + lane;
+        const int64_t obase = ((int64_t)slot * p.P + pb * 256 + 128 * (int)rank + lrow) * p.N + w.q0;
+        constexpr int NSTEPS = 256 / 4 / kEpiStep;
+        uint32_t pre[NSTEPS][8];
+        epilogue_prefetch<EV, NSTEPS>(p, obase, nullptr, nullptr, cq * 64, pre);
+        if (!empty) {
+          if (!(ok = warp_wait(false, tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 14))) break;
+          tcgen05_fence_after();
+        }
+        using Ev = EvTraits<EV>;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
+        if (p.dbg & 4) {
+        } else if (EV == EV_WGRAD)
+          epilogue_lines<NSTEPS>(p.out0, obase - (int64_t)lane * p.N, p.N, taddr, empty, cq * 64,
+                                 store_strip[ew], !(p.dbg & 1));
+        else
+          epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
+              p, taddr, empty, true, p.out0, obase, nullptr, cq * 64, pre, nullptr);
+        if (!empty) {
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster((tempty0 + 8 * acc) & kPeerMask);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols) : "memory");
+  }
+}

@@ -265,6 +265,7 @@ struct TcParams {
   const float* c_gates;
   __nv_bfloat16* c_y;          // null: no fused combine
   int c_k, c_Cs;
+  int dbg;
 };
 
 // y[0..7] (eight bf16 pairs = 16 columns) += v, as two 16-byte reductions at L2.  With k <= 2 a
@@ -284,20 +285,23 @@ struct WorkItem {
   int t0, t1;     // wgrad: tile range of the expert
 };
 
+// `start` is the kernel's shared-memory copy of expert_tile_start: shared memory takes nearly all
+// of the SM's L1, so a chain of dependent global loads (the binary search) would cost an L2 round
+// trip per step, per work item, on the critical path of every role.
 template <int MODE, int BN>
-__device__ __forceinline__ WorkItem decode_item(const TcParams& p, int item) {
+__device__ __forceinline__ WorkItem decode_item(const TcParams& p, const int* start, int item) {
   WorkItem w;
   w.valid = 0;
   if (MODE == TC_ROWS) {
     const int nb = p.N / BN;
-    const int total = (*p.n_tiles) * nb;
+    const int total = start[p.n_experts] * nb;
     if (item >= total) return w;
     int lo = 0, hi = p.n_experts;            // last expert with tile_start * nb <= item
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (p.expert_tile_start[mid] * nb <= item) lo = mid; else hi = mid;
+      if (start[mid] * nb <= item) lo = mid; else hi = mid;
     }
-    const int s = p.expert_tile_start[lo], nt = p.expert_tile_start[lo + 1] - s;
+    const int s = start[lo], nt = start[lo + 1] - s;
     const int local = item - s * nb;
     const int tile = s + local % nt;
     w.valid = 1;
@@ -313,8 +317,8 @@ __device__ __forceinline__ WorkItem decode_item(const TcParams& p, int item) {
     const int r = item - w.el * pb * qb;
     w.row0 = (r / qb) * kBM;
     w.n0 = (r % qb) * BN;
-    w.t0 = p.expert_tile_start[w.el];
-    w.t1 = p.expert_tile_start[w.el + 1];
+    w.t0 = start[w.el];
+    w.t1 = start[w.el + 1];
   }
   return w;
 }
@@ -524,7 +528,7 @@ constexpr int kStripBytes = 2048;
 template <int NSTEPS>
 __device__ __forceinline__ void epilogue_lines(__nv_bfloat16* out, int64_t warp_base, int ldo,
                                                uint32_t taddr, bool empty, int c_begin,
-                                               uint8_t* strip) {
+                                               uint8_t* strip, bool store = true) {
   constexpr int kRowBytes = NSTEPS * 32;
   constexpr int kRows = kStripBytes / kRowBytes;      // rows per pass
   constexpr int kPasses = 32 / kRows;
@@ -567,7 +571,7 @@ __device__ __forceinline__ void epilogue_lines(__nv_bfloat16* out, int64_t warp_
       const uint4 lo = *reinterpret_cast<const uint4*>(row + (((2 * ra) ^ (rr & kMask)) << 4));
       const uint4 hi = *reinterpret_cast<const uint4*>(row + (((2 * ra + 1) ^ (rr & kMask)) << 4));
       const uint32_t v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-      st_v8(out + warp_base + (int64_t)(kRows * j + rr) * ldo + c_begin + kEpiStep * ra, v);
+      if (store) st_v8(out + warp_base + (int64_t)(kRows * j + rr) * ldo + c_begin + kEpiStep * ra, v);
     }
     if (j + 1 < kPasses) __syncwarp();
   }
@@ -636,6 +640,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
   __shared__ __align__(16) uint8_t scatter_strip[kEpiWarps][kScatterStripBytes];   // ... scatter_lines
+  __shared__ int start_s[kMaxLocalExperts + 1];                   // expert_tile_start, see decode_item
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -644,6 +649,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t drain0 = smem_u32(&bars[2 * STAGES + 4]);      // used only after an abort
   const uint32_t smem_base = smem_u32(smem);
 
+  for (int i = threadIdx.x; i <= p.n_experts; i += kThreads) start_s[i] = p.expert_tile_start[i];
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
     mbar_init(drain0, 1);
@@ -678,7 +684,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0, issued = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok; item += gridDim.x) {
-        const WorkItem w = decode_item<MODE, BN>(p, item);
+        const WorkItem w = decode_item<MODE, BN>(p, start_s, item);
         if (!w.valid) break;
         const int slot = p.slot.s[p.e_begin + w.el];
         if (MODE == TC_ROWS) {
@@ -735,7 +741,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok; item += gridDim.x) {
-        const WorkItem w = decode_item<MODE, BN>(p, item);
+        const WorkItem w = decode_item<MODE, BN>(p, start_s, item);
         if (!w.valid) break;
         if (MODE == TC_WGRAD && w.t1 == w.t0) continue;      // empty expert: epilogue writes zeros
         if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 2))) break;
@@ -791,7 +797,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int item = blockIdx.x;; item += gridDim.x) {
-      const WorkItem w = decode_item<MODE, BN>(p, item);
+      const WorkItem w = decode_item<MODE, BN>(p, start_s, item);
       if (!w.valid) break;
       const int e = p.e_begin + w.el;
       const int slot = p.slot.s[e];
@@ -937,22 +943,22 @@ struct PairItem {
 };
 
 template <int MODE>
-__device__ __forceinline__ PairItem decode_pair(const TcParams& p, int item) {
+__device__ __forceinline__ PairItem decode_pair(const TcParams& p, const int* start, const int* pstart, int item) {
   PairItem w;
   w.valid = 0;
   if (MODE == TC_ROWS) {
     const int nb = p.N / kBN2;
-    const int total = p.expert_pair_start[p.n_experts] * nb;
+    const int total = pstart[p.n_experts] * nb;
     if (item >= total) return w;
     int lo = 0, hi = p.n_experts;
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (p.expert_pair_start[mid] * nb <= item) lo = mid; else hi = mid;
+      if (pstart[mid] * nb <= item) lo = mid; else hi = mid;
     }
-    const int ps = p.expert_pair_start[lo], np = p.expert_pair_start[lo + 1] - ps;
+    const int ps = pstart[lo], np = pstart[lo + 1] - ps;
     const int local = item - ps * nb;
     const int pair = local % np;
-    const int ts = p.expert_tile_start[lo], te = p.expert_tile_start[lo + 1];
+    const int ts = start[lo], te = start[lo + 1];
     w.valid = 1;
     w.el = lo;
     w.n0 = (local / np) * kBN2;
@@ -968,8 +974,8 @@ __device__ __forceinline__ PairItem decode_pair(const TcParams& p, int item) {
     w.row0[0] = (r / qb) * 256;
     w.row0[1] = w.row0[0] + 128;
     w.n0 = (r % qb) * kBN2;
-    w.t0 = p.expert_tile_start[w.el];
-    w.t1 = p.expert_tile_start[w.el + 1];
+    w.t0 = start[w.el];
+    w.t1 = start[w.el + 1];
   }
   return w;
 }
@@ -999,6 +1005,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __shared__ __align__(16) float bias_strip[kEpiWarps][64];       // per epilogue warp: bias of its columns
   __shared__ __align__(16) uint8_t store_strip[kEpiWarps][kStripBytes];   // per epilogue warp: epilogue_lines
   __shared__ __align__(16) uint8_t scatter_strip[kEpiWarps][kScatterStripBytes];   // ... scatter_lines
+  __shared__ int start_s[kMaxLocalExperts + 1], pstart_s[kMaxLocalExperts + 1];    // see decode_item
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1010,6 +1017,10 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const uint32_t smem_base = smem_u32(smem);
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
+  for (int i = threadIdx.x; i <= p.n_experts; i += kThreads) {
+    start_s[i] = p.expert_tile_start[i];
+    pstart_s[i] = p.expert_pair_start[i];
+  }
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
     mbar_init(drain0, 1);          // the drain commit is multicast like the others: one arrival per CTA
@@ -1041,7 +1052,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t phase = 0, issued = 0;
       bool ok = true;
       for (int item = cluster_id; ok; item += n_clusters) {
-        const PairItem w = decode_pair<MODE>(p, item);
+        const PairItem w = decode_pair<MODE>(p, start_s, pstart_s, item);
         if (!w.valid) break;
         const int slot = p.slot.s[p.e_begin + w.el];
         const bool have_a = w.row0[rank] >= 0;
@@ -1100,7 +1111,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int item = cluster_id; ok; item += n_clusters) {
-        const PairItem w = decode_pair<MODE>(p, item);
+        const PairItem w = decode_pair<MODE>(p, start_s, pstart_s, item);
         if (!w.valid) break;
         if (MODE == TC_WGRAD && w.t1 == w.t0) continue;
         if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12))) break;
@@ -1155,7 +1166,7 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int item = cluster_id;; item += n_clusters) {
-      const PairItem w = decode_pair<MODE>(p, item);
+      const PairItem w = decode_pair<MODE>(p, start_s, pstart_s, item);
       if (!w.valid) break;
       const int slot = p.slot.s[p.e_begin + w.el];
       const bool empty = MODE == TC_WGRAD && w.t1 == w.t0;
@@ -1223,6 +1234,8 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                  "r"(kTmemCols) : "memory");
   }
 }
+
+#include "gemm_panel.cuh"
 
 // ---- host side ------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1368,7 +1381,93 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
   return MOLE_OK;
 }
 
+// Launch of the panel kernel: as launch_tc2, one work unit = (expert, 256 features, row panel).
+template <bool W_KMAJOR, int EV>
+static int launch_panel(const PanelMaps& maps, const TcParams& p, int max_items, cudaStream_t st) {
+  constexpr size_t smem = (size_t)kPanelStages * kPanelStageBytes + 1024;
+  auto kern = panel_gemm_kernel<W_KMAJOR, EV>;
+  static PerDeviceInt max_clusters_of;
+  const int dev = current_device();
+  int max_clusters = (int)max_clusters_of.get(dev);
+  if (max_clusters == 0) {
+    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    max_clusters = n;
+    max_clusters_of.set(dev, n);
+  }
+  int clusters = max_clusters < max_items ? max_clusters : max_items;
+  if (clusters <= 0) return MOLE_OK;
+  if (profile_enabled()) profile_begin(st, p.epi);
+  kern<<<2 * clusters, kThreads, smem, st>>>(maps, p);
+  if (profile_enabled()) profile_end(st);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
+// Launch of the resident-operand weight gradient.  A unit is (expert, 256 columns, one of `split`
+// ranges of p-blocks); `split` is chosen so that the last round of units over the resident
+// clusters is as full as possible.
+template <int RES, int EV>
+static int launch_res(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int n_experts,
+                      cudaStream_t st) {
+  constexpr size_t smem = (size_t)kResTotalStages * kResStageBytes + 1024;
+  auto kern = wgrad_resident_kernel<RES, EV>;
+  static PerDeviceInt max_clusters_of;
+  const int dev = current_device();
+  int max_clusters = (int)max_clusters_of.get(dev);
+  if (max_clusters == 0) {
+    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    max_clusters = n;
+    max_clusters_of.set(dev, n);
+  }
+  const int base = n_experts * (p.N / 256), pb = p.P / 256;
+  int split = 1;
+  double best = 0.0;
+  for (int sp = 1; sp <= 8 && sp <= pb; sp *= 2) {
+    const int units = base * sp;
+    const int rounds = (units + max_clusters - 1) / max_clusters;
+    const double fill = (double)units / ((double)rounds * max_clusters);
+    if (fill > best + 0.02) { best = fill; split = sp; }
+  }
+  const int units = base * split;
+  int clusters = max_clusters < units ? max_clusters : units;
+  if (clusters <= 0) return MOLE_OK;
+  if (profile_enabled()) profile_begin(st, p.epi);
+  kern<<<2 * clusters, kThreads, smem, st>>>(ma, mb, p, split);
+  if (profile_enabled()) profile_end(st);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
 static void fill_sched(TcParams& p, const Schedule& s) {
+  { const char* v = getenv("MOLE_DBG"); p.dbg = v ? atoi(v) : 0; }
   p.n_tiles = s.n_tiles;
   p.expert_tile_start = s.expert_tile_start;
   p.tile_row0 = s.tile_row0;
@@ -1381,9 +1480,17 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   MOLE_REQUIRE(a.N % 128 == 0 && a.K % kBK == 0, "tensor-core GEMM needs N %% 128 == 0 and K %% 64 == 0 (N=%d K=%d)", a.N, a.K);
   MOLE_REQUIRE(a.total_rows % kTileRows == 0, "row buffers must hold whole 128-row tiles");
   const int BN = a.N % 256 == 0 ? 256 : 128;
-  const bool pair = BN == 256 && !a.single_cta;
+  const bool panel = a.panel && BN == 256 && a.rowmap == nullptr && a.peers.n == 0 && a.c_y == nullptr;
+  const bool pair = BN == 256 && (!a.single_cta || panel);
   CUtensorMap ma, mb;
-  {
+  PanelMaps pm;
+  if (panel) {
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.total_rows};
+      const uint32_t box[2] = {kBK, (uint32_t)(64 >> i)};
+      if (int rc = make_map(&pm.x[i], a.A, 2, dims, box)) return rc;
+    }
+  } else {
     const uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.total_rows};
     const uint32_t box[2] = {kBK, kBM};
     if (int rc = make_map(&ma, a.A, 2, dims, box)) return rc;
@@ -1432,9 +1539,11 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
     MOLE_REQUIRE((reinterpret_cast<uintptr_t>(q) & 31) == 0, "epilogue operand %p not 32-byte aligned", q);
   MOLE_REQUIRE(a.c_y == nullptr || (!pair && a.rowmap == nullptr && (a.epi == EPI_BIAS || a.epi == EPI_STORE)),
                "the fused combine needs the one-CTA kernel and rows that are not scattered");
+  if (panel) pm.w = mb;
   // one kernel per (operand layout, tile shape, epilogue variant)
 #define MOLE_ROWS(KM, EV)                                                                    \
-  return pair ? launch_tc2<TC_ROWS, KM, EV>(ma, mb, p, max_items, st)                        \
+  return panel ? launch_panel<KM, EV>(pm, p, max_items, st)                                  \
+         : pair ? launch_tc2<TC_ROWS, KM, EV>(ma, mb, p, max_items, st)                      \
               : BN == 256 ? launch_tc<TC_ROWS, KM, 256, EV>(ma, mb, p, max_items, st)        \
                           : launch_tc<TC_ROWS, KM, 128, EV>(ma, mb, p, max_items, st)
   const bool relu = a.act == MOLE_ACT_RELU;
@@ -1484,6 +1593,16 @@ int tc_wgrad(const WgradArgs& a, cudaStream_t st) {
   p.slot = a.gslot;
   MOLE_REQUIRE((reinterpret_cast<uintptr_t>(a.out) & 31) == 0, "gradient base not 32-byte aligned");
   const int max_items = a.n_experts * (a.P / kBM) * (a.Q / BN);
+  // an expert's 64-row stages: at most two per 128-row tile
+  const int max_stages = 2 * a.max_tiles_per_expert;
+  if (a.resident && BN == 256 && a.P % 256 == 0 && max_stages > 0 && max_stages <= 8) {
+    if (max_stages <= 6) {
+      if (a.accumulate) return launch_res<6, EV_WGRAD_ACC>(ma, mb, p, a.n_experts, st);
+      return launch_res<6, EV_WGRAD>(ma, mb, p, a.n_experts, st);
+    }
+    if (a.accumulate) return launch_res<8, EV_WGRAD_ACC>(ma, mb, p, a.n_experts, st);
+    return launch_res<8, EV_WGRAD>(ma, mb, p, a.n_experts, st);
+  }
 #define MOLE_WG(EV)                                                                               \
   if (BN == 256 && a.P % 256 == 0 && !a.single_cta)                                               \
     return launch_tc2<TC_WGRAD, true, EV>(ma, mb, p, a.n_experts * (a.P / 256) * (a.Q / 256), st); \

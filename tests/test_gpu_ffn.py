@@ -118,7 +118,8 @@ def test_ffn_fp32_two_sources_and_relu():
     check(case, out, dx, grads, range(4), wscale=4.0)
 
 
-@pytest.mark.parametrize("backend", [1, 2, 3], ids=["cuda_cores", "tcgen05_one_cta", "tcgen05_cta_pair"])
+@pytest.mark.parametrize("backend", [1, 2, 3, 4],
+                         ids=["cuda_cores", "tcgen05_one_cta", "tcgen05_cta_pair", "tcgen05_panel"])
 def test_ffn_bf16(backend):
     case = Case(M=256, F=512, L=8, n_src=1, Cs=256, counts=RAGGED, dtype=torch.bfloat16, seed=1)
     out, dx, grads = run_gpu(case, backend=backend)
@@ -133,7 +134,7 @@ def test_ffn_bf16_tcgen05_narrow_tiles_two_sources():
     check(case, out, dx, grads, range(4))
 
 
-@pytest.mark.parametrize("backend", [2, 3])
+@pytest.mark.parametrize("backend", [2, 3, 4])
 def test_ffn_bf16_four_sources_packed_per_expert(backend):
     """Four source ranks per expert: the tensor-core path packs each expert's rows of all sources
     into one run (rows cross 128-row tile edges inside a source's chunk), computes there and
@@ -156,7 +157,8 @@ def test_ffn_bf16_four_sources_packed_per_expert(backend):
         assert torch.isnan(out_r[:, l].float()).all()
 
 
-def test_ffn_bf16_expert_range_slots_and_accumulate():
+@pytest.mark.parametrize("backend", [0, 4], ids=["default", "tcgen05_panel"])
+def test_ffn_bf16_expert_range_slots_and_accumulate(backend):
     """A record of experts [2, 5) with weights living in permuted slots and gradients
     accumulated onto existing values (the offload pipeline's way of calling the FFN)."""
     from mole_b200 import ops
@@ -166,7 +168,8 @@ def test_ffn_bf16_expert_range_slots_and_accumulate():
     base = [torch.full((8, 256, 256), 0.5), torch.full((8, 256), 0.5),
             torch.full((8, 256, 256), 0.5), torch.full((8, 256), 0.5)]
     grads = [b.bfloat16().cuda() for b in base]
-    out, dx, grads = run_gpu(case, e_begin=2, e_end=5, accumulate=True, slots=slots, grads=grads)
+    out, dx, grads = run_gpu(case, e_begin=2, e_end=5, accumulate=True, slots=slots, grads=grads,
+                             backend=backend)
     for l in (2, 3, 4):
         o_ref, dx_ref, g_ref = case.oracle(l)
         assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
@@ -203,6 +206,11 @@ def test_ffn_bf16_full_size_spot_check():
     assert torch.equal(out[valid], out3[valid]) and torch.equal(dx[valid], dx3[valid])
     for a, b in zip(grads, grads3):
         assert torch.equal(a, b)
+    # the panel kernel (two or three row panels per expert here) sums over K in the same order
+    out4, dx4, grads4 = run_gpu(case, backend=4)
+    assert torch.equal(out[valid], out4[valid]) and torch.equal(dx[valid], dx4[valid])
+    for a, b in zip(grads, grads4):
+        assert torch.equal(a, b)
     for l in (0, 10, 37):
         o_ref, dx_ref, g_ref = case.oracle(l)
         assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
@@ -212,9 +220,10 @@ def test_ffn_bf16_full_size_spot_check():
     assert (grads[0][3] == 0).all() and (grads[2][3] == 0).all()
 
 
-@pytest.mark.parametrize("backend,dtype", [(2, torch.bfloat16), (3, torch.bfloat16), (1, torch.bfloat16),
-                                           (0, torch.float32)],
-                         ids=["tcgen05_one_cta", "tcgen05_cta_pair", "cuda_cores_bf16", "cuda_cores_fp32"])
+@pytest.mark.parametrize("backend,dtype", [(2, torch.bfloat16), (3, torch.bfloat16), (4, torch.bfloat16),
+                                           (1, torch.bfloat16), (0, torch.float32)],
+                         ids=["tcgen05_one_cta", "tcgen05_cta_pair", "tcgen05_panel", "cuda_cores_bf16",
+                              "cuda_cores_fp32"])
 def test_ffn_tanh_gelu_derivative(backend, dtype):
     """The reference's shipped backward: ``USE_MOLE_GELU`` is defined (MOLE/cpp/define.hpp:6), so
     dX1 is multiplied by the tanh-approximation derivative of MOLE/cpp/gelu.cu:3-14 while the
@@ -244,12 +253,14 @@ def test_ffn_bf16_config3_shape_spot_check():
     case = Case(M, F, L, 1, Cs, counts, torch.bfloat16, seed=10)
     out, dx, grads = run_gpu(case)                       # backend 0: picks the one-CTA kernel here
     out3, dx3, grads3 = run_gpu(case, backend=3)
+    out4, dx4, grads4 = run_gpu(case, backend=4)         # panels of 16-row granularity
     valid = torch.zeros(1, L, Cs, dtype=torch.bool)
     for l in range(L):
         valid[0, l, :counts[l]] = True
     assert torch.equal(out[valid], out3[valid]) and torch.equal(dx[valid], dx3[valid])
-    for a, b in zip(grads, grads3):
-        assert torch.equal(a, b)
+    assert torch.equal(out[valid], out4[valid]) and torch.equal(dx[valid], dx4[valid])
+    for a, b, c4 in zip(grads, grads3, grads4):
+        assert torch.equal(a, b) and torch.equal(a, c4)
     for l in (1, 4, 6):
         o_ref, dx_ref, g_ref = case.oracle(l)
         assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
@@ -258,7 +269,7 @@ def test_ffn_bf16_config3_shape_spot_check():
             assert_close(got[l], ref, case.dtype, f"grad {l}")
 
 
-@pytest.mark.parametrize("backend", [2, 3])
+@pytest.mark.parametrize("backend", [2, 3, 4])
 def test_ffn_bf16_rows_packed_by_the_senders(backend):
     """``desc.compact = 3``: x and dout arrive already packed -- expert l's rows of all four source
     ranks in source order at the front of its run ``[l][n_src * Cs]``, pad rows holding garbage --
