@@ -53,9 +53,12 @@ static int single_cta(const mole_ffn_desc* d) {
 static bool compacting(const mole_ffn_desc* d);
 // The panel kernel (weights on the M side of the MMA, an expert's rows on the N side in steps of
 // 16) needs every expert's rows in one run: one source rank, or the compacted layout.
-static int panel_ok(const mole_ffn_desc* d) {
-  if (d->backend != 4) return 0;
-  return d->n_src == 1 || compacting(d);
+static bool contiguous_rows(const mole_ffn_desc* d) { return d->n_src == 1 || compacting(d); }
+static int panel_ok(const mole_ffn_desc* d) { return d->backend == 4 && contiguous_rows(d); }
+// The resident-operand weight gradient: same requirement; measured faster than the tile kernels
+// wherever an expert's rows fit its shared-memory budget (the launch falls back beyond it).
+static int resident_ok(const mole_ffn_desc* d) {
+  return (d->backend == 0 || d->backend == 4) && contiguous_rows(d);
 }
 
 // With several source ranks per expert the tensor-core path first packs each expert's rows of
@@ -229,7 +232,7 @@ static int ffn_fwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   a.e_begin = d->e_begin;
   a.n_experts = d->e_end - d->e_begin;
   a.single_cta = single_cta(d);
-  a.panel = panel_ok(d);
+  a.panel = panel_ok(d); a.max_rows_per_expert = d->n_src * d->Cs;
   // FC1: [rows, M] x W1_e^T ([F, M] read as [N=F][K=M])
   a.A = x; a.W = w1; a.w_nk = 1; a.N = d->F; a.K = d->M; a.bias = b1; a.aux = nullptr;
   a.out0 = x1; a.out1 = h; a.epi = EPI_FC1;
@@ -320,7 +323,7 @@ static int ffn_bwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   g.sched = s; g.gslot = gslot; g.n_slots = n_grad_slots; g.total_rows = total_rows;
   g.accumulate = d->accumulate; g.e_begin = d->e_begin; g.n_experts = n_experts;
   g.P = d->F; g.Q = d->M; g.single_cta = single_cta(d);
-  g.resident = panel_ok(d); g.max_tiles_per_expert = d->n_src * (d->Cs / kTileRows);
+  g.resident = resident_ok(d); g.max_tiles_per_expert = d->n_src * (d->Cs / kTileRows);
   ColsumArgs c{};
   c.sched = s; c.gslot = gslot; c.accumulate = d->accumulate; c.e_begin = d->e_begin;
   c.n_experts = n_experts;
@@ -333,7 +336,7 @@ static int ffn_bwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   a.sched = s; a.wslot = wslot; a.w_expert_stride = (int64_t)d->F * d->M; a.n_slots = d->n_slots;
   a.total_rows = total_rows; a.act = d->act; a.gelu_bwd = d->gelu_bwd;
   a.e_begin = d->e_begin; a.n_experts = n_experts; a.single_cta = single_cta(d);
-  a.panel = panel_ok(d);
+  a.panel = panel_ok(d); a.max_rows_per_expert = d->n_src * d->Cs;
   a.A = dout; a.W = w2; a.w_nk = 1; a.N = d->F; a.K = d->M; a.bias = nullptr; a.aux = x1;
   a.out0 = dx1; a.out1 = nullptr; a.epi = EPI_DACT;
   if (int rc = row_gemm(d, a, st)) return rc;

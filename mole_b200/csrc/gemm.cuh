@@ -32,6 +32,7 @@ struct RowGemmArgs {
   int single_cta;           // tensor cores: keep to the one-CTA kernel (A/B comparisons)
   int panel;                // tensor cores: every expert's rows are one contiguous run and the panel
                             // kernel may take the launch (outputs in place, no fused combine)
+  int max_rows_per_expert;  // bound on an expert's rows (sizes the panel kernel's stages)
   const int32_t* rowmap;    // tensor cores, FC2 / dX: scatter output rows (-1 = drop), or null
   PeerMap peers;            // with rowmap: the scattered rows go to their source ranks (n > 0)
   int peer_Cs;              // rows per chunk of the receive buffers

@@ -2,13 +2,19 @@
 // gemm_tc.cu (it uses that file's PTX wrappers, TcParams and epilogue traits).
 //
 // The tile kernels put 128 rows of an expert on the M side of the MMA: an expert with 264 rows
-// pays for 384.  Here the WEIGHTS are the M operand -- a CTA pair (cta_group::2) takes 256 output
-// features of one expert, 128 per SM, always full -- and the expert's rows are the N operand,
-// whose extent can be any multiple of 16 up to 256: D^T[feature][row] = W[feature][k] * X[row][k].
-// An expert's rows are cut into ceil(rows / 256) panels of equal size (rounded up to 16), so 264
-// rows cost 288 and every weight element crosses shared memory once per panel instead of once
-// per 128-row tile.  Each CTA stages its 128 features of W and half of the panel's rows; the
-// accumulator (128 lanes = features, N columns = rows) is double-buffered in TMEM.
+// pays for 384, and every extra tile streams the expert's weights through shared memory again.
+// The GEMMs run at the rate shared memory can be refilled (bytes in flight / load latency), so
+// what counts is the work done per byte staged.  Here the WEIGHTS are the M operand -- a CTA pair
+// (cta_group::2) takes 256 output features of one expert, 128 per SM, always full -- and the
+// expert's rows are the N operand: D^T[feature][row] = W[feature][k] * X[row][k].  A work item is
+// (expert, 256 features, panel of up to 512 rows): up to 256 rows go into one accumulator
+// (N = rows rounded up to 16), more into two accumulators of equal size (N1 = N2, rows rounded up
+// to 32) that are fed by alternating MMAs from the same staged weights.  264 rows cost 288, and
+// the weights cross shared memory once per expert.
+//
+// TMEM holds 512 columns.  Items alternate between the two ends of it ([0, c) and [512 - c, 512));
+// while the two regions do not overlap, the epilogue of one item runs under the main loop of
+// the next; where they do (c + c' > 512) the issuer first waits for the previous item's drain.
 //
 // The accumulator comes out transposed: a thread of the epilogue owns one feature and reads 16
 // rows of it per tcgen05.ld, and a warp's store instruction writes 32 neighbouring features of
@@ -18,10 +24,7 @@
 // and outputs that stay in place (no row map).
 #pragma once
 
-constexpr int kPanelStages = 6;
-constexpr uint32_t kPanelABytes = 128 * kBK * 2;      // 128 features x 64 K
-constexpr uint32_t kPanelBBytes = 128 * kBK * 2;      // up to 128 rows x 64 K per CTA
-constexpr uint32_t kPanelStageBytes = kPanelABytes + kPanelBBytes;
+constexpr uint32_t kPanelABytes = 128 * kBK * 2;      // 128 features x 64 K per CTA and stage
 
 struct PanelMaps {
   CUtensorMap w;        // weights: box 64 K x 128 features (K-major) or 64 features x 64 K (N-major)
@@ -33,32 +36,38 @@ struct PanelItem {
   int el;          // expert relative to e_begin
   int n0;          // first of the pair's 256 output features
   int row0;        // first row of the panel
-  int n;           // rows of the panel, a multiple of 16 (0: nothing to do)
+  int n1, n2;      // columns of the two accumulators (multiples of 16; n2 may be 0; n1 = 0: nothing to do)
 };
 
-__device__ __forceinline__ PanelItem decode_panel(const TcParams& p, const int* start, const int* pstart, int item) {
+// `istart` = prefix over the experts of their panels, ceil(rows / 512); `start` = expert_tile_start
+__device__ __forceinline__ PanelItem decode_panel(const TcParams& p, const int* start, const int* istart,
+                                                  int item) {
   PanelItem w;
   w.valid = 0;
   const int nb = p.N / 256;
-  if (item >= pstart[p.n_experts] * nb) return w;
+  if (item >= istart[p.n_experts] * nb) return w;
   int lo = 0, hi = p.n_experts;
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
-    if (pstart[mid] * nb <= item) lo = mid; else hi = mid;
+    if (istart[mid] * nb <= item) lo = mid; else hi = mid;
   }
-  // expert_pair_start is the prefix of ceil(tiles / 2) = ceil(rows / 256): the panels per expert
-  const int ps = pstart[lo], np = pstart[lo + 1] - ps;
+  const int ps = istart[lo], np = istart[lo + 1] - ps;
   const int local = item - ps * nb;
   const int pan = local % np;            // panels of a feature block are neighbours: they share W through L2
   const int ts = start[lo], te = start[lo + 1];
   const int rows = (te - ts - 1) * kTileRows + p.tile_rows[te - 1];
-  const int per = (((rows + np - 1) / np) + 15) & ~15;
+  const int per = (((rows + np - 1) / np) + 31) & ~31;      // <= 512
   const int left = rows - pan * per;
   w.valid = 1;
   w.el = lo;
   w.n0 = (local / np) * 256;
   w.row0 = p.tile_row0[ts] + pan * per;
-  w.n = left <= 0 ? 0 : min(per, (left + 15) & ~15);
+  w.n1 = w.n2 = 0;
+  if (left > 0) {
+    const int r = min(per, left);
+    if (r <= 256) w.n1 = (r + 15) & ~15;
+    else w.n1 = w.n2 = ((r + 31) & ~31) >> 1;
+  }
   return w;
 }
 
@@ -68,12 +77,55 @@ __device__ __forceinline__ uint16_t bf16_bits(float v) {
 __device__ __forceinline__ void st_b16(__nv_bfloat16* p, uint16_t v) {
   asm volatile("st.global.b16 [%0], %1;" ::"l"(p), "h"(v) : "memory");
 }
+// One lane polls, the warp gets the answer (or every lane polls: `one` = false).
+__device__ __forceinline__ bool warp_wait(bool one, uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* fault, int code) {
+  if (!one) return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, fault, code));
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, fault, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 
+// The epilogue of 16 rows x one feature per thread; `x1w` = packed pre-activations (dX2)
+template <int EV>
+__device__ __forceinline__ void panel_store16(const TcParams& p, const uint32_t (&r)[16], int64_t off,
+                                              float bias, const uint32_t (&x1w)[8]) {
+  using Ev = EvTraits<EV>;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float v = __uint_as_float(r[i]);
+    const int64_t o = off + (int64_t)i * p.N;
+    if (Ev::epi == EPI_FC1) {
+      const uint16_t x1 = bf16_bits(v + bias);
+      st_b16(p.out0 + o, x1);
+      // the activation is taken of the rounded pre-activation, as backward sees it
+      st_b16(p.out1 + o, bf16_bits(act_fwd_t<Ev::act>(__uint_as_float((uint32_t)x1 << 16))));
+    } else if (Ev::epi == EPI_DACT) {
+      const uint32_t pw = x1w[i >> 1];
+      const float x1 = (i & 1) ? bf16_hi(pw) : bf16_lo(pw);
+      st_b16(p.out0 + o, bf16_bits(v * act_grad_t<Ev::act, Ev::gbwd>(x1)));
+    } else {
+      st_b16(p.out0 + o, bf16_bits(v + bias));
+    }
+  }
+}
+__device__ __forceinline__ void panel_load_x1(const TcParams& p, int64_t off, uint32_t (&x1w)[8]) {
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(p.aux) + off;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t lo = src[(int64_t)(2 * i) * p.N], hi = src[(int64_t)(2 * i + 1) * p.N];
+    x1w[i] = lo | (hi << 16);
+  }
+}
+
+// `stages` x `stage_bytes` of dynamic shared memory: a stage is this CTA's 128 features x 64 K of
+// weights (16 KB) followed by its share of the panel's rows (up to `stage_bytes` - 16 KB).
+constexpr int kPanelMaxStages = 8;
 template <bool W_KMAJOR, int EV>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant__ TcParams p) {
-  constexpr int STAGES = kPanelStages;
-  constexpr uint32_t kTmemCols = 512;                   // two accumulators of up to 256 columns
+panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant__ TcParams p,
+                  const int stages, const uint32_t stage_bytes) {
+  constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kBoxBytes = 128 * kBK;             // one 64-feature box of N-major weights
   // f32 accumulate, bf16 operands, A (weights) K-major or MN-major, B (rows) K-major, M = 256
   constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((W_KMAJOR ? 0u : 1u) << 15) |
@@ -83,30 +135,31 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];
+  __shared__ __align__(8) uint64_t bars[2 * kPanelMaxStages + 5];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
-  __shared__ int start_s[kMaxLocalExperts + 1], pstart_s[kMaxLocalExperts + 1];    // see decode_item
+  __shared__ int start_s[kMaxLocalExperts + 1], istart_s[kMaxLocalExperts + 1];    // see decode_item
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
-  const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
-  const uint32_t drain0 = smem_u32(&bars[2 * STAGES + 4]);      // used only after an abort
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kPanelMaxStages]);
+  const uint32_t tfull0 = smem_u32(&bars[2 * kPanelMaxStages]), tempty0 = smem_u32(&bars[2 * kPanelMaxStages + 2]);
+  const uint32_t drain0 = smem_u32(&bars[2 * kPanelMaxStages + 4]);      // used only after an abort
   const uint32_t smem_base = smem_u32(smem);
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int nkb = p.K / kBK;
 
   for (int i = threadIdx.x; i <= p.n_experts; i += kThreads) {
     start_s[i] = p.expert_tile_start[i];
-    pstart_s[i] = p.expert_pair_start[i];
+    istart_s[i] = p.expert_pair_start[i];        // turned into the prefix of panels below
   }
+  __syncthreads();
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
     mbar_init(drain0, 1);
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < kPanelMaxStages; ++s) {
       mbar_init(full0 + 8 * s, 1);               // the even CTA's arrive.expect_tx
       mbar_init(empty0 + 8 * s, 1);              // one multicast commit
     }
@@ -115,6 +168,15 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
       mbar_init(tempty0 + 8 * a, 2 * kEpiWarps); // epilogue warps of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // panels per expert: ceil(pairs of tiles / 2) = ceil(rows / 512)
+    int run = 0, lo = istart_s[0];
+    for (int e = 0; e < p.n_experts; ++e) {
+      const int hi = istart_s[e + 1];
+      istart_s[e] = run;
+      run += (hi - lo + 1) >> 1;
+      lo = hi;
+    }
+    istart_s[p.n_experts] = run;
   }
   __syncthreads();
   if (warp == 1) {
@@ -129,76 +191,103 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs, whole warp) --------------
-    // A stage is one or two weight boxes and the CTA's half of the panel's rows, cut into boxes
-    // of 64, 32, 16 and 8 rows; each box is issued by its own lane so they leave together.
+    // A stage is one or two weight boxes and the CTA's share of the panel's rows -- half of each
+    // accumulator's rows, cut into boxes of 64, 32, 16 and 8 rows; every box has its own lane.
     int stage = 0;
     uint32_t phase = 0, issued = 0;
     bool ok = true;
     for (int item = cluster_id; ok; item += n_clusters) {
-      const PanelItem w = decode_panel(p, start_s, pstart_s, item);
+      const PanelItem w = decode_panel(p, start_s, istart_s, item);
       if (!w.valid) break;
-      if (w.n == 0) continue;
+      if (w.n1 == 0) continue;
       const int slot = p.slot.s[p.e_begin + w.el];
-      const int half = w.n >> 1;                       // rows this CTA stages (a multiple of 8)
-      const uint32_t tx = 2u * (kPanelABytes + (uint32_t)half * 128u);
+      const int h1 = w.n1 >> 1, h2 = w.n2 >> 1;          // rows this CTA stages per accumulator
+      const uint32_t tx = 2u * (kPanelABytes + (uint32_t)(h1 + h2) * 128u);
       const int f0 = w.n0 + 128 * (int)rank;           // this CTA's features
-      const int r0 = w.row0 + half * (int)rank;        // this CTA's rows
-      // what this lane loads in every stage of the item
-      int kind = -1, off = 0;                          // kind 0..3: row box of 64 >> kind rows at row offset `off`
-      const int n64 = half >> 6, rem = half & 63;
-      if (lane >= 2 && lane < 4) { if (lane - 2 < n64) { kind = 0; off = 64 * (lane - 2); } }
-      else if (lane == 4) { if (rem & 32) { kind = 1; off = 64 * n64; } }
-      else if (lane == 5) { if (rem & 16) { kind = 2; off = 64 * n64 + (rem & 32); } }
-      else if (lane == 6) { if (rem & 8) { kind = 3; off = 64 * n64 + (rem & 48); } }
+      // what this lane loads in every stage of the item: lanes 2..6 the first accumulator's rows,
+      // lanes 7..11 the second's
+      int kind = -1, off = 0, srow = 0;                // kind 0..3: a box of 64 >> kind rows
+      {
+        const int part = lane >= 7 ? 1 : 0;
+        const int l = lane - (part ? 7 : 2);           // 0, 1: boxes of 64; 2, 3, 4: 32, 16, 8
+        const int h = part ? h2 : h1;
+        const int n64 = h >> 6, rem = h & 63;
+        if (lane >= 2 && lane < 12) {
+          if (l < 2) { if (l < n64) { kind = 0; off = 64 * l; } }
+          else if (l == 2) { if (rem & 32) { kind = 1; off = 64 * n64; } }
+          else if (l == 3) { if (rem & 16) { kind = 2; off = 64 * n64 + (rem & 32); } }
+          else { if (rem & 8) { kind = 3; off = 64 * n64 + (rem & 48); } }
+        }
+        // accumulator 1 holds the panel's rows [0, n1), accumulator 2 rows [n1, n1 + n2); this CTA
+        // supplies the lower (rank 0) or upper half of each
+        srow = w.row0 + (part ? w.n1 + h2 * (int)rank : h1 * (int)rank) + off;
+        off += part ? h1 : 0;                          // position in the stage's row area
+      }
       for (int kb = 0; kb < nkb; ++kb) {
-        ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 21));
+        ok = warp_wait(false, empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 21);
         if (!ok) break;
         const uint32_t bar = (full0 + 8 * stage) & kPeerMask;     // the even CTA's barrier
-        const uint32_t sa = smem_base + stage * kPanelStageBytes, sb = sa + kPanelABytes;
+        const uint32_t sa = smem_base + stage * stage_bytes, sb = sa + kPanelABytes;
         if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, tx);
         if (W_KMAJOR) {
           if (lane == 0) tma2_load_3d(sa, &maps.w, bar, kb * kBK, f0, slot);
         } else {
           if (lane < 2) tma2_load_3d(sa + lane * kBoxBytes, &maps.w, bar, f0 + 64 * lane, kb * kBK, slot);
         }
-        if (kind >= 0) tma2_load_2d(sb + off * 128, &maps.x[kind], bar, kb * kBK, r0 + off);
+        if (kind >= 0) tma2_load_2d(sb + off * 128, &maps.x[kind], bar, kb * kBK, srow);
         ++issued;
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == stages) { stage = 0; phase ^= 1; }
       }
     }
     // both CTAs' loads complete on the even CTA's barriers: it waits for the pair
-    if (leader && lane == 0 && *abort_flag) drain_loads(full0, STAGES, issued);
+    if (leader && lane == 0 && *abort_flag) drain_loads(full0, stages, issued);
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (even CTA only) -----------------------
     if (lane == 0 && leader) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      int stage = 0, acc = 0, c_prev = 0;
+      uint32_t phase = 0, aph0 = 0, aph1 = 0;           // phase of each end's barriers
       bool ok = true;
       for (int item = cluster_id; ok; item += n_clusters) {
-        const PanelItem w = decode_panel(p, start_s, pstart_s, item);
+        const PanelItem w = decode_panel(p, start_s, istart_s, item);
         if (!w.valid) break;
-        if (w.n == 0) continue;
-        if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 22))) break;
+        if (w.n1 == 0) continue;
+        const int c = w.n1 + w.n2;
+        if (!(ok = mbar_wait(tempty0 + 8 * acc, (acc ? aph1 : aph0) ^ 1, abort_flag, p.fault, 22))) break;
+        // the previous item sits at the other end of TMEM: wait for its drain if the two overlap
+        if (c + c_prev > (int)kTmemCols &&
+            !(ok = mbar_wait(tempty0 + 8 * (acc ^ 1), (acc ? aph0 : aph1) ^ 1, abort_flag, p.fault, 22))) break;
         tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * 256;
-        const uint32_t idesc = kIdescBase | ((uint32_t)(w.n >> 3) << 17);
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!(ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 23))) break;
-          tcgen05_fence_after();
-          const uint32_t sa = smem_base + stage * kPanelStageBytes, sb = sa + kPanelABytes;
+        const uint32_t d_tmem = tmem_base + (acc ? kTmemCols - c : 0);
+        const uint32_t idesc1 = kIdescBase | ((uint32_t)(w.n1 >> 3) << 17);
+        const uint32_t idesc2 = kIdescBase | ((uint32_t)(w.n2 >> 3) << 17);
+        const uint32_t b2off = (uint32_t)(w.n1 >> 1) * 128u;
+        // the two forms of the K loop are separate straight-line code: a branch between the MMAs of
+        // a stage slows their issue
+        auto k_loop = [&](auto dual) {
+          for (int kb = 0; kb < nkb; ++kb) {
+            if (!(ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 23))) break;
+            tcgen05_fence_after();
+            const uint32_t sa = smem_base + stage * stage_bytes, sb = sa + kPanelABytes;
 #pragma unroll
-          for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
-            const uint64_t ad = W_KMAJOR ? make_desc(sa + ks * (kUmmaK * 2), 16, 1024)
-                                         : make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024);
-            const uint64_t bd = make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
-            tcgen05_mma2_bf16(d_tmem, ad, bd, idesc, (kb | ks) ? 1u : 0u);
+            for (int ks = 0; ks < kBK / kUmmaK; ++ks) {
+              const uint64_t ad = W_KMAJOR ? make_desc(sa + ks * (kUmmaK * 2), 16, 1024)
+                                           : make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024);
+              tcgen05_mma2_bf16(d_tmem, ad, make_desc(sb + ks * (kUmmaK * 2), 16, 1024), idesc1,
+                                (kb | ks) ? 1u : 0u);
+              if (decltype(dual)::value)
+                tcgen05_mma2_bf16(d_tmem + w.n1, ad, make_desc(sb + b2off + ks * (kUmmaK * 2), 16, 1024),
+                                  idesc2, (kb | ks) ? 1u : 0u);
+            }
+            tcgen05_commit2(empty0 + 8 * stage);
+            if (++stage == stages) { stage = 0; phase ^= 1; }
           }
-          tcgen05_commit2(empty0 + 8 * stage);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
+        };
+        if (w.n2) k_loop(std::true_type{}); else k_loop(std::false_type{});
         if (!ok) break;
         tcgen05_commit2(tfull0 + 8 * acc);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (acc) aph1 ^= 1; else aph0 ^= 1;
+        acc ^= 1;
+        c_prev = c;
       }
       if (*abort_flag) {                      // MMAs already issued retire before the TMEM goes
         tcgen05_commit2(drain0);
@@ -211,67 +300,43 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
     const int quarter = warp & 3;
     const int grp = (warp - 2) >> 2;
     int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t aph0 = 0, aph1 = 0;                      // phase of each end's barriers
     for (int item = cluster_id;; item += n_clusters) {
-      const PanelItem w = decode_panel(p, start_s, pstart_s, item);
+      const PanelItem w = decode_panel(p, start_s, istart_s, item);
       if (!w.valid) break;
-      if (w.n == 0) continue;
+      if (w.n1 == 0) continue;
+      const int c = w.n1 + w.n2;
       const int slot = p.slot.s[p.e_begin + w.el];
       const int f = w.n0 + 128 * (int)rank + 32 * quarter + lane;
       const int64_t obase = (int64_t)w.row0 * p.N + f;         // element (row0, f) of the outputs
       float bias = 0.f;
       if (Ev::bias) bias = __bfloat162float(p.bias[(int64_t)slot * p.N + f]);
-      // dX2: the pre-activations of this thread's (feature, rows), fetched before the wait
-      uint32_t pre[4][8];
-      if (Ev::epi == EPI_DACT) {
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const int c0 = (grp + 4 * jj) * 16;
-          if (c0 < w.n) {
-            const uint16_t* src = reinterpret_cast<const uint16_t*>(p.aux) + obase + (int64_t)c0 * p.N;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const uint32_t lo = src[(int64_t)(2 * i) * p.N], hi = src[(int64_t)(2 * i + 1) * p.N];
-              pre[jj][i] = lo | (hi << 16);
-            }
-          }
-        }
-      }
-      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.fault, 24)))
+      // dX2: the pre-activations of the thread's next chunk are in flight while it works on one;
+      // the first chunk's are fetched before the wait for the accumulator
+      int c0 = grp * 16;
+      uint32_t cur[8];
+      if (Ev::epi == EPI_DACT && c0 < c) panel_load_x1(p, obase + (int64_t)c0 * p.N, cur);
+      if (!warp_wait(false, tfull0 + 8 * acc, acc ? aph1 : aph0, abort_flag, p.fault, 24))
         break;                                        // nothing is stored for this item
       tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (acc ? kTmemCols - c : 0);
+      for (; c0 < c; c0 += 64) {                      // warp-uniform
+        uint32_t nxt[8];
+        if (Ev::epi == EPI_DACT && c0 + 64 < c) panel_load_x1(p, obase + (int64_t)(c0 + 64) * p.N, nxt);
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+        panel_store16<EV>(p, r, obase + (int64_t)c0 * p.N, bias, cur);
+        if (Ev::epi == EPI_DACT) {
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int c0 = (grp + 4 * jj) * 16;
-        if (c0 < w.n) {                               // warp-uniform
-          uint32_t r[16];
-          tmem_ld16(taddr + c0, r);
-          tmem_ld_wait();
-          __nv_bfloat16* o0 = p.out0 + obase + (int64_t)c0 * p.N;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float v = __uint_as_float(r[i]);
-            if (Ev::epi == EPI_FC1) {
-              const uint16_t x1 = bf16_bits(v + bias);
-              st_b16(o0 + (int64_t)i * p.N, x1);
-              // the activation is taken of the rounded pre-activation, as backward sees it
-              st_b16(p.out1 + obase + (int64_t)(c0 + i) * p.N,
-                     bf16_bits(act_fwd_t<Ev::act>(__uint_as_float((uint32_t)x1 << 16))));
-            } else if (Ev::epi == EPI_DACT) {
-              const uint32_t pw = pre[jj][i >> 1];
-              const float x1 = (i & 1) ? bf16_hi(pw) : bf16_lo(pw);
-              st_b16(o0 + (int64_t)i * p.N, bf16_bits(v * act_grad_t<Ev::act, Ev::gbwd>(x1)));
-            } else {
-              st_b16(o0 + (int64_t)i * p.N, bf16_bits(v + bias));
-            }
-          }
+          for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
         }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster((tempty0 + 8 * acc) & kPeerMask);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (acc) aph1 ^= 1; else aph0 ^= 1;
+      acc ^= 1;
     }
   }
 
@@ -302,14 +367,6 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
 // Barriers as in tc2_gemm_kernel, plus bfull (resident operand landed; armed by the even CTA,
 // completed by both CTAs' loads) and bfree (every MMA that reads the resident operand has
 // retired; a multicast commit).
-// One lane polls, the warp gets the answer.
-__device__ __forceinline__ bool warp_wait(bool one, uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* fault, int code) {
-  if (!one) return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, fault, code));
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, fault, code) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
 constexpr int kResTotalStages = 12;
 constexpr uint32_t kResStageBytes = 128 * kWBK * 2;      // 16 KB: 64 rows x 128 columns, two boxes
 
@@ -440,12 +497,8 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (ok) {
               const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
               const uint32_t sa = ring_base + stage * kResStageBytes;
-              if (p.dbg & 8) {
-                if (leader && lane == 0) mbar_arrive(full0 + 8 * stage);
-              } else {
-                if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, 2u * kResStageBytes);
-                if (lane < 2) tma2_load_2d(sa + lane * kBoxBytes, &tmap_a, bar, ph, w.row0 + s * kWBK);
-              }
+              if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, 2u * kResStageBytes);
+              if (lane < 2) tma2_load_2d(sa + lane * kBoxBytes, &tmap_a, bar, ph, w.row0 + s * kWBK);
               ++issued;
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -483,13 +536,18 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 tcgen05_fence_after();
                 const uint32_t sa = ring_base + stage * kResStageBytes;
                 const uint32_t sb = res_base + s * kResStageBytes;
+                // a full stage is straight-line code: a branch between the MMAs slows their issue
+                if (ksteps == kWBK / kUmmaK) {
 #pragma unroll
-                for (int ks = 0; ks < kWBK / kUmmaK; ++ks) {
-                  if (ks < ksteps && !((p.dbg & 2) && !(s == 0 && ks == 0))) {
-                    const uint64_t ad = make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024);
-                    const uint64_t bd = make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024);
-                    tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (s == 0 && ks == 0) ? 0u : 1u);
-                  }
+                  for (int ks = 0; ks < kWBK / kUmmaK; ++ks)
+                    tcgen05_mma2_bf16(d_tmem, make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024),
+                                      make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024), kIdesc,
+                                      (s == 0 && ks == 0) ? 0u : 1u);
+                } else {
+                  for (int ks = 0; ks < ksteps; ++ks)
+                    tcgen05_mma2_bf16(d_tmem, make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024),
+                                      make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024), kIdesc,
+                                      (s == 0 && ks == 0) ? 0u : 1u);
                 }
                 tcgen05_commit2(empty0 + 8 * stage);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -534,10 +592,9 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         using Ev = EvTraits<EV>;
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
-        if (p.dbg & 4) {
-        } else if (EV == EV_WGRAD)
+        if (EV == EV_WGRAD)
           epilogue_lines<NSTEPS>(p.out0, obase - (int64_t)lane * p.N, p.N, taddr, empty, cq * 64,
-                                 store_strip[ew], !(p.dbg & 1));
+                                 store_strip[ew]);
         else
           epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
               p, taddr, empty, true, p.out0, obase, nullptr, cq * 64, pre, nullptr);

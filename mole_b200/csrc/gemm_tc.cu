@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "gemm.cuh"
@@ -265,7 +266,6 @@ struct TcParams {
   const float* c_gates;
   __nv_bfloat16* c_y;          // null: no fused combine
   int c_k, c_Cs;
-  int dbg;
 };
 
 // y[0..7] (eight bf16 pairs = 16 columns) += v, as two 16-byte reductions at L2.  With k <= 2 a
@@ -528,7 +528,7 @@ constexpr int kStripBytes = 2048;
 template <int NSTEPS>
 __device__ __forceinline__ void epilogue_lines(__nv_bfloat16* out, int64_t warp_base, int ldo,
                                                uint32_t taddr, bool empty, int c_begin,
-                                               uint8_t* strip, bool store = true) {
+                                               uint8_t* strip) {
   constexpr int kRowBytes = NSTEPS * 32;
   constexpr int kRows = kStripBytes / kRowBytes;      // rows per pass
   constexpr int kPasses = 32 / kRows;
@@ -571,7 +571,7 @@ __device__ __forceinline__ void epilogue_lines(__nv_bfloat16* out, int64_t warp_
       const uint4 lo = *reinterpret_cast<const uint4*>(row + (((2 * ra) ^ (rr & kMask)) << 4));
       const uint4 hi = *reinterpret_cast<const uint4*>(row + (((2 * ra + 1) ^ (rr & kMask)) << 4));
       const uint32_t v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-      if (store) st_v8(out + warp_base + (int64_t)(kRows * j + rr) * ldo + c_begin + kEpiStep * ra, v);
+      st_v8(out + warp_base + (int64_t)(kRows * j + rr) * ldo + c_begin + kEpiStep * ra, v);
     }
     if (j + 1 < kPasses) __syncwarp();
   }
@@ -752,15 +752,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (!ok || !(ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 3))) return;
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
+          auto mma_step = [&](int ks) {
+            const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024)
+                                     : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
+            const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024)
+                                     : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
+            tcgen05_mma_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
+          };
+          // a full stage is straight-line code: a branch between the MMAs of a stage slows their
+          // issue (measured: the same MMAs behind a run-time condition each took 30 % longer)
+          if (ksteps == KR / kUmmaK) {
 #pragma unroll
-          for (int ks = 0; ks < KR / kUmmaK; ++ks) {
-            if (ks < ksteps) {
-              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024)
-                                       : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
-              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024)
-                                       : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
-              tcgen05_mma_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
-            }
+            for (int ks = 0; ks < KR / kUmmaK; ++ks) mma_step(ks);
+          } else {
+            for (int ks = 0; ks < ksteps; ++ks) mma_step(ks);
           }
           tcgen05_commit(empty0 + 8 * stage);         // frees the smem stage when the MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -1121,15 +1126,18 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           if (!ok || !(ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 13))) return;
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStage2Bytes, sb = sa + kABytes;
+          auto mma_step = [&](int ks) {
+            const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024)
+                                     : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
+            const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024)
+                                     : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
+            tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
+          };
+          if (ksteps == KR / kUmmaK) {                // straight-line, see tc_gemm_kernel
 #pragma unroll
-          for (int ks = 0; ks < KR / kUmmaK; ++ks) {
-            if (ks < ksteps) {
-              const uint64_t ad = A_MN ? make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024)
-                                       : make_desc(sa + ks * (kUmmaK * 2), 16, 1024);
-              const uint64_t bd = B_MN ? make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024)
-                                       : make_desc(sb + ks * (kUmmaK * 2), 16, 1024);
-              tcgen05_mma2_bf16(d_tmem, ad, bd, kIdesc, (first && ks == 0) ? 0u : 1u);
-            }
+            for (int ks = 0; ks < KR / kUmmaK; ++ks) mma_step(ks);
+          } else {
+            for (int ks = 0; ks < ksteps; ++ks) mma_step(ks);
           }
           tcgen05_commit2(empty0 + 8 * stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -1382,15 +1390,22 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
 }
 
 // Launch of the panel kernel: as launch_tc2, one work unit = (expert, 256 features, row panel).
+// `max_rows` bounds an expert's rows: it sizes the row area of a shared-memory stage.
 template <bool W_KMAJOR, int EV>
-static int launch_panel(const PanelMaps& maps, const TcParams& p, int max_items, cudaStream_t st) {
-  constexpr size_t smem = (size_t)kPanelStages * kPanelStageBytes + 1024;
+static int launch_panel(const PanelMaps& maps, const TcParams& p, int max_items, int max_rows,
+                        cudaStream_t st) {
+  const int n_max = max_rows > 512 ? 512 : (max_rows <= 256 ? ((max_rows + 15) & ~15) : ((max_rows + 31) & ~31));
+  const uint32_t stage_bytes = kPanelABytes + (uint32_t)(n_max / 2) * 128u;
+  constexpr size_t kBudget = 224 * 1024;
+  int stages = (int)((kBudget - 1024) / stage_bytes);
+  if (stages > kPanelMaxStages) stages = kPanelMaxStages;
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
   auto kern = panel_gemm_kernel<W_KMAJOR, EV>;
   static PerDeviceInt max_clusters_of;
   const int dev = current_device();
   int max_clusters = (int)max_clusters_of.get(dev);
   if (max_clusters == 0) {
-    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOLE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBudget));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (sm_count() / 2));
     cfg.blockDim = dim3(kThreads);
@@ -1411,7 +1426,7 @@ static int launch_panel(const PanelMaps& maps, const TcParams& p, int max_items,
   int clusters = max_clusters < max_items ? max_clusters : max_items;
   if (clusters <= 0) return MOLE_OK;
   if (profile_enabled()) profile_begin(st, p.epi);
-  kern<<<2 * clusters, kThreads, smem, st>>>(maps, p);
+  kern<<<2 * clusters, kThreads, smem, st>>>(maps, p, stages, stage_bytes);
   if (profile_enabled()) profile_end(st);
   MOLE_LAUNCH_OK();
   return MOLE_OK;
@@ -1467,7 +1482,6 @@ static int launch_res(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
 }
 
 static void fill_sched(TcParams& p, const Schedule& s) {
-  { const char* v = getenv("MOLE_DBG"); p.dbg = v ? atoi(v) : 0; }
   p.n_tiles = s.n_tiles;
   p.expert_tile_start = s.expert_tile_start;
   p.tile_row0 = s.tile_row0;
@@ -1542,7 +1556,7 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   if (panel) pm.w = mb;
   // one kernel per (operand layout, tile shape, epilogue variant)
 #define MOLE_ROWS(KM, EV)                                                                    \
-  return panel ? launch_panel<KM, EV>(pm, p, max_items, st)                                  \
+  return panel ? launch_panel<KM, EV>(pm, p, max_items, a.max_rows_per_expert, st)                               \
          : pair ? launch_tc2<TC_ROWS, KM, EV>(ma, mb, p, max_items, st)                      \
               : BN == 256 ? launch_tc<TC_ROWS, KM, 256, EV>(ma, mb, p, max_items, st)        \
                           : launch_tc<TC_ROWS, KM, 128, EV>(ma, mb, p, max_items, st)
