@@ -39,13 +39,17 @@ struct PanelItem {
   int n1, n2;      // columns of the two accumulators (multiples of 16; n2 may be 0; n1 = 0: nothing to do)
 };
 
-// `istart` = prefix over the experts of their panels, ceil(rows / 512); `start` = expert_tile_start
+// Experts are visited in the order of falling row counts (`order`, built once per CTA): items of
+// more than 256 rows cost about 1.3 of the others, and a launch may have only half a dozen items
+// per cluster, so the round-robin assignment must deal both kinds out evenly.
+// `istart` = prefix over the ORDERED experts of their panels, ceil(rows / 512); `start` =
+// expert_tile_start (by expert).
 __device__ __forceinline__ PanelItem decode_panel(const TcParams& p, const int* start, const int* istart,
-                                                  int item) {
+                                                  const uint8_t* order, int item) {
   PanelItem w;
   w.valid = 0;
   const int nb = p.N / 256;
-  if (item >= istart[p.n_experts] * nb) return w;
+  if (item < 0 || item >= istart[p.n_experts] * nb) return w;
   int lo = 0, hi = p.n_experts;
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -54,12 +58,13 @@ __device__ __forceinline__ PanelItem decode_panel(const TcParams& p, const int* 
   const int ps = istart[lo], np = istart[lo + 1] - ps;
   const int local = item - ps * nb;
   const int pan = local % np;            // panels of a feature block are neighbours: they share W through L2
-  const int ts = start[lo], te = start[lo + 1];
+  const int e = order[lo];
+  const int ts = start[e], te = start[e + 1];
   const int rows = (te - ts - 1) * kTileRows + p.tile_rows[te - 1];
   const int per = (((rows + np - 1) / np) + 31) & ~31;      // <= 512
   const int left = rows - pan * per;
   w.valid = 1;
-  w.el = lo;
+  w.el = e;
   w.n0 = (local / np) * 256;
   w.row0 = p.tile_row0[ts] + pan * per;
   w.n1 = w.n2 = 0;
@@ -70,6 +75,8 @@ __device__ __forceinline__ PanelItem decode_panel(const TcParams& p, const int* 
   }
   return w;
 }
+// Columns of an item without reading its rows' position: what the epilogue needs of the NEXT item
+__device__ __forceinline__ int panel_cols(const PanelItem& w) { return w.valid ? w.n1 + w.n2 : 0; }
 
 __device__ __forceinline__ uint16_t bf16_bits(float v) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(v));
@@ -135,10 +142,12 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ __align__(8) uint64_t bars[2 * kPanelMaxStages + 5];
+  __shared__ __align__(8) uint64_t bars[2 * kPanelMaxStages + 7];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
   __shared__ int start_s[kMaxLocalExperts + 1], istart_s[kMaxLocalExperts + 1];    // see decode_item
+  __shared__ int pairs_s[kMaxLocalExperts + 1];
+  __shared__ uint8_t order_s[kMaxLocalExperts];
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -147,13 +156,25 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kPanelMaxStages]);
   const uint32_t tfull0 = smem_u32(&bars[2 * kPanelMaxStages]), tempty0 = smem_u32(&bars[2 * kPanelMaxStages + 2]);
   const uint32_t drain0 = smem_u32(&bars[2 * kPanelMaxStages + 4]);      // used only after an abort
+  const uint32_t tovl0 = smem_u32(&bars[2 * kPanelMaxStages + 5]);       // overlap columns drained
   const uint32_t smem_base = smem_u32(smem);
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int nkb = p.K / kBK;
 
   for (int i = threadIdx.x; i <= p.n_experts; i += kThreads) {
     start_s[i] = p.expert_tile_start[i];
-    istart_s[i] = p.expert_pair_start[i];        // turned into the prefix of panels below
+    pairs_s[i] = p.expert_pair_start[i];
+  }
+  __syncthreads();
+  // rank of every expert by falling number of tile pairs (ties: by index): its place in the order
+  for (int e = threadIdx.x; e < p.n_experts; e += kThreads) {
+    const int mine = pairs_s[e + 1] - pairs_s[e];
+    int rk = 0;
+    for (int o = 0; o < p.n_experts; ++o) {
+      const int other = pairs_s[o + 1] - pairs_s[o];
+      rk += (other > mine) || (other == mine && o < e);
+    }
+    order_s[rk] = (uint8_t)e;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -166,15 +187,15 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8 * a, 1);
       mbar_init(tempty0 + 8 * a, 2 * kEpiWarps); // epilogue warps of both CTAs
+      mbar_init(tovl0 + 8 * a, 2 * kEpiWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    // panels per expert: ceil(pairs of tiles / 2) = ceil(rows / 512)
-    int run = 0, lo = istart_s[0];
-    for (int e = 0; e < p.n_experts; ++e) {
-      const int hi = istart_s[e + 1];
-      istart_s[e] = run;
-      run += (hi - lo + 1) >> 1;
-      lo = hi;
+    // panels per expert, in the order: ceil(pairs of tiles / 2) = ceil(rows / 512)
+    int run = 0;
+    for (int i = 0; i < p.n_experts; ++i) {
+      const int e = order_s[i];
+      istart_s[i] = run;
+      run += (pairs_s[e + 1] - pairs_s[e] + 1) >> 1;
     }
     istart_s[p.n_experts] = run;
   }
@@ -197,7 +218,7 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
     uint32_t phase = 0, issued = 0;
     bool ok = true;
     for (int item = cluster_id; ok; item += n_clusters) {
-      const PanelItem w = decode_panel(p, start_s, istart_s, item);
+      const PanelItem w = decode_panel(p, start_s, istart_s, order_s, item);
       if (!w.valid) break;
       if (w.n1 == 0) continue;
       const int slot = p.slot.s[p.e_begin + w.el];
@@ -248,14 +269,15 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
       uint32_t phase = 0, aph0 = 0, aph1 = 0;           // phase of each end's barriers
       bool ok = true;
       for (int item = cluster_id; ok; item += n_clusters) {
-        const PanelItem w = decode_panel(p, start_s, istart_s, item);
+        const PanelItem w = decode_panel(p, start_s, istart_s, order_s, item);
         if (!w.valid) break;
         if (w.n1 == 0) continue;
         const int c = w.n1 + w.n2;
         if (!(ok = mbar_wait(tempty0 + 8 * acc, (acc ? aph1 : aph0) ^ 1, abort_flag, p.fault, 22))) break;
-        // the previous item sits at the other end of TMEM: wait for its drain if the two overlap
+        // the previous item sits at the other end of TMEM: if the two overlap, wait until its
+        // epilogue has drained the columns they share (it takes those first)
         if (c + c_prev > (int)kTmemCols &&
-            !(ok = mbar_wait(tempty0 + 8 * (acc ^ 1), (acc ? aph0 : aph1) ^ 1, abort_flag, p.fault, 22))) break;
+            !(ok = mbar_wait(tovl0 + 8 * (acc ^ 1), (acc ? aph0 : aph1) ^ 1, abort_flag, p.fault, 22))) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (acc ? kTmemCols - c : 0);
         const uint32_t idesc1 = kIdescBase | ((uint32_t)(w.n1 >> 3) << 17);
@@ -302,7 +324,7 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
     int acc = 0;
     uint32_t aph0 = 0, aph1 = 0;                      // phase of each end's barriers
     for (int item = cluster_id;; item += n_clusters) {
-      const PanelItem w = decode_panel(p, start_s, istart_s, item);
+      const PanelItem w = decode_panel(p, start_s, istart_s, order_s, item);
       if (!w.valid) break;
       if (w.n1 == 0) continue;
       const int c = w.n1 + w.n2;
@@ -311,25 +333,47 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
       const int64_t obase = (int64_t)w.row0 * p.N + f;         // element (row0, f) of the outputs
       float bias = 0.f;
       if (Ev::bias) bias = __bfloat162float(p.bias[(int64_t)slot * p.N + f]);
-      // dX2: the pre-activations of the thread's next chunk are in flight while it works on one;
-      // the first chunk's are fetched before the wait for the accumulator
-      int c0 = grp * 16;
+      // Columns [ov_lo, ov_hi) of this item (local numbering) are where the next item's
+      // accumulators will sit: they are drained first and released on their own barrier.
+      int ov_lo = 0, ov_hi = 0;
+      {
+        const int c_next = panel_cols(decode_panel(p, start_s, istart_s, order_s, item + n_clusters));
+        if (c + c_next > (int)kTmemCols) {
+          if (acc) { ov_lo = 0; ov_hi = c + c_next - (int)kTmemCols; }
+          else { ov_lo = (int)kTmemCols - c_next; ov_hi = c; }
+        }
+      }
+      // dX2: the pre-activations of the first chunk this warp will take are fetched before the
+      // wait for the accumulator
+      int first = grp * 16;
+      if (ov_hi > ov_lo) {
+        const int k0 = ov_lo >> 4;                            // first chunk of the shared columns
+        const int c_in = (k0 + ((grp - k0) & 3)) * 16;        // this group's first chunk at or after it
+        if (c_in < ov_hi) first = c_in;
+      }
       uint32_t cur[8];
-      if (Ev::epi == EPI_DACT && c0 < c) panel_load_x1(p, obase + (int64_t)c0 * p.N, cur);
+      bool fresh = false;                                     // cur holds chunk `first`
+      if (Ev::epi == EPI_DACT && first < c) { panel_load_x1(p, obase + (int64_t)first * p.N, cur); fresh = true; }
       if (!warp_wait(false, tfull0 + 8 * acc, acc ? aph1 : aph0, abort_flag, p.fault, 24))
         break;                                        // nothing is stored for this item
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (acc ? kTmemCols - c : 0);
-      for (; c0 < c; c0 += 64) {                      // warp-uniform
-        uint32_t nxt[8];
-        if (Ev::epi == EPI_DACT && c0 + 64 < c) panel_load_x1(p, obase + (int64_t)(c0 + 64) * p.N, nxt);
-        uint32_t r[16];
-        tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
-        panel_store16<EV>(p, r, obase + (int64_t)c0 * p.N, bias, cur);
-        if (Ev::epi == EPI_DACT) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+#pragma unroll 1
+      for (int pass = 0; pass < 2; ++pass) {
+        for (int c0 = grp * 16; c0 < c; c0 += 64) {   // warp-uniform
+          const bool inside = c0 >= ov_lo && c0 < ov_hi;
+          if (inside != (pass == 0)) continue;
+          if (Ev::epi == EPI_DACT && !(fresh && c0 == first)) panel_load_x1(p, obase + (int64_t)c0 * p.N, cur);
+          fresh = false;
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+          panel_store16<EV>(p, r, obase + (int64_t)c0 * p.N, bias, cur);
+        }
+        if (pass == 0) {                              // the shared columns are free
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster((tovl0 + 8 * acc) & kPeerMask);
         }
       }
       tcgen05_fence_before();
@@ -360,14 +404,16 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
 // rows of the expert, 128 columns per CTA -- in shared memory while it walks down the expert's
 // p-blocks of 256, streaming only A: operand bytes per output tile drop from 240 KB to ~85 KB.
 //
-//   shared memory per CTA: RES resident stages of 64 rows x 128 q (16 KB each) + a ring of
-//   12 - RES stages of 64 rows x 128 p (16 KB each); an expert may have at most RES 64-row
-//   stages (the host checks the bound and falls back to the tile kernel beyond it).
+//   shared memory per CTA: twelve stages of 64 rows x 128 columns (16 KB each).  A unit's resident
+//   operand takes as many as the expert has 64-row stages (at most eight; the host checks the
+//   bound and falls back to the tile kernel beyond it), the ring of the streamed operand the
+//   rest: the loads in flight, which set the kernel's pace, get every byte that is left.
 //
 // Barriers as in tc2_gemm_kernel, plus bfull (resident operand landed; armed by the even CTA,
 // completed by both CTAs' loads) and bfree (every MMA that reads the resident operand has
 // retired; a multicast commit).
 constexpr int kResTotalStages = 12;
+constexpr int kResMaxResident = 8;
 constexpr uint32_t kResStageBytes = 128 * kWBK * 2;      // 16 KB: 64 rows x 128 columns, two boxes
 
 struct ResUnit {
@@ -402,11 +448,12 @@ __device__ __forceinline__ ResUnit decode_res(const TcParams& p, int unit, int s
   return w;
 }
 
-template <int RES, int EV>
+template <int EV>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ TcParams p, const int split) {
-  constexpr int STAGES = kResTotalStages - RES;
+  constexpr int STAGES = kResTotalStages;       // barriers; a unit's ring has 12 - (its resident stages)
+  constexpr int RES = kResMaxResident;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kBoxBytes = 128 * kWBK;            // one box: 64 columns x 64 rows
   constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
@@ -428,8 +475,7 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
   const uint32_t drain0 = smem_u32(&bars[2 * STAGES + 4]);      // used only after an abort
   const uint32_t bfull = smem_u32(&bars[2 * STAGES + 5]), bfree = smem_u32(&bars[2 * STAGES + 6]);
-  const uint32_t res_base = smem_u32(smem);                      // resident stages
-  const uint32_t ring_base = res_base + RES * kResStageBytes;    // streamed stages
+  const uint32_t res_base = smem_u32(smem);      // a unit's resident stages, followed by its ring
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
@@ -460,8 +506,8 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs, whole warp) --------------
-    int stage = 0;
-    uint32_t phase = 0, issued = 0, unit_phase = 0, res_armed = 0;
+    // eph: bit i = parity of the number of uses of ring barrier i so far; used: barriers ever armed
+    uint32_t eph = 0, used = 0, unit_phase = 0, res_armed = 0;
     bool ok = true;
     for (int unit = cluster_id; ok; unit += n_clusters) {
       const ResUnit w = decode_res(p, unit, split);
@@ -488,19 +534,24 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tma2_load_2d(res_base + s * kResStageBytes + (lane & 1) * kBoxBytes, &tmap_b, bar,
                        qh + 64 * (lane & 1), w.row0 + s * kWBK);
       }
-      // streamed operand: every p-block walks the expert's stages
+      // streamed operand: every p-block walks the expert's stages.  The ring takes the stages the
+      // resident operand leaves (it is empty here: the wait on bfree above saw every MMA retire)
+      const int ring = kResTotalStages - ns;
+      const uint32_t ring_base = res_base + ns * kResStageBytes;
+      int stage = 0;
       for (int pb = w.pb0; pb < w.pb1 && ok; ++pb) {
         const int ph = pb * 256 + 128 * (int)rank + 64 * (lane & 1);     // this lane's 64 output rows
         for (int s = 0; s < ns && ok; ++s) {
           {
-            ok = warp_wait(false, empty0 + 8 * stage, phase ^ 1, abort_flag, p.fault, 32);
+            ok = warp_wait(false, empty0 + 8 * stage, ((eph >> stage) & 1u) ^ 1u, abort_flag, p.fault, 32);
             if (ok) {
               const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
               const uint32_t sa = ring_base + stage * kResStageBytes;
               if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, 2u * kResStageBytes);
               if (lane < 2) tma2_load_2d(sa + lane * kBoxBytes, &tmap_a, bar, ph, w.row0 + s * kWBK);
-              ++issued;
-              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+              eph ^= 1u << stage;
+              used |= 1u << stage;
+              if (++stage == ring) stage = 0;
             }
           }
         }
@@ -508,14 +559,16 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       unit_phase ^= 1;
     }
     if (leader && lane == 0 && *abort_flag) {
-      drain_loads(full0, STAGES, issued);
+      const uint64_t deadline = globaltimer_ns() + 200000000ull;
+      for (int i = 0; i < STAGES; ++i)               // the last phase armed on each ring barrier
+        if ((used >> i) & 1u) mbar_drain(full0 + 8 * i, ((eph >> i) & 1u) ^ 1u, deadline);
       if (res_armed > 0) mbar_drain(bfull, (res_armed - 1) & 1u, globaltimer_ns() + 200000000ull);
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (even CTA only) -----------------------
     if (lane == 0 && leader) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0, unit_phase = 0;
+      int acc = 0;
+      uint32_t fph = 0, acc_phase = 0, unit_phase = 0;      // fph: as eph in the producer
       bool ok = true;
       for (int unit = cluster_id; ok; unit += n_clusters) {
         const ResUnit w = decode_res(p, unit, split);
@@ -525,6 +578,9 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (ns > RES) break;                          // the producer has raised the fault
         if (!(ok = mbar_wait(bfull, unit_phase, abort_flag, p.fault, 33))) break;
         tcgen05_fence_after();
+        const int ring = kResTotalStages - ns;
+        const uint32_t ring_base = res_base + ns * kResStageBytes;
+        int stage = 0;
         for (int pb = w.pb0; pb < w.pb1 && ok; ++pb) {
           if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12))) break;
           tcgen05_fence_after();
@@ -532,7 +588,7 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           for (int s = 0; s < ns && ok; ++s) {
             {
               const int ksteps = res_ksteps(w.rows, s);
-              if ((ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.fault, 13))) {
+              if ((ok = mbar_wait(full0 + 8 * stage, (fph >> stage) & 1u, abort_flag, p.fault, 13))) {
                 tcgen05_fence_after();
                 const uint32_t sa = ring_base + stage * kResStageBytes;
                 const uint32_t sb = res_base + s * kResStageBytes;
@@ -550,7 +606,8 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                       (s == 0 && ks == 0) ? 0u : 1u);
                 }
                 tcgen05_commit2(empty0 + 8 * stage);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                fph ^= 1u << stage;
+                if (++stage == ring) stage = 0;
               }
             }
           }

@@ -1396,7 +1396,7 @@ static int launch_panel(const PanelMaps& maps, const TcParams& p, int max_items,
                         cudaStream_t st) {
   const int n_max = max_rows > 512 ? 512 : (max_rows <= 256 ? ((max_rows + 15) & ~15) : ((max_rows + 31) & ~31));
   const uint32_t stage_bytes = kPanelABytes + (uint32_t)(n_max / 2) * 128u;
-  constexpr size_t kBudget = 224 * 1024;
+  constexpr size_t kBudget = 222 * 1024;    // + the kernel's static 3.5 KB: under the 227 KB a block may have
   int stages = (int)((kBudget - 1024) / stage_bytes);
   if (stages > kPanelMaxStages) stages = kPanelMaxStages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
@@ -1435,11 +1435,11 @@ static int launch_panel(const PanelMaps& maps, const TcParams& p, int max_items,
 // Launch of the resident-operand weight gradient.  A unit is (expert, 256 columns, one of `split`
 // ranges of p-blocks); `split` is chosen so that the last round of units over the resident
 // clusters is as full as possible.
-template <int RES, int EV>
+template <int EV>
 static int launch_res(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int n_experts,
                       cudaStream_t st) {
   constexpr size_t smem = (size_t)kResTotalStages * kResStageBytes + 1024;
-  auto kern = wgrad_resident_kernel<RES, EV>;
+  auto kern = wgrad_resident_kernel<EV>;
   static PerDeviceInt max_clusters_of;
   const int dev = current_device();
   int max_clusters = (int)max_clusters_of.get(dev);
@@ -1494,7 +1494,8 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   MOLE_REQUIRE(a.N % 128 == 0 && a.K % kBK == 0, "tensor-core GEMM needs N %% 128 == 0 and K %% 64 == 0 (N=%d K=%d)", a.N, a.K);
   MOLE_REQUIRE(a.total_rows % kTileRows == 0, "row buffers must hold whole 128-row tiles");
   const int BN = a.N % 256 == 0 ? 256 : 128;
-  const bool panel = a.panel && BN == 256 && a.rowmap == nullptr && a.peers.n == 0 && a.c_y == nullptr;
+  const bool panel = a.panel && BN == 256 && a.rowmap == nullptr && a.peers.n == 0 && a.c_y == nullptr &&
+                     a.max_rows_per_expert <= 8192;
   const bool pair = BN == 256 && (!a.single_cta || panel);
   CUtensorMap ma, mb;
   PanelMaps pm;
@@ -1609,13 +1610,9 @@ int tc_wgrad(const WgradArgs& a, cudaStream_t st) {
   const int max_items = a.n_experts * (a.P / kBM) * (a.Q / BN);
   // an expert's 64-row stages: at most two per 128-row tile
   const int max_stages = 2 * a.max_tiles_per_expert;
-  if (a.resident && BN == 256 && a.P % 256 == 0 && max_stages > 0 && max_stages <= 8) {
-    if (max_stages <= 6) {
-      if (a.accumulate) return launch_res<6, EV_WGRAD_ACC>(ma, mb, p, a.n_experts, st);
-      return launch_res<6, EV_WGRAD>(ma, mb, p, a.n_experts, st);
-    }
-    if (a.accumulate) return launch_res<8, EV_WGRAD_ACC>(ma, mb, p, a.n_experts, st);
-    return launch_res<8, EV_WGRAD>(ma, mb, p, a.n_experts, st);
+  if (a.resident && BN == 256 && a.P % 256 == 0 && max_stages > 0 && max_stages <= kResMaxResident) {
+    if (a.accumulate) return launch_res<EV_WGRAD_ACC>(ma, mb, p, a.n_experts, st);
+    return launch_res<EV_WGRAD>(ma, mb, p, a.n_experts, st);
   }
 #define MOLE_WG(EV)                                                                               \
   if (BN == 256 && a.P % 256 == 0 && !a.single_cta)                                               \
