@@ -231,12 +231,19 @@ typedef struct {
                              at the front of its run (the packed form of mole_dispatch_fwd_peer /
                              mole_combine_bwd_peer): nothing is gathered, the call writes the pad
                              rows of x (forward) and dout (backward) in place */
-  int32_t backend;        /* 0: tensor cores for bf16 (CTA pairs, cta_group::2, where the shape
-                             allows), CUDA cores for fp32 (the fp32 layer needs fp32-exact
-                             products); 1: CUDA-core kernels also for bf16, used to bisect
-                             numerics; 2: tensor cores with the one-CTA kernel only; 3: tensor cores
-                             with CTA pairs wherever the shape allows (0 picks between 2 and 3 by
-                             the number of row tiles an expert can have) */
+  int32_t backend;        /* 0: tensor cores for bf16, CUDA cores for fp32 (the fp32 layer needs
+                             fp32-exact products).  For bf16, 0 picks per launch: the panel kernel
+                             (weights on the M side of the MMA, an expert's rows on N) for row
+                             GEMMs up to 1024 rows per expert whose rows are one run and whose
+                             outputs stay in place, the resident-operand kernel for weight
+                             gradients of experts with at most 512 rows, otherwise 128x256 tiles
+                             (one CTA) or 256x256 tiles (CTA pairs) by the number of row tiles an
+                             expert can have.
+                             1: CUDA-core kernels also for bf16, used to bisect numerics;
+                             2: the one-CTA tile kernel everywhere; 3: CTA-pair tile kernels
+                             wherever the shape allows; 4: panel and resident-operand kernels
+                             wherever they are eligible (2-4 exist for A/B comparisons; all
+                             tensor-core back ends give bit-identical results) */
 } mole_ffn_desc;
 
 /* scratch the FFN needs per call (tile schedule); bytes depends only on L, n_src, Cs */
