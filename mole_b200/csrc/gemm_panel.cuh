@@ -93,37 +93,149 @@ __device__ __forceinline__ bool warp_wait(bool one, uint32_t bar, uint32_t parit
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-// The epilogue of 16 rows x one feature per thread; `x1w` = packed pre-activations (dX2)
+// The epilogue of 16 rows x one feature per thread for FC2 / dX (bias or plain store)
 template <int EV>
 __device__ __forceinline__ void panel_store16(const TcParams& p, const uint32_t (&r)[16], int64_t off,
-                                              float bias, const uint32_t (&x1w)[8]) {
-  using Ev = EvTraits<EV>;
+                                              float bias) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float v = __uint_as_float(r[i]);
-    const int64_t o = off + (int64_t)i * p.N;
-    if (Ev::epi == EPI_FC1) {
-      const uint16_t x1 = bf16_bits(v + bias);
-      st_b16(p.out0 + o, x1);
-      // the activation is taken of the rounded pre-activation, as backward sees it
-      st_b16(p.out1 + o, bf16_bits(act_fwd_t<Ev::act>(__uint_as_float((uint32_t)x1 << 16))));
-    } else if (Ev::epi == EPI_DACT) {
-      const uint32_t pw = x1w[i >> 1];
-      const float x1 = (i & 1) ? bf16_hi(pw) : bf16_lo(pw);
-      st_b16(p.out0 + o, bf16_bits(v * act_grad_t<Ev::act, Ev::gbwd>(x1)));
-    } else {
-      st_b16(p.out0 + o, bf16_bits(v + bias));
-    }
-  }
+  for (int i = 0; i < 16; ++i)
+    st_b16(p.out0 + off + (int64_t)i * p.N, bf16_bits(__uint_as_float(r[i]) + bias));
 }
-__device__ __forceinline__ void panel_load_x1(const TcParams& p, int64_t off, uint32_t (&x1w)[8]) {
-  const uint16_t* src = reinterpret_cast<const uint16_t*>(p.aux) + off;
+
+// ---- FC1 / dX2 epilogue of the panel kernel -----------------------------------------------
+// These two epilogues are bound by instruction issue (activation, rounding, two outputs), so
+// they are written for few instructions per element:
+//   * the arithmetic runs on pairs of rows with the packed fp32 instructions (fma / mul / add
+//     .f32x2), in the same order of operations as the scalar code: results are bit-identical;
+//   * the transposed accumulator (thread = feature, registers = rows) is turned round in a 1 KB
+//     shared-memory strip per warp, so that global memory sees 16-byte accesses: a lane stores
+//     (or, for the pre-activations of dX2, loads) eight neighbouring features of two rows, where
+//     it would otherwise issue sixteen 2-byte accesses with sixteen addresses.
+// Strip layout: word (rp, l) = rows (2 rp, 2 rp + 1) of feature l, at rp * 32 + (l ^ 4 (rp & 1));
+// the swap of neighbouring groups of four lanes in odd row pairs keeps the 16-byte accesses of
+// the row side free of bank conflicts.
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_dup(float a) { return f2_pack(a, a); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// gelu_parts on two values: the same operations in the same order
+struct GeluParts2 { uint64_t cdf, e; };
+__device__ __forceinline__ GeluParts2 gelu_parts2(uint64_t x) {
+  float x0, x1;
+  f2_unpack(x, x0, x1);
+  const uint64_t d = f2_fma(f2_dup(0.3275911f * 0.70710678f), x & 0x7fffffff7fffffffull, f2_dup(1.0f));
+  float d0, d1;
+  f2_unpack(d, d0, d1);
+  const uint64_t t = f2_pack(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
+  float a0, a1, e0, e1;
+  f2_unpack(f2_mul(f2_mul(x, x), f2_dup(-0.72134752f)), a0, a1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(a0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(a1));
+  GeluParts2 g;
+  g.e = f2_pack(e0, e1);
+  // the factor 0.5 of 0.5 * t * poly * e sits in the coefficients (an exact scaling)
+  uint64_t poly = f2_fma(t, f2_dup(0.5f * 1.061405429f), f2_dup(0.5f * -1.453152027f));
+  poly = f2_fma(t, poly, f2_dup(0.5f * 1.421413741f));
+  poly = f2_fma(t, poly, f2_dup(0.5f * -0.284496736f));
+  poly = f2_fma(t, poly, f2_dup(0.5f * 0.254829592f));
+  const uint64_t he = f2_mul(f2_mul(t, poly), g.e);                     // 0.5 erfc(|x| / sqrt 2)
+  const uint64_t up = f2_fma(he, f2_dup(-1.0f), f2_dup(1.0f));          // 1 - he
+  float h0, h1, u0, u1;
+  f2_unpack(he, h0, h1);
+  f2_unpack(up, u0, u1);
+  g.cdf = f2_pack(x0 >= 0.f ? u0 : h0, x1 >= 0.f ? u1 : h1);
+  return g;
+}
+template <int ACT>
+__device__ __forceinline__ uint32_t act_fwd_pair(uint32_t xw) {          // bf16 pair -> bf16 pair
+  const float lo = bf16_lo(xw), hi = bf16_hi(xw);
+  if (ACT == MOLE_ACT_RELU) return pack_bf16(fmaxf(lo, 0.f), fmaxf(hi, 0.f));
+  const uint64_t x = f2_pack(lo, hi);
+  float o0, o1;
+  f2_unpack(f2_mul(x, gelu_parts2(x).cdf), o0, o1);
+  return pack_bf16(o0, o1);
+}
+template <int ACT, int GBWD>
+__device__ __forceinline__ uint32_t act_bwd_pair(float v0, float v1, uint32_t xw) {   // v * act'(x)
+  const float lo = bf16_lo(xw), hi = bf16_hi(xw);
+  if (ACT == MOLE_ACT_RELU || GBWD == MOLE_GELU_BWD_TANH)
+    return pack_bf16(v0 * act_grad_t<ACT, GBWD>(lo), v1 * act_grad_t<ACT, GBWD>(hi));
+  const uint64_t x = f2_pack(lo, hi);
+  const GeluParts2 g = gelu_parts2(x);
+  const uint64_t d = f2_fma(f2_mul(x, f2_dup(0.39894228f)), g.e, g.cdf);
+  float o0, o1;
+  f2_unpack(f2_mul(f2_pack(v0, v1), d), o0, o1);
+  return pack_bf16(o0, o1);
+}
+
+struct PanelStrip {
+  uint32_t* we;        // feature side: this lane's word of an even / odd row pair (+ 32 per pair)
+  uint32_t* wo;
+  uint4* ra;           // row side: features 0-3 / 4-7 of this lane's (row pair, group of eight)
+  uint4* rb;
+  __device__ __forceinline__ void init(uint32_t* strip, int lane) {
+    we = strip + lane;
+    wo = strip + (lane ^ 4);
+    const int rp = lane >> 2, g = lane & 3;
+    uint4* s4 = reinterpret_cast<uint4*>(strip);
+    ra = s4 + rp * 8 + 2 * g + (rp & 1);
+    rb = s4 + rp * 8 + 2 * g + 1 - (rp & 1);
+  }
+  __device__ __forceinline__ void put(const uint32_t (&w)[8]) const {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t lo = src[(int64_t)(2 * i) * p.N], hi = src[(int64_t)(2 * i + 1) * p.N];
-    x1w[i] = lo | (hi << 16);
+    for (int i = 0; i < 8; ++i) ((i & 1) ? wo : we)[32 * i] = w[i];
   }
+  __device__ __forceinline__ void get(uint32_t (&w)[8]) const {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = ((i & 1) ? wo : we)[32 * i];
+  }
+  // eight features of the lane's two rows, as they lie in memory
+  __device__ __forceinline__ void take_rows(uint4& a, uint4& b) const {
+    const uint4 lo = *ra, hi = *rb;
+    a = make_uint4(__byte_perm(lo.x, lo.y, 0x5410), __byte_perm(lo.z, lo.w, 0x5410),
+                   __byte_perm(hi.x, hi.y, 0x5410), __byte_perm(hi.z, hi.w, 0x5410));
+    b = make_uint4(__byte_perm(lo.x, lo.y, 0x7632), __byte_perm(lo.z, lo.w, 0x7632),
+                   __byte_perm(hi.x, hi.y, 0x7632), __byte_perm(hi.z, hi.w, 0x7632));
+  }
+  __device__ __forceinline__ void put_rows(const uint4& a, const uint4& b) const {
+    *ra = make_uint4(__byte_perm(a.x, b.x, 0x5410), __byte_perm(a.x, b.x, 0x7632),
+                     __byte_perm(a.y, b.y, 0x5410), __byte_perm(a.y, b.y, 0x7632));
+    *rb = make_uint4(__byte_perm(a.z, b.z, 0x5410), __byte_perm(a.z, b.z, 0x7632),
+                     __byte_perm(a.w, b.w, 0x5410), __byte_perm(a.w, b.w, 0x7632));
+  }
+};
+__device__ __forceinline__ void st_v4(__nv_bfloat16* p, const uint4& v) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};"
+               ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+__device__ __forceinline__ uint4 ld_v4(const __nv_bfloat16* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+constexpr bool panel_heavy(int epi) { return epi == EPI_FC1 || epi == EPI_DACT; }
+constexpr int kPanelStripWords = 256;      // 1 KB per epilogue warp (FC1 / dX2 only)
 
 // `stages` x `stage_bytes` of dynamic shared memory: a stage is this CTA's 128 features x 64 K of
 // weights (16 KB) followed by its share of the panel's rows (up to `stage_bytes` - 16 KB).
@@ -146,8 +258,9 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag_s;
   __shared__ int start_s[kMaxLocalExperts + 1], istart_s[kMaxLocalExperts + 1];    // see decode_item
-  __shared__ int pairs_s[kMaxLocalExperts + 1];
+  __shared__ int pairs_s[kMaxLocalExperts + 1], rows_s[kMaxLocalExperts];
   __shared__ uint8_t order_s[kMaxLocalExperts];
+  __shared__ __align__(16) uint32_t xstrip_s[panel_heavy(Ev::epi) ? kEpiWarps * kPanelStripWords : 4];
   volatile int* abort_flag = &abort_flag_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -168,6 +281,8 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
   __syncthreads();
   // rank of every expert by falling number of tile pairs (ties: by index): its place in the order
   for (int e = threadIdx.x; e < p.n_experts; e += kThreads) {
+    const int ts = start_s[e], te = start_s[e + 1];
+    rows_s[e] = te > ts ? (te - ts - 1) * kTileRows + p.tile_rows[te - 1] : 0;
     const int mine = pairs_s[e + 1] - pairs_s[e];
     int rk = 0;
     for (int o = 0; o < p.n_experts; ++o) {
@@ -190,12 +305,14 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
       mbar_init(tovl0 + 8 * a, 2 * kEpiWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    // panels per expert, in the order: ceil(pairs of tiles / 2) = ceil(rows / 512)
+    // panels per expert, in the order: ceil(pairs of tiles / 2) = ceil(rows / 512); with
+    // `panel_split` an expert of more than 320 rows gets one panel per 256 rows instead
     int run = 0;
     for (int i = 0; i < p.n_experts; ++i) {
       const int e = order_s[i];
+      const int pairs = pairs_s[e + 1] - pairs_s[e];
       istart_s[i] = run;
-      run += (pairs_s[e + 1] - pairs_s[e] + 1) >> 1;
+      run += (p.panel_split && rows_s[e] > 320) ? pairs : (pairs + 1) >> 1;
     }
     istart_s[p.n_experts] = run;
   }
@@ -343,37 +460,113 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
           else { ov_lo = (int)kTmemCols - c_next; ov_hi = c; }
         }
       }
-      // dX2: the pre-activations of the first chunk this warp will take are fetched before the
-      // wait for the accumulator
-      int first = grp * 16;
-      if (ov_hi > ov_lo) {
-        const int k0 = ov_lo >> 4;                            // first chunk of the shared columns
-        const int c_in = (k0 + ((grp - k0) & 3)) * 16;        // this group's first chunk at or after it
-        if (c_in < ov_hi) first = c_in;
-      }
-      uint32_t cur[8];
-      bool fresh = false;                                     // cur holds chunk `first`
-      if (Ev::epi == EPI_DACT && first < c) { panel_load_x1(p, obase + (int64_t)first * p.N, cur); fresh = true; }
-      if (!warp_wait(false, tfull0 + 8 * acc, acc ? aph1 : aph0, abort_flag, p.fault, 24))
-        break;                                        // nothing is stored for this item
-      tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (acc ? kTmemCols - c : 0);
-#pragma unroll 1
-      for (int pass = 0; pass < 2; ++pass) {
-        for (int c0 = grp * 16; c0 < c; c0 += 64) {   // warp-uniform
-          const bool inside = c0 >= ov_lo && c0 < ov_hi;
-          if (inside != (pass == 0)) continue;
-          if (Ev::epi == EPI_DACT && !(fresh && c0 == first)) panel_load_x1(p, obase + (int64_t)c0 * p.N, cur);
-          fresh = false;
-          uint32_t r[16];
-          tmem_ld16(taddr + c0, r);
-          tmem_ld_wait();
-          panel_store16<EV>(p, r, obase + (int64_t)c0 * p.N, bias, cur);
+      // This warp's chunks of 16 rows in drain order: those inside the shared columns first.
+      int it_pass = 0, it_c = grp * 16 - 64;
+      auto next_chunk = [&]() -> int {
+        while (it_pass < 2) {
+          it_c += 64;
+          if (it_c >= c) { ++it_pass; it_c = grp * 16 - 64; continue; }
+          const bool inside = it_c >= ov_lo && it_c < ov_hi;
+          if (inside == (it_pass == 0)) return it_c;
         }
-        if (pass == 0) {                              // the shared columns are free
-          tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster((tovl0 + 8 * acc) & kPeerMask);
+        return -1;
+      };
+      int cur = next_chunk(), cur_pass = it_pass;
+      const uint32_t taddr0 = ((uint32_t)(quarter * 32) << 16) + (acc ? kTmemCols - c : 0);
+      auto release_shared = [&]() {                     // the shared columns are free
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster((tovl0 + 8 * acc) & kPeerMask);
+      };
+      if (panel_heavy(Ev::epi)) {
+        PanelStrip xs;
+        xs.init(xstrip_s + (warp - 2) * kPanelStripWords, lane);
+        // row side: this lane's two rows (2 rp, 2 rp + 1 of a chunk) and eight features
+        const int64_t rbase = ((int64_t)w.row0 + 2 * (lane >> 2)) * p.N + (f - lane) + 8 * (lane & 3);
+        // dX2: the pre-activations of a chunk are fetched one chunk ahead, those of the first
+        // chunk before the wait for the accumulator
+        uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
+        if (Ev::epi == EPI_DACT && cur >= 0) {
+          const __nv_bfloat16* src = p.aux + rbase + (int64_t)cur * p.N;
+          xa = ld_v4(src);
+          xb = ld_v4(src + p.N);
+        }
+        if (!warp_wait(false, tfull0 + 8 * acc, acc ? aph1 : aph0, abort_flag, p.fault, 24))
+          break;                                        // nothing is stored for this item
+        tcgen05_fence_after();
+        bool released = false;
+        if (cur < 0 || cur_pass == 1) { release_shared(); released = true; }
+        const uint64_t bias2 = f2_dup(bias);
+        while (cur >= 0) {
+          const int nxt = next_chunk(), nxt_pass = it_pass;
+          const int64_t o = rbase + (int64_t)cur * p.N;
+          uint32_t xw[8], ow[8];
+          if (Ev::epi == EPI_DACT) {
+            __syncwarp();
+            xs.put_rows(xa, xb);
+            __syncwarp();
+            xs.get(xw);
+            if (nxt >= 0) {
+              const __nv_bfloat16* src = p.aux + rbase + (int64_t)nxt * p.N;
+              xa = ld_v4(src);
+              xb = ld_v4(src + p.N);
+            }
+          }
+          uint32_t r[16];
+          tmem_ld16(tmem_base + taddr0 + cur, r);
+          tmem_ld_wait();
+          uint4 ra, rb;
+          if (Ev::epi == EPI_FC1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
+              if (Ev::bias) f2_unpack(f2_add(f2_pack(s0, s1), bias2), s0, s1);
+              xw[i] = pack_bf16(s0, s1);
+              // the activation is taken of the rounded pre-activation, as backward sees it
+              ow[i] = act_fwd_pair<Ev::act>(xw[i]);
+            }
+            __syncwarp();
+            xs.put(xw);
+            __syncwarp();
+            xs.take_rows(ra, rb);
+            st_v4(p.out0 + o, ra);
+            st_v4(p.out0 + o + p.N, rb);
+            __syncwarp();
+            xs.put(ow);
+            __syncwarp();
+            xs.take_rows(ra, rb);
+            st_v4(p.out1 + o, ra);
+            st_v4(p.out1 + o + p.N, rb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              ow[i] = act_bwd_pair<Ev::act, Ev::gbwd>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), xw[i]);
+            __syncwarp();
+            xs.put(ow);
+            __syncwarp();
+            xs.take_rows(ra, rb);
+            st_v4(p.out0 + o, ra);
+            st_v4(p.out0 + o + p.N, rb);
+          }
+          if (!released && cur_pass == 0 && (nxt < 0 || nxt_pass == 1)) { release_shared(); released = true; }
+          cur = nxt;
+          cur_pass = nxt_pass;
+        }
+      } else {
+        if (!warp_wait(false, tfull0 + 8 * acc, acc ? aph1 : aph0, abort_flag, p.fault, 24))
+          break;                                        // nothing is stored for this item
+        tcgen05_fence_after();
+        bool released = false;
+        if (cur < 0 || cur_pass == 1) { release_shared(); released = true; }
+        while (cur >= 0) {
+          const int nxt = next_chunk(), nxt_pass = it_pass;
+          uint32_t r[16];
+          tmem_ld16(tmem_base + taddr0 + cur, r);
+          tmem_ld_wait();
+          panel_store16<EV>(p, r, obase + (int64_t)cur * p.N, bias);
+          if (!released && cur_pass == 0 && (nxt < 0 || nxt_pass == 1)) { release_shared(); released = true; }
+          cur = nxt;
+          cur_pass = nxt_pass;
         }
       }
       tcgen05_fence_before();

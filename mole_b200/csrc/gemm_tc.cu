@@ -19,6 +19,7 @@
 // Every wait on an mbarrier is bounded: when it runs out the kernel records a code in the
 // library's fault word, stops waiting for the rest of its run, still frees its TMEM and exits.
 #include <cuda.h>
+#include <cstdlib>
 
 #include <mutex>
 #include <type_traits>
@@ -252,6 +253,7 @@ struct TcParams {
   int N, K;                 // rows mode: output columns / reduction.  wgrad: Q / unused
   int P;                    // wgrad: output rows per expert
   int epi, act, gelu_bwd, accumulate;
+  int panel_split;          // panel kernel: experts of more than 320 rows are cut into panels of <= 256 rows
   const __nv_bfloat16* bias;
   const __nv_bfloat16* aux;
   __nv_bfloat16* out0;
@@ -1394,9 +1396,12 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
 template <bool W_KMAJOR, int EV>
 static int launch_panel(const PanelMaps& maps, const TcParams& p, int max_items, int max_rows,
                         cudaStream_t st) {
+  if (p.panel_split && max_rows > 320) max_rows = 320;      // no panel holds more
   const int n_max = max_rows > 512 ? 512 : (max_rows <= 256 ? ((max_rows + 15) & ~15) : ((max_rows + 31) & ~31));
   const uint32_t stage_bytes = kPanelABytes + (uint32_t)(n_max / 2) * 128u;
-  constexpr size_t kBudget = 222 * 1024;    // + the kernel's static 3.5 KB: under the 227 KB a block may have
+  // + the kernel's static 3.5 KB (and the 16 KB of transposing strips of the FC1 / dX2 epilogues):
+  // under the 227 KB a block may have
+  constexpr size_t kBudget = (panel_heavy(EvTraits<EV>::epi) ? 206 : 222) * 1024;
   int stages = (int)((kBudget - 1024) / stage_bytes);
   if (stages > kPanelMaxStages) stages = kPanelMaxStages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
@@ -1532,6 +1537,11 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   p.act = a.act;
   p.gelu_bwd = a.gelu_bwd;
   p.accumulate = 0;
+  // FC1 / dX2 with a short reduction: the epilogue (activation, two stores per element) takes as
+  // long as the MMAs of the item, and a panel of 512 columns fills the TMEM, so nothing overlaps.
+  // Panels of at most 256 rows leave room for the next item's accumulator.
+  p.panel_split = (a.epi == EPI_FC1 || a.epi == EPI_DACT) && a.K <= 1024;
+  if (const char* v = getenv("MOLE_PANEL_SPLIT")) p.panel_split = atoi(v);
   p.bias = static_cast<const __nv_bfloat16*>(a.bias);
   p.aux = static_cast<const __nv_bfloat16*>(a.aux);
   p.out0 = static_cast<__nv_bfloat16*>(a.out0);
