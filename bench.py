@@ -898,10 +898,19 @@ def run_ours(args):
     hs.barrier()
 
     # ---- device-resident timed region --------------------------------------------------------
-    with ClockSampler(local) as clocks:
-        n0 = hs.launches()
-        ms, host_ms = hs.timed(step, args.steps)
-        n1 = hs.launches()
+    # A region in which the host needed nearly as long to enqueue a step as the GPU to run it
+    # (another tenant's job on the host's cores) measures the host, not the kernels: it is taken
+    # again, at most twice, and the count is reported.
+    host_bound_retries = 0
+    while True:
+        with ClockSampler(local) as clocks:
+            n0 = hs.launches()
+            ms, host_ms = hs.timed(step, args.steps)
+            n1 = hs.launches()
+        host_bound = hs.max_over_ranks(1.0 if host_ms >= 0.85 * ms / args.steps else 0.0) > 0
+        if not host_bound or host_bound_retries >= 2:
+            break
+        host_bound_retries += 1
     ms_per_step = ms / args.steps
     value = world * T / (ms_per_step * 1e-3)
     check_fault("after the timed region")
@@ -953,7 +962,8 @@ def run_ours(args):
                    "timing": "CUDA events around the K steps on the launching stream; a ~25 ms GPU spin "
                              "queued before the first event lets the host enqueue ahead"},
         "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": n1 - n0,
-        "host_enqueue_ms_per_step": host_ms, "warmup_settling_steps": extra,
+        "host_enqueue_ms_per_step": host_ms, "host_bound_retries": host_bound_retries,
+        "warmup_settling_steps": extra,
     }
     if near_cores:
         out["host_cores_near_gpu"] = near_cores

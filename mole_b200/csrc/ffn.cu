@@ -82,7 +82,11 @@ struct Workspace {
   int32_t* rowmap;   // [rows_total]
   void* buf_a;       // [rows_total, M]
   void* buf_b;       // [rows_total, M]
+  float* colsum;     // partial column sums of dX1 from the dX2 launch (panel kernel), or null
 };
+// Column sums of dX1 (the FC1 bias gradient) come out of the dX2 launch when the panel kernel
+// takes it: its epilogue threads each own one feature and walk down the rows anyway.
+static bool fused_colsum(const mole_ffn_desc* d) { return use_tc(d) && panel_ok(d) && d->F % 256 == 0; }
 static int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 static int64_t workspace_bytes_of(const mole_ffn_desc* d) {
   int64_t b = align256(schedule_bytes(d->L, d->n_src, d->Cs));
@@ -91,20 +95,25 @@ static int64_t workspace_bytes_of(const mole_ffn_desc* d) {
     b += align256(rows * 4);
     if (!prepacked(d)) b += 2 * align256(rows * d->M * 2);
   }
+  if (fused_colsum(d)) b += align256(tc_panel_colsum_bytes(d->L, d->n_src * d->Cs, d->F));
   return b;
 }
 static Workspace carve_workspace(const mole_ffn_desc* d, void* ws) {
   Workspace w{};
   w.sched = carve_schedule(ws, d->L, d->n_src, d->Cs);
+  char* p = static_cast<char*>(ws) + align256(schedule_bytes(d->L, d->n_src, d->Cs));
   if (compacting(d)) {
     const int64_t rows = (int64_t)d->L * d->n_src * d->Cs;
-    char* p = static_cast<char*>(ws) + align256(schedule_bytes(d->L, d->n_src, d->Cs));
     w.rowmap = reinterpret_cast<int32_t*>(p);
     p += align256(rows * 4);
-    w.buf_a = p;
-    p += align256(rows * d->M * 2);
-    w.buf_b = p;
+    if (!prepacked(d)) {
+      w.buf_a = p;
+      p += align256(rows * d->M * 2);
+      w.buf_b = p;
+      p += align256(rows * d->M * 2);
+    }
   }
+  if (fused_colsum(d)) w.colsum = reinterpret_cast<float*>(p);
   return w;
 }
 
@@ -345,7 +354,14 @@ static int ffn_bwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   a.panel = panel_ok(d); a.max_rows_per_expert = d->n_src * d->Cs;
   a.A = dout; a.W = w2; a.w_nk = 1; a.N = d->F; a.K = d->M; a.bias = nullptr; a.aux = x1;
   a.out0 = dx1; a.out1 = nullptr; a.epi = EPI_DACT;
+  a.colsum_ws = wk.colsum;
+  const bool gb1_fused = use_tc(d) && tc_panel_colsum(a);
   if (int rc = row_gemm(d, a, st)) return rc;
+  // gb1 = sum_rows dX1: left as partial sums by the launch above, or by a pass over dX1 below
+  if (gb1_fused) {
+    if (int rc = tc_panel_colsum_reduce(a, gslot, d->accumulate, gb1, st)) return rc;
+  }
+  a.colsum_ws = nullptr;
   // gb2 = sum_rows dO
   c.A = dout; c.N = d->M; c.out = gb2;
   if (int rc = colsum(d->dtype, c, st)) return rc;
@@ -353,8 +369,10 @@ static int ffn_bwd_impl(const mole_ffn_desc* d, const int32_t* counts,
   g.A = dx1; g.B = x; g.out = gw1;
   if (int rc = wgrad(d, g, st)) return rc;
   // gb1 = sum_rows dX1
-  c.A = dx1; c.N = d->F; c.out = gb1;
-  if (int rc = colsum(d->dtype, c, st)) return rc;
+  if (!gb1_fused) {
+    c.A = dx1; c.N = d->F; c.out = gb1;
+    if (int rc = colsum(d->dtype, c, st)) return rc;
+  }
   // dX = dX1 W1:  W1_e read as [K=F][N=M]
   if (dx != nullptr || peers != nullptr) {
     a.A = dx1; a.W = w1; a.w_nk = 0; a.N = d->M; a.K = d->F; a.bias = nullptr; a.aux = nullptr;

@@ -41,7 +41,7 @@ constexpr int kGmLdb = kGmCols + 8;
 
 // ---- dx = gather(ddisp) + dlogits @ Wg ------------------------------------------------------
 // Block: 8 warps, 64 tokens x 128 columns.  Warp w: tokens 16 (w & 3) .., columns 64 (w >> 2) ..
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 2)
 dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* __restrict__ idx,
                         const int32_t* __restrict__ slot, const float* __restrict__ dlogits,
                         const __nv_bfloat16* __restrict__ wg, int64_t Ttok, int M, int E, int EP,
@@ -61,54 +61,116 @@ dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* 
   constexpr int kIt = kGmTok * (kGmCols / 8) / 256;
   const bool early = k <= 2 && ddisp != nullptr;
   uint4 pre[kIt][2];
+  uint32_t okmask = 0;               // which of them are rows to add (applied where they are used)
   if (early) {
+    // Branch-free, in two rounds: first every (expert, slot) pair this thread needs, then every
+    // row vector (rows that were dropped or lie past the end read a valid dummy address and are
+    // left out of the sum).  With a branch per row the loads went out one memory round trip after
+    // the other, twenty-four per block.
+    int sl[kIt][2], ex[kIt][2];
+#pragma unroll
+    for (int it = 0; it < kIt; ++it) {
+      const int64_t t = min(tok0 + ((tid + 256 * it) >> 4), Ttok - 1);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int64_t pi = t * k + min(j, k - 1);
+        sl[it][j] = slot[pi];
+        ex[it][j] = idx[pi];
+      }
+    }
+    bool ok[kIt][2];
 #pragma unroll
     for (int it = 0; it < kIt; ++it) {
       const int w = tid + 256 * it;
-      const int tl = w >> 4, c8 = (w & 15) * 8;
-      const int64_t t = tok0 + tl;
+      const int c8 = (w & 15) * 8;
+      const int64_t t = tok0 + (w >> 4);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        pre[it][j] = make_uint4(0, 0, 0, 0);
-        if (t < Ttok && j < k) {
-          const int s = slot[t * k + j];
-          if (s < C)
-            pre[it][j] = *reinterpret_cast<const uint4*>(
-                ddisp + ((int64_t)idx[t * k + j] * Cs + s) * M + col0 + c8);
-        }
+        ok[it][j] = t < Ttok && j < k && sl[it][j] < C;
+        const int64_t r = ok[it][j] ? (int64_t)ex[it][j] * Cs + sl[it][j] : 0;
+        pre[it][j] = *reinterpret_cast<const uint4*>(ddisp + r * M + col0 + c8);
       }
     }
+#pragma unroll
+    for (int it = 0; it < kIt; ++it)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) okmask |= (ok[it][j] ? 1u : 0u) << (2 * it + j);
   }
 
-  if (E == EP && (E & 3) == 0) {            // four experts per thread and step: 16-byte loads
+  if (E == EP && EP <= 64 && (E & 3) == 0) {
+    // Common case (up to 64 experts): every load of the two operand tiles is issued before the
+    // first one is used -- a loop that loads, converts and stores one vector at a time pays a
+    // memory round trip per iteration, eight per block.
     const int q4 = EP >> 2;
-    for (int i = tid; i < kGmTok * q4; i += 256) {
+    float4 dv[4];
+    uint4 wv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + 256 * u;
       const int tl = i / q4, e = (i - tl * q4) * 4;
       const int64_t t = tok0 + tl;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (t < Ttok) v = *reinterpret_cast<const float4*>(dlogits + t * E + e);
-      __align__(8) __nv_bfloat16 h[4];
-      __align__(8) __nv_bfloat16 l[4];
-      split_bf16(v.x, h[0], l[0]);
-      split_bf16(v.y, h[1], l[1]);
-      split_bf16(v.z, h[2], l[2]);
-      split_bf16(v.w, h[3], l[3]);
-      *reinterpret_cast<uint2*>(a_hi + tl * lda + e) = *reinterpret_cast<const uint2*>(h);
-      *reinterpret_cast<uint2*>(a_lo + tl * lda + e) = *reinterpret_cast<const uint2*>(l);
+      dv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < kGmTok * q4 && t < Ttok) dv[u] = *reinterpret_cast<const float4*>(dlogits + t * E + e);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + 256 * u;
+      const int e = i >> 4, v = i & 15;
+      wv[u] = make_uint4(0, 0, 0, 0);
+      if (e < E) wv[u] = *reinterpret_cast<const uint4*>(wg + (int64_t)e * M + col0 + v * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + 256 * u;
+      const int tl = i / q4, e = (i - tl * q4) * 4;
+      if (i < kGmTok * q4) {
+        __align__(8) __nv_bfloat16 h[4];
+        __align__(8) __nv_bfloat16 l[4];
+        split_bf16(dv[u].x, h[0], l[0]);
+        split_bf16(dv[u].y, h[1], l[1]);
+        split_bf16(dv[u].z, h[2], l[2]);
+        split_bf16(dv[u].w, h[3], l[3]);
+        *reinterpret_cast<uint2*>(a_hi + tl * lda + e) = *reinterpret_cast<const uint2*>(h);
+        *reinterpret_cast<uint2*>(a_lo + tl * lda + e) = *reinterpret_cast<const uint2*>(l);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + 256 * u;
+      const int e = i >> 4, v = i & 15;
+      if (e < EP) *reinterpret_cast<uint4*>(bs + e * kGmLdb + v * 8) = wv[u];
     }
   } else {
-    for (int i = tid; i < kGmTok * EP; i += 256) {
-      const int tl = i / EP, e = i - tl * EP;
-      const int64_t t = tok0 + tl;
-      const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
-      split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+    if (E == EP && (E & 3) == 0) {            // four experts per thread and step: 16-byte loads
+      const int q4 = EP >> 2;
+      for (int i = tid; i < kGmTok * q4; i += 256) {
+        const int tl = i / q4, e = (i - tl * q4) * 4;
+        const int64_t t = tok0 + tl;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < Ttok) v = *reinterpret_cast<const float4*>(dlogits + t * E + e);
+        __align__(8) __nv_bfloat16 h[4];
+        __align__(8) __nv_bfloat16 l[4];
+        split_bf16(v.x, h[0], l[0]);
+        split_bf16(v.y, h[1], l[1]);
+        split_bf16(v.z, h[2], l[2]);
+        split_bf16(v.w, h[3], l[3]);
+        *reinterpret_cast<uint2*>(a_hi + tl * lda + e) = *reinterpret_cast<const uint2*>(h);
+        *reinterpret_cast<uint2*>(a_lo + tl * lda + e) = *reinterpret_cast<const uint2*>(l);
+      }
+    } else {
+      for (int i = tid; i < kGmTok * EP; i += 256) {
+        const int tl = i / EP, e = i - tl * EP;
+        const int64_t t = tok0 + tl;
+        const float v = (t < Ttok && e < E) ? dlogits[t * E + e] : 0.f;
+        split_bf16(v, a_hi[tl * lda + e], a_lo[tl * lda + e]);
+      }
     }
-  }
-  for (int i = tid; i < EP * (kGmCols / 8); i += 256) {
-    const int e = i >> 4, v = i & 15;
-    uint4 w = make_uint4(0, 0, 0, 0);
-    if (e < E) w = *reinterpret_cast<const uint4*>(wg + (int64_t)e * M + col0 + v * 8);
-    *reinterpret_cast<uint4*>(bs + e * kGmLdb + v * 8) = w;
+    for (int i = tid; i < EP * (kGmCols / 8); i += 256) {
+      const int e = i >> 4, v = i & 15;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (e < E) w = *reinterpret_cast<const uint4*>(wg + (int64_t)e * M + col0 + v * 8);
+      *reinterpret_cast<uint4*>(bs + e * kGmLdb + v * 8) = w;
+    }
   }
   __syncthreads();
 
@@ -159,7 +221,9 @@ dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* 
     if (early) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const uint32_t wd[4] = {pre[it][j].x, pre[it][j].y, pre[it][j].z, pre[it][j].w};
+        const uint32_t keep = ((okmask >> (2 * it + j)) & 1u) ? 0xffffffffu : 0u;
+        const uint32_t wd[4] = {pre[it][j].x & keep, pre[it][j].y & keep, pre[it][j].z & keep,
+                                pre[it][j].w & keep};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           v[2 * c] += __uint_as_float(wd[c] << 16);
@@ -231,18 +295,69 @@ gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[a][i][j] = 0.f;
 
+  // Up to 64 experts (MT == 1, the common case): the loads of a sub-chunk's two operand tiles are
+  // all issued at once, one sub-chunk ahead, and wait in registers while the previous sub-chunk is
+  // multiplied -- a loop that loads, converts and stores one vector at a time pays a memory round
+  // trip per iteration (eight per sub-chunk, 6 us where the data needs 1 us).
+  const bool fast = MT == 1 && E == EP && (E & 3) == 0;
+  const int q4 = EP >> 2;
+  float4 dv[4];
+  uint4 xv[4];
+  auto fetch = [&](int64_t tok0) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + 256 * u;
+      const int tl = i / q4, e = (i - tl * q4) * 4;
+      const int64_t t = tok0 + tl;
+      dv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < kGmTok * q4 && t < Ttok) dv[u] = *reinterpret_cast<const float4*>(dlogits + t * E + e);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + 256 * u;
+      const int tl = i >> 4, v = i & 15;
+      const int64_t t = tok0 + tl;
+      xv[u] = make_uint4(0, 0, 0, 0);
+      if (t < Ttok) xv[u] = *reinterpret_cast<const uint4*>(x + t * M + col0 + v * 8);
+    }
+  };
+  if (fast && chunk0 < Ttok) fetch(chunk0);
+
   for (int sub = 0; sub < chunk / kGmTok; ++sub) {
     const int64_t tok0 = chunk0 + sub * kGmTok;
     if (tok0 >= Ttok) break;                                  // block-uniform
+    if (fast) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = tid + 256 * u;
+        const int tl = i / q4, e = (i - tl * q4) * 4;
+        if (i < kGmTok * q4) {
+          __align__(8) __nv_bfloat16 h[4];
+          __align__(8) __nv_bfloat16 l[4];
+          split_bf16(dv[u].x, h[0], l[0]);
+          split_bf16(dv[u].y, h[1], l[1]);
+          split_bf16(dv[u].z, h[2], l[2]);
+          split_bf16(dv[u].w, h[3], l[3]);
+          *reinterpret_cast<uint2*>(a_hi + tl * lda + e) = *reinterpret_cast<const uint2*>(h);
+          *reinterpret_cast<uint2*>(a_lo + tl * lda + e) = *reinterpret_cast<const uint2*>(l);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = tid + 256 * u;
+        *reinterpret_cast<uint4*>(xs + (i >> 4) * kGmLdb + (i & 15) * 8) = xv[u];
+      }
+      __syncthreads();
+      if (sub + 1 < chunk / kGmTok && tok0 + kGmTok < Ttok) fetch(tok0 + kGmTok);
+    } else {
     if (E == EP && (E & 3) == 0) {          // four experts per thread and step: 16-byte loads
-      const int q4 = EP >> 2;
       for (int i = tid; i < kGmTok * q4; i += 256) {
         const int tl = i / q4, e = (i - tl * q4) * 4;
         const int64_t t = tok0 + tl;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (t < Ttok) v = *reinterpret_cast<const float4*>(dlogits + t * E + e);
         __align__(8) __nv_bfloat16 h[4];
-      __align__(8) __nv_bfloat16 l[4];
+        __align__(8) __nv_bfloat16 l[4];
         split_bf16(v.x, h[0], l[0]);
         split_bf16(v.y, h[1], l[1]);
         split_bf16(v.z, h[2], l[2]);
@@ -266,6 +381,7 @@ gate_wgrad_mma_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __
       *reinterpret_cast<uint4*>(xs + tl * kGmLdb + v * 8) = w;
     }
     __syncthreads();
+    }
 #pragma unroll
     for (int ks = 0; ks < kGmTok / 16; ++ks) {
       uint32_t b[4][4];

@@ -33,6 +33,8 @@ struct RowGemmArgs {
   int panel;                // tensor cores: every expert's rows are one contiguous run and the panel
                             // kernel may take the launch (outputs in place, no fused combine)
   int max_rows_per_expert;  // bound on an expert's rows (sizes the panel kernel's stages)
+  float* colsum_ws;         // dX2 on the panel kernel: room for partial column sums of the output
+                            // (tc_panel_colsum_bytes), or null: no fused column sums
   const int32_t* rowmap;    // tensor cores, FC2 / dX: scatter output rows (-1 = drop), or null
   PeerMap peers;            // with rowmap: the scattered rows go to their source ranks (n > 0)
   int peer_Cs;              // rows per chunk of the receive buffers
@@ -90,6 +92,12 @@ int colsum(int dtype, const ColsumArgs& a, cudaStream_t st);
 
 int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st);     // bf16 only
 int tc_wgrad(const WgradArgs& a, cudaStream_t st);          // bf16 only
+// Column sums of dX1 fused into the dX2 launch (panel kernel only): whether tc_row_gemm(a) leaves
+// the partial sums in a.colsum_ws, their size, and the fixed-order reduction into out[slot, N].
+bool tc_panel_colsum(const RowGemmArgs& a);
+int64_t tc_panel_colsum_bytes(int n_experts, int max_rows_per_expert, int N);
+int tc_panel_colsum_reduce(const RowGemmArgs& a, const SlotMap& gslot, int accumulate, void* out,
+                           cudaStream_t st);
 bool tc_supported(int M, int F);
 
 // scalar epilogue shared by both back ends

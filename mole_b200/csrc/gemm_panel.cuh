@@ -37,7 +37,14 @@ struct PanelItem {
   int n0;          // first of the pair's 256 output features
   int row0;        // first row of the panel
   int n1, n2;      // columns of the two accumulators (multiples of 16; n2 may be 0; n1 = 0: nothing to do)
+  int pan;         // which of the expert's panels
 };
+
+// Panels of an expert with `pairs` = ceil(tiles / 2) pairs of row tiles: ceil(rows / 512), or, with
+// `split`, one per 256 rows once the expert has more than 320 rows.
+__device__ __forceinline__ int panel_count(int rows, int pairs, int split) {
+  return (split && rows > 320) ? pairs : (pairs + 1) >> 1;
+}
 
 // Experts are visited in the order of falling row counts (`order`, built once per CTA): items of
 // more than 256 rows cost about 1.3 of the others, and a launch may have only half a dozen items
@@ -68,6 +75,7 @@ __device__ __forceinline__ PanelItem decode_panel(const TcParams& p, const int* 
   w.n0 = (local / np) * 256;
   w.row0 = p.tile_row0[ts] + pan * per;
   w.n1 = w.n2 = 0;
+  w.pan = pan;
   if (left > 0) {
     const int r = min(per, left);
     if (r <= 256) w.n1 = (r + 15) & ~15;
@@ -114,80 +122,6 @@ __device__ __forceinline__ void panel_store16(const TcParams& p, const uint32_t 
 // Strip layout: word (rp, l) = rows (2 rp, 2 rp + 1) of feature l, at rp * 32 + (l ^ 4 (rp & 1));
 // the swap of neighbouring groups of four lanes in odd row pairs keeps the 16-byte accesses of
 // the row side free of bank conflicts.
-__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_dup(float a) { return f2_pack(a, a); }
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-// gelu_parts on two values: the same operations in the same order
-struct GeluParts2 { uint64_t cdf, e; };
-__device__ __forceinline__ GeluParts2 gelu_parts2(uint64_t x) {
-  float x0, x1;
-  f2_unpack(x, x0, x1);
-  const uint64_t d = f2_fma(f2_dup(0.3275911f * 0.70710678f), x & 0x7fffffff7fffffffull, f2_dup(1.0f));
-  float d0, d1;
-  f2_unpack(d, d0, d1);
-  const uint64_t t = f2_pack(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
-  float a0, a1, e0, e1;
-  f2_unpack(f2_mul(f2_mul(x, x), f2_dup(-0.72134752f)), a0, a1);
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(a0));
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(a1));
-  GeluParts2 g;
-  g.e = f2_pack(e0, e1);
-  // the factor 0.5 of 0.5 * t * poly * e sits in the coefficients (an exact scaling)
-  uint64_t poly = f2_fma(t, f2_dup(0.5f * 1.061405429f), f2_dup(0.5f * -1.453152027f));
-  poly = f2_fma(t, poly, f2_dup(0.5f * 1.421413741f));
-  poly = f2_fma(t, poly, f2_dup(0.5f * -0.284496736f));
-  poly = f2_fma(t, poly, f2_dup(0.5f * 0.254829592f));
-  const uint64_t he = f2_mul(f2_mul(t, poly), g.e);                     // 0.5 erfc(|x| / sqrt 2)
-  const uint64_t up = f2_fma(he, f2_dup(-1.0f), f2_dup(1.0f));          // 1 - he
-  float h0, h1, u0, u1;
-  f2_unpack(he, h0, h1);
-  f2_unpack(up, u0, u1);
-  g.cdf = f2_pack(x0 >= 0.f ? u0 : h0, x1 >= 0.f ? u1 : h1);
-  return g;
-}
-template <int ACT>
-__device__ __forceinline__ uint32_t act_fwd_pair(uint32_t xw) {          // bf16 pair -> bf16 pair
-  const float lo = bf16_lo(xw), hi = bf16_hi(xw);
-  if (ACT == MOLE_ACT_RELU) return pack_bf16(fmaxf(lo, 0.f), fmaxf(hi, 0.f));
-  const uint64_t x = f2_pack(lo, hi);
-  float o0, o1;
-  f2_unpack(f2_mul(x, gelu_parts2(x).cdf), o0, o1);
-  return pack_bf16(o0, o1);
-}
-template <int ACT, int GBWD>
-__device__ __forceinline__ uint32_t act_bwd_pair(float v0, float v1, uint32_t xw) {   // v * act'(x)
-  const float lo = bf16_lo(xw), hi = bf16_hi(xw);
-  if (ACT == MOLE_ACT_RELU || GBWD == MOLE_GELU_BWD_TANH)
-    return pack_bf16(v0 * act_grad_t<ACT, GBWD>(lo), v1 * act_grad_t<ACT, GBWD>(hi));
-  const uint64_t x = f2_pack(lo, hi);
-  const GeluParts2 g = gelu_parts2(x);
-  const uint64_t d = f2_fma(f2_mul(x, f2_dup(0.39894228f)), g.e, g.cdf);
-  float o0, o1;
-  f2_unpack(f2_mul(f2_pack(v0, v1), d), o0, o1);
-  return pack_bf16(o0, o1);
-}
-
 struct PanelStrip {
   uint32_t* we;        // feature side: this lane's word of an even / odd row pair (+ 32 per pair)
   uint32_t* wo;
@@ -312,7 +246,7 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
       const int e = order_s[i];
       const int pairs = pairs_s[e + 1] - pairs_s[e];
       istart_s[i] = run;
-      run += (p.panel_split && rows_s[e] > 320) ? pairs : (pairs + 1) >> 1;
+      run += panel_count(rows_s[e], pairs, p.panel_split);
     }
     istart_s[p.n_experts] = run;
   }
@@ -443,10 +377,17 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
     for (int item = cluster_id;; item += n_clusters) {
       const PanelItem w = decode_panel(p, start_s, istart_s, order_s, item);
       if (!w.valid) break;
-      if (w.n1 == 0) continue;
+      const int f = w.n0 + 128 * (int)rank + 32 * quarter + lane;
+      // dX2 with fused column sums: this warp's part of sum_rows dX1[:, f] for the panel
+      float* cs_out = nullptr;
+      if (Ev::epi == EPI_DACT && p.colsum_ws != nullptr)
+        cs_out = p.colsum_ws + ((int64_t)(w.el * p.colsum_panels + w.pan) * 4 + grp) * p.N + f;
+      if (w.n1 == 0) {
+        if (cs_out) *cs_out = 0.f;
+        continue;
+      }
       const int c = w.n1 + w.n2;
       const int slot = p.slot.s[p.e_begin + w.el];
-      const int f = w.n0 + 128 * (int)rank + 32 * quarter + lane;
       const int64_t obase = (int64_t)w.row0 * p.N + f;         // element (row0, f) of the outputs
       float bias = 0.f;
       if (Ev::bias) bias = __bfloat162float(p.bias[(int64_t)slot * p.N + f]);
@@ -497,6 +438,7 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
         bool released = false;
         if (cur < 0 || cur_pass == 1) { release_shared(); released = true; }
         const uint64_t bias2 = f2_dup(bias);
+        float csum = 0.f;
         while (cur >= 0) {
           const int nxt = next_chunk(), nxt_pass = it_pass;
           const int64_t o = rbase + (int64_t)cur * p.N;
@@ -539,8 +481,10 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
             st_v4(p.out1 + o + p.N, rb);
           } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 8; ++i) {
               ow[i] = act_bwd_pair<Ev::act, Ev::gbwd>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), xw[i]);
+              csum += bf16_lo(ow[i]) + bf16_hi(ow[i]);       // of the stored (rounded) values
+            }
             __syncwarp();
             xs.put(ow);
             __syncwarp();
@@ -552,6 +496,7 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
           cur = nxt;
           cur_pass = nxt_pass;
         }
+        if (cs_out) *cs_out = csum;
       } else {
         if (!warp_wait(false, tfull0 + 8 * acc, acc ? aph1 : aph0, abort_flag, p.fault, 24))
           break;                                        // nothing is stored for this item
@@ -586,6 +531,32 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
   }
 }
 
+// Column sums that the dX2 panel kernel left as partial sums -- per (expert, panel, one of the four
+// row groups of the epilogue, feature) -- added in a fixed order: bit-reproducible.
+struct PanelColsumArgs {
+  const float* ws;
+  const int32_t* expert_tile_start;
+  const int32_t* tile_rows;
+  const int32_t* expert_pair_start;
+  int N, panels, split, accumulate, e_begin;
+  __nv_bfloat16* out;          // [n_slots, N]
+  SlotMap gslot;
+};
+__global__ void __launch_bounds__(256)
+panel_colsum_reduce_kernel(const __grid_constant__ PanelColsumArgs a) {
+  const int el = blockIdx.y;
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  if (n >= a.N) return;
+  const int ts = a.expert_tile_start[el], te = a.expert_tile_start[el + 1];
+  const int rows = te > ts ? (te - ts - 1) * kTileRows + a.tile_rows[te - 1] : 0;
+  const int np = panel_count(rows, a.expert_pair_start[el + 1] - a.expert_pair_start[el], a.split);
+  float v = 0.f;
+  for (int i = 0; i < np * 4; ++i) v += a.ws[((int64_t)el * a.panels * 4 + i) * a.N + n];
+  __nv_bfloat16* out = a.out + (int64_t)a.gslot.s[a.e_begin + el] * a.N + n;
+  if (a.accumulate) v += __bfloat162float(*out);
+  *out = __float2bfloat16_rn(v);
+}
+
 // =========================================================================================
 // Weight gradient with one operand resident in shared memory.
 //
@@ -601,6 +572,8 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
 //   operand takes as many as the expert has 64-row stages (at most eight; the host checks the
 //   bound and falls back to the tile kernel beyond it), the ring of the streamed operand the
 //   rest: the loads in flight, which set the kernel's pace, get every byte that is left.
+//   (Measured: letting stages beyond the eighth follow A through the ring, or keeping fewer than
+//   eight resident, brings an expert of ~512 rows to the tile kernel's time, not below it.)
 //
 // Barriers as in tc2_gemm_kernel, plus bfull (resident operand landed; armed by the even CTA,
 // completed by both CTAs' loads) and bfree (every MMA that reads the resident operand has
@@ -735,17 +708,15 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       for (int pb = w.pb0; pb < w.pb1 && ok; ++pb) {
         const int ph = pb * 256 + 128 * (int)rank + 64 * (lane & 1);     // this lane's 64 output rows
         for (int s = 0; s < ns && ok; ++s) {
-          {
-            ok = warp_wait(false, empty0 + 8 * stage, ((eph >> stage) & 1u) ^ 1u, abort_flag, p.fault, 32);
-            if (ok) {
-              const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
-              const uint32_t sa = ring_base + stage * kResStageBytes;
-              if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, 2u * kResStageBytes);
-              if (lane < 2) tma2_load_2d(sa + lane * kBoxBytes, &tmap_a, bar, ph, w.row0 + s * kWBK);
-              eph ^= 1u << stage;
-              used |= 1u << stage;
-              if (++stage == ring) stage = 0;
-            }
+          ok = warp_wait(false, empty0 + 8 * stage, ((eph >> stage) & 1u) ^ 1u, abort_flag, p.fault, 32);
+          if (ok) {
+            const uint32_t bar = (full0 + 8 * stage) & kPeerMask;
+            const uint32_t sa = ring_base + stage * kResStageBytes;
+            if (leader && lane == 0) mbar_expect_tx(full0 + 8 * stage, 2u * kResStageBytes);
+            if (lane < 2) tma2_load_2d(sa + lane * kBoxBytes, &tmap_a, bar, ph, w.row0 + s * kWBK);
+            eph ^= 1u << stage;
+            used |= 1u << stage;
+            if (++stage == ring) stage = 0;
           }
         }
       }
@@ -778,31 +749,29 @@ wgrad_resident_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.fault, 12))) break;
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + acc * 256;
-          for (int s = 0; s < ns && ok; ++s) {
-            {
-              const int ksteps = res_ksteps(w.rows, s);
-              if ((ok = mbar_wait(full0 + 8 * stage, (fph >> stage) & 1u, abort_flag, p.fault, 13))) {
-                tcgen05_fence_after();
-                const uint32_t sa = ring_base + stage * kResStageBytes;
-                const uint32_t sb = res_base + s * kResStageBytes;
-                // a full stage is straight-line code: a branch between the MMAs slows their issue
-                if (ksteps == kWBK / kUmmaK) {
+          for (int s = 0; s < ns; ++s) {
+            const int ksteps = res_ksteps(w.rows, s);
+            const int st_a = stage;
+            if (!(ok = mbar_wait(full0 + 8 * st_a, (fph >> st_a) & 1u, abort_flag, p.fault, 13))) break;
+            const uint32_t sa = ring_base + st_a * kResStageBytes;
+            const uint32_t sb = res_base + s * kResStageBytes;
+            tcgen05_fence_after();
+            // a full stage is straight-line code: a branch between the MMAs slows their issue
+            if (ksteps == kWBK / kUmmaK) {
 #pragma unroll
-                  for (int ks = 0; ks < kWBK / kUmmaK; ++ks)
-                    tcgen05_mma2_bf16(d_tmem, make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024),
-                                      make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024), kIdesc,
-                                      (s == 0 && ks == 0) ? 0u : 1u);
-                } else {
-                  for (int ks = 0; ks < ksteps; ++ks)
-                    tcgen05_mma2_bf16(d_tmem, make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024),
-                                      make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024), kIdesc,
-                                      (s == 0 && ks == 0) ? 0u : 1u);
-                }
-                tcgen05_commit2(empty0 + 8 * stage);
-                fph ^= 1u << stage;
-                if (++stage == ring) stage = 0;
-              }
+              for (int ks = 0; ks < kWBK / kUmmaK; ++ks)
+                tcgen05_mma2_bf16(d_tmem, make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024),
+                                  make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024), kIdesc,
+                                  (s == 0 && ks == 0) ? 0u : 1u);
+            } else {
+              for (int ks = 0; ks < ksteps; ++ks)
+                tcgen05_mma2_bf16(d_tmem, make_desc(sa + ks * (kUmmaK * 128), kBoxBytes, 1024),
+                                  make_desc(sb + ks * (kUmmaK * 128), kBoxBytes, 1024), kIdesc,
+                                  (s == 0 && ks == 0) ? 0u : 1u);
             }
+            tcgen05_commit2(empty0 + 8 * st_a);
+            fph ^= 1u << st_a;
+            stage = st_a + 1 == ring ? 0 : st_a + 1;
           }
           if (!ok) break;
           tcgen05_commit2(tfull0 + 8 * acc);

@@ -19,7 +19,6 @@
 // Every wait on an mbarrier is bounded: when it runs out the kernel records a code in the
 // library's fault word, stops waiting for the rest of its run, still frees its TMEM and exits.
 #include <cuda.h>
-#include <cstdlib>
 
 #include <mutex>
 #include <type_traits>
@@ -254,6 +253,8 @@ struct TcParams {
   int P;                    // wgrad: output rows per expert
   int epi, act, gelu_bwd, accumulate;
   int panel_split;          // panel kernel: experts of more than 320 rows are cut into panels of <= 256 rows
+  float* colsum_ws;         // panel kernel, dX2: partial column sums [expert][panel][4][N], or null
+  int colsum_panels;        // panels per expert the partial sums are laid out for
   const __nv_bfloat16* bias;
   const __nv_bfloat16* aux;
   __nv_bfloat16* out0;
@@ -352,6 +353,83 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&b);
 }
+// Pairs of values on the packed fp32 instructions (fma / mul / add .f32x2): the FC1 and dX2
+// epilogues are bound by instruction issue, and the pair forms do the same operations in the same
+// order as the scalar code in about half the instructions (results are bit-identical).
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_dup(float a) { return f2_pack(a, a); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// gelu_parts on two values: the same operations in the same order
+struct GeluParts2 { uint64_t cdf, e; };
+__device__ __forceinline__ GeluParts2 gelu_parts2(uint64_t x) {
+  float x0, x1;
+  f2_unpack(x, x0, x1);
+  const uint64_t d = f2_fma(f2_dup(0.3275911f * 0.70710678f), x & 0x7fffffff7fffffffull, f2_dup(1.0f));
+  float d0, d1;
+  f2_unpack(d, d0, d1);
+  const uint64_t t = f2_pack(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
+  float a0, a1, e0, e1;
+  f2_unpack(f2_mul(f2_mul(x, x), f2_dup(-0.72134752f)), a0, a1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(a0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(a1));
+  GeluParts2 g;
+  g.e = f2_pack(e0, e1);
+  // the factor 0.5 of 0.5 * t * poly * e sits in the coefficients (an exact scaling)
+  uint64_t poly = f2_fma(t, f2_dup(0.5f * 1.061405429f), f2_dup(0.5f * -1.453152027f));
+  poly = f2_fma(t, poly, f2_dup(0.5f * 1.421413741f));
+  poly = f2_fma(t, poly, f2_dup(0.5f * -0.284496736f));
+  poly = f2_fma(t, poly, f2_dup(0.5f * 0.254829592f));
+  const uint64_t he = f2_mul(f2_mul(t, poly), g.e);                     // 0.5 erfc(|x| / sqrt 2)
+  const uint64_t up = f2_fma(he, f2_dup(-1.0f), f2_dup(1.0f));          // 1 - he
+  float h0, h1, u0, u1;
+  f2_unpack(he, h0, h1);
+  f2_unpack(up, u0, u1);
+  g.cdf = f2_pack(x0 >= 0.f ? u0 : h0, x1 >= 0.f ? u1 : h1);
+  return g;
+}
+template <int ACT>
+__device__ __forceinline__ uint32_t act_fwd_pair(uint32_t xw) {          // bf16 pair -> bf16 pair
+  const float lo = bf16_lo(xw), hi = bf16_hi(xw);
+  if (ACT == MOLE_ACT_RELU) return pack_bf16(fmaxf(lo, 0.f), fmaxf(hi, 0.f));
+  const uint64_t x = f2_pack(lo, hi);
+  float o0, o1;
+  f2_unpack(f2_mul(x, gelu_parts2(x).cdf), o0, o1);
+  return pack_bf16(o0, o1);
+}
+template <int ACT, int GBWD>
+__device__ __forceinline__ uint32_t act_bwd_pair(float v0, float v1, uint32_t xw) {   // v * act'(x)
+  const float lo = bf16_lo(xw), hi = bf16_hi(xw);
+  if (ACT == MOLE_ACT_RELU || GBWD == MOLE_GELU_BWD_TANH)
+    return pack_bf16(v0 * act_grad_t<ACT, GBWD>(lo), v1 * act_grad_t<ACT, GBWD>(hi));
+  const uint64_t x = f2_pack(lo, hi);
+  const GeluParts2 g = gelu_parts2(x);
+  const uint64_t d = f2_fma(f2_mul(x, f2_dup(0.39894228f)), g.e, g.cdf);
+  float o0, o1;
+  f2_unpack(f2_mul(f2_pack(v0, v1), d), o0, o1);
+  return pack_bf16(o0, o1);
+}
+
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -462,7 +540,7 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
           // the saved pre-activation is bf16: the activation is taken of the rounded value so
           // that backward's act'(x1) and forward's act(x1) see the same x1
           o[i] = pack_bf16(lo, hi);
-          h[i] = pack_bf16(act_fwd_t<ACT>(bf16_lo(o[i])), act_fwd_t<ACT>(bf16_hi(o[i])));
+          h[i] = act_fwd_pair<ACT>(o[i]);
         }
         st_v8(p.out0 + obase + c, o);
         st_v8(p.out1 + obase + c, h);
@@ -491,8 +569,7 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
       } else if (EPI == EPI_DACT) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          o[i] = pack_bf16(__uint_as_float(r[2 * i]) * act_grad_t<ACT, GBWD>(bf16_lo(cur[i])),
-                           __uint_as_float(r[2 * i + 1]) * act_grad_t<ACT, GBWD>(bf16_hi(cur[i])));
+          o[i] = act_bwd_pair<ACT, GBWD>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), cur[i]);
         st_v8(p.out0 + obase + c, o);
       } else {
 #pragma unroll
@@ -1495,12 +1572,51 @@ static void fill_sched(TcParams& p, const Schedule& s) {
   p.expert_pair_start = s.expert_pair_start;
 }
 
+static bool takes_panel(const RowGemmArgs& a) {
+  return a.panel && a.N % 256 == 0 && a.rowmap == nullptr && a.peers.n == 0 && a.c_y == nullptr &&
+         a.max_rows_per_expert <= 8192;
+}
+// FC1 / dX2 with a short reduction: the epilogue (activation, two stores per element) takes as
+// long as the MMAs of the item, and a panel of 512 columns fills the TMEM, so nothing overlaps.
+// Panels of at most 256 rows leave room for the next item's accumulator.
+static int panel_split_of(const RowGemmArgs& a) {
+  return (a.epi == EPI_FC1 || a.epi == EPI_DACT) && a.K <= 1024;
+}
+static int colsum_panels_of(int max_rows_per_expert) { return (max_rows_per_expert + 255) / 256; }
+
+bool tc_panel_colsum(const RowGemmArgs& a) {
+  return a.epi == EPI_DACT && a.colsum_ws != nullptr && takes_panel(a);
+}
+int64_t tc_panel_colsum_bytes(int n_experts, int max_rows_per_expert, int N) {
+  return (int64_t)n_experts * colsum_panels_of(max_rows_per_expert) * 4 * N * (int64_t)sizeof(float);
+}
+int tc_panel_colsum_reduce(const RowGemmArgs& a, const SlotMap& gslot, int accumulate, void* out,
+                           cudaStream_t st) {
+  MOLE_REQUIRE(tc_panel_colsum(a), "no fused column sums for this launch");
+  if (a.n_experts <= 0) return MOLE_OK;
+  PanelColsumArgs r{};
+  r.ws = a.colsum_ws;
+  r.expert_tile_start = a.sched.expert_tile_start;
+  r.tile_rows = a.sched.tile_rows;
+  r.expert_pair_start = a.sched.expert_pair_start;
+  r.N = a.N;
+  r.panels = colsum_panels_of(a.max_rows_per_expert);
+  r.split = panel_split_of(a);
+  r.accumulate = accumulate;
+  r.e_begin = a.e_begin;
+  r.out = static_cast<__nv_bfloat16*>(out);
+  r.gslot = gslot;
+  dim3 grid((a.N + 255) / 256, a.n_experts);
+  panel_colsum_reduce_kernel<<<grid, 256, 0, st>>>(r);
+  MOLE_LAUNCH_OK();
+  return MOLE_OK;
+}
+
 int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   MOLE_REQUIRE(a.N % 128 == 0 && a.K % kBK == 0, "tensor-core GEMM needs N %% 128 == 0 and K %% 64 == 0 (N=%d K=%d)", a.N, a.K);
   MOLE_REQUIRE(a.total_rows % kTileRows == 0, "row buffers must hold whole 128-row tiles");
   const int BN = a.N % 256 == 0 ? 256 : 128;
-  const bool panel = a.panel && BN == 256 && a.rowmap == nullptr && a.peers.n == 0 && a.c_y == nullptr &&
-                     a.max_rows_per_expert <= 8192;
+  const bool panel = takes_panel(a);
   const bool pair = BN == 256 && (!a.single_cta || panel);
   CUtensorMap ma, mb;
   PanelMaps pm;
@@ -1537,11 +1653,9 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   p.act = a.act;
   p.gelu_bwd = a.gelu_bwd;
   p.accumulate = 0;
-  // FC1 / dX2 with a short reduction: the epilogue (activation, two stores per element) takes as
-  // long as the MMAs of the item, and a panel of 512 columns fills the TMEM, so nothing overlaps.
-  // Panels of at most 256 rows leave room for the next item's accumulator.
-  p.panel_split = (a.epi == EPI_FC1 || a.epi == EPI_DACT) && a.K <= 1024;
-  if (const char* v = getenv("MOLE_PANEL_SPLIT")) p.panel_split = atoi(v);
+  p.panel_split = panel_split_of(a);
+  p.colsum_ws = tc_panel_colsum(a) ? a.colsum_ws : nullptr;
+  p.colsum_panels = colsum_panels_of(a.max_rows_per_expert);
   p.bias = static_cast<const __nv_bfloat16*>(a.bias);
   p.aux = static_cast<const __nv_bfloat16*>(a.aux);
   p.out0 = static_cast<__nv_bfloat16*>(a.out0);

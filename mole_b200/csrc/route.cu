@@ -792,7 +792,10 @@ extern "C" int mole_gate_bwd(const float* scores, const int32_t* idx, const int3
 // (multiples of 128), the same split for the CUDA-core and the mma.sync kernel.
 static void wgrad_split(int64_t T, int M, int col_width, int* chunk, int* n_chunks) {
   const int col_blocks = (M + col_width - 1) / col_width;
-  const int64_t want = (2 * sm_count() + col_blocks - 1) / col_blocks;
+  // chunks per column block so that all blocks fit one wave of two per SM (rounding up left a
+  // second, nearly empty wave)
+  int64_t want = 2 * sm_count() / col_blocks;
+  if (want < 1) want = 1;
   int64_t c = ((T + want - 1) / want + kWgTok - 1) / kWgTok * kWgTok;
   if (c < 256) c = 256;
   *chunk = (int)c;

@@ -209,8 +209,13 @@ def test_ffn_bf16_full_size_spot_check():
     # the panel kernel (two or three row panels per expert here) sums over K in the same order
     out4, dx4, grads4 = run_gpu(case, backend=4)
     assert torch.equal(out[valid], out4[valid]) and torch.equal(dx[valid], dx4[valid])
-    for a, b in zip(grads, grads4):
-        assert torch.equal(a, b)
+    for i, (a, b) in enumerate(zip(grads, grads4)):
+        if i == 1:
+            # the FC1 bias gradient comes out of the panel kernel's dX2 epilogue: the same bf16
+            # values of dX1 added in another (fixed) order, so a last-bit difference may remain
+            assert rel_fro(a, b) < 2e-3
+        else:
+            assert torch.equal(a, b)
     for l in (0, 10, 37):
         o_ref, dx_ref, g_ref = case.oracle(l)
         assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
@@ -251,7 +256,7 @@ def test_ffn_bf16_config3_shape_spot_check():
     counts = torch.randint(240, 273, (L,), generator=g).tolist()
     counts[1], counts[4], counts[6] = 256, 320, 257
     case = Case(M, F, L, 1, Cs, counts, torch.bfloat16, seed=10)
-    out, dx, grads = run_gpu(case)                       # backend 0: picks the one-CTA kernel here
+    out, dx, grads = run_gpu(case)                       # backend 0: panel + resident-operand kernels here
     out3, dx3, grads3 = run_gpu(case, backend=3)
     out4, dx4, grads4 = run_gpu(case, backend=4)         # panels of 16-row granularity
     valid = torch.zeros(1, L, Cs, dtype=torch.bool)
@@ -259,8 +264,12 @@ def test_ffn_bf16_config3_shape_spot_check():
         valid[0, l, :counts[l]] = True
     assert torch.equal(out[valid], out3[valid]) and torch.equal(dx[valid], dx3[valid])
     assert torch.equal(out[valid], out4[valid]) and torch.equal(dx[valid], dx4[valid])
-    for a, b, c4 in zip(grads, grads3, grads4):
-        assert torch.equal(a, b) and torch.equal(a, c4)
+    for i, (a, b, c4) in enumerate(zip(grads, grads3, grads4)):
+        assert torch.equal(a, c4)
+        if i == 1:      # FC1 bias gradient: summed in the panel kernel's dX2 epilogue, in another order
+            assert rel_fro(a, b) < 2e-3
+        else:
+            assert torch.equal(a, b)
     for l in (1, 4, 6):
         o_ref, dx_ref, g_ref = case.oracle(l)
         assert_close(case.expert_rows(out, l), o_ref, case.dtype, f"out {l}")
