@@ -318,18 +318,21 @@ simt_wgrad_kernel(const __grid_constant__ WgradArgs a) {
     }
 }
 
-// Block: 32 column groups of one 16-byte vector x 8 row lanes; one expert, 32 vectors of
-// columns.  Every thread keeps four 16-byte loads in flight.
+// Block: 8 column groups of one 16-byte vector (a row segment of 128 bytes) x 32 row lanes; one
+// expert.  Every thread keeps four 16-byte loads in flight.  Narrow column blocks keep the grid
+// large when a rank owns few experts with many rows each (8 experts x 2048 rows on eight GPUs: a
+// 256-column block per expert left 64 blocks for 148 SMs, each walking 2048 rows).
+constexpr int kCsCG = 8, kCsRL = 32;
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __grid_constant__ ColsumArgs a) {
   constexpr int V = Vec16<T>::N;
-  __shared__ float red[8][32 * V + 4];
+  __shared__ float red[kCsRL][kCsCG * V + 1];
   const int el = blockIdx.y;
   const int t0 = a.sched.expert_tile_start[el], t1 = a.sched.expert_tile_start[el + 1];
   const int slot = a.gslot.s[a.e_begin + el];
-  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
-  const int col = (blockIdx.x * 32 + cg) * V;
+  const int cg = threadIdx.x % kCsCG, rl = threadIdx.x / kCsCG;
+  const int col = (blockIdx.x * kCsCG + cg) * V;
   const T* A = static_cast<const T*>(a.A);
   float s[V];
 #pragma unroll
@@ -338,33 +341,32 @@ colsum_kernel(const __grid_constant__ ColsumArgs a) {
     for (int t = t0; t < t1; ++t) {
       const T* base = A + ((int64_t)a.sched.tile_row0[t] + rl) * a.N + col;
       const int valid = a.sched.tile_rows[t];               // rows beyond it may never have been written
-      for (int r0 = 0; r0 < valid; r0 += 32) {              // rows rl + {0, 8, 16, 24} + r0
-        float v[4][V];
+      // rows rl + {0, 32, 64, 96} of the tile (kTileRows = 4 * kCsRL)
+      float v[4][V];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (r0 + 8 * u + rl < valid) {
-            Vec16<T>::load(base + (int64_t)(r0 + 8 * u) * a.N, v[u]);
-          } else {
+      for (int u = 0; u < 4; ++u) {
+        if (kCsRL * u + rl < valid) {
+          Vec16<T>::load(base + (int64_t)(kCsRL * u) * a.N, v[u]);
+        } else {
 #pragma unroll
-            for (int c = 0; c < V; ++c) v[u][c] = 0.f;
-          }
+          for (int c = 0; c < V; ++c) v[u][c] = 0.f;
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-#pragma unroll
-          for (int c = 0; c < V; ++c) s[c] += v[u][c];
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int c = 0; c < V; ++c) s[c] += v[u][c];
     }
   }
 #pragma unroll
   for (int c = 0; c < V; ++c) red[rl][cg * V + c] = s[c];
   __syncthreads();
-  for (int i = threadIdx.x; i < 32 * V; i += 256) {
-    const int n = blockIdx.x * 32 * V + i;
+  for (int i = threadIdx.x; i < kCsCG * V; i += 256) {
+    const int n = blockIdx.x * kCsCG * V + i;
     if (n < a.N) {
       float v = 0.f;
 #pragma unroll
-      for (int r = 0; r < 8; ++r) v += red[r][i];
+      for (int r = 0; r < kCsRL; ++r) v += red[r][i];
       T* out = static_cast<T*>(a.out) + (int64_t)slot * a.N + n;
       if (a.accumulate) v += Elem<T>::to_f(*out);
       *out = Elem<T>::from_f(v);
@@ -397,7 +399,8 @@ int colsum(int dtype, const ColsumArgs& a, cudaStream_t st) {
   const int vec = dtype == MOLE_F32 ? 4 : 8;
   MOLE_REQUIRE(a.N % vec == 0, "column sums need 16-byte rows");
   if (a.n_experts <= 0) return MOLE_OK;
-  dim3 grid((a.N + 32 * vec - 1) / (32 * vec), a.n_experts);
+  static_assert(kTileRows == 4 * kCsRL, "a thread takes four rows of a tile");
+  dim3 grid((a.N + kCsCG * vec - 1) / (kCsCG * vec), a.n_experts);
   if (dtype == MOLE_F32) colsum_kernel<float><<<grid, 256, 0, st>>>(a);
   else colsum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
   MOLE_LAUNCH_OK();

@@ -1576,12 +1576,11 @@ static bool takes_panel(const RowGemmArgs& a) {
   return a.panel && a.N % 256 == 0 && a.rowmap == nullptr && a.peers.n == 0 && a.c_y == nullptr &&
          a.max_rows_per_expert <= 8192;
 }
-// FC1 / dX2 with a short reduction: the epilogue (activation, two stores per element) takes as
-// long as the MMAs of the item, and a panel of 512 columns fills the TMEM, so nothing overlaps.
-// Panels of at most 256 rows leave room for the next item's accumulator.
-static int panel_split_of(const RowGemmArgs& a) {
-  return (a.epi == EPI_FC1 || a.epi == EPI_DACT) && a.K <= 1024;
-}
+// FC1 / dX2: a panel of 512 columns fills the TMEM, so its epilogue (activation, two stores per
+// element: as long as the item's MMAs when the reduction is short) overlaps nothing.  Panels of
+// at most 256 rows leave room for the next item's accumulator (measured: -5 % at K = 2048 and
+// ~512 rows per expert, -5 to -8 % at K = 1024).
+static int panel_split_of(const RowGemmArgs& a) { return a.epi == EPI_FC1 || a.epi == EPI_DACT; }
 static int colsum_panels_of(int max_rows_per_expert) { return (max_rows_per_expert + 255) / 256; }
 
 bool tc_panel_colsum(const RowGemmArgs& a) {
