@@ -243,10 +243,13 @@ typedef struct {
                              2: the one-CTA tile kernel everywhere; 3: CTA-pair tile kernels
                              wherever the shape allows; 4: panel and resident-operand kernels
                              wherever they are eligible (2-4 exist for A/B comparisons; all
-                             tensor-core back ends give bit-identical results) */
+                             tensor-core back ends give bit-identical rows and weight
+                             gradients; gb1 comes out of the panel kernel's dX2 epilogue where that
+                             kernel runs -- the same values added in another fixed order) */
 } mole_ffn_desc;
 
-/* scratch the FFN needs per call (tile schedule); bytes depends only on L, n_src, Cs */
+/* scratch the FFN needs per call (tile schedule, packed-row map, partial column sums of the
+ * panel kernel); bytes depends only on dtype, backend, compact, L, n_src, Cs, M and F */
 int mole_ffn_workspace_bytes(const mole_ffn_desc* d, int64_t* bytes);
 
 /* x rows [n_src*L*Cs, M] -> out rows [.., M]; saves pre-activation x1 and activation h
