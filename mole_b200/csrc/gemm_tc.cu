@@ -210,10 +210,16 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* p, const float (&v)
 //   erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-z^2).
 // exp(-z^2) = exp(-x^2 / 2) is also the Gaussian density's exponential, so value and derivative
 // share one ex2 and one rcp.  The fp32 layer keeps erff (CUDA-core path).
+// 1 / d for d in [1, 2^126): one MUFU.RCP (a division by the fast-math intrinsic adds range handling)
+__device__ __forceinline__ float rcp_approx(float d) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return r;
+}
 struct GeluParts { float cdf, e; };     // Phi(x) and exp(-x^2 / 2)
 __device__ __forceinline__ GeluParts gelu_parts(float x) {
   const float ax = fabsf(x);
-  const float t = __fdividef(1.0f, fmaf(0.3275911f * 0.70710678f, ax, 1.0f));
+  const float t = rcp_approx(fmaf(0.3275911f * 0.70710678f, ax, 1.0f));
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * x * -0.72134752f));
   float poly = fmaf(t, 1.061405429f, -1.453152027f);
@@ -388,7 +394,7 @@ __device__ __forceinline__ GeluParts2 gelu_parts2(uint64_t x) {
   const uint64_t d = f2_fma(f2_dup(0.3275911f * 0.70710678f), x & 0x7fffffff7fffffffull, f2_dup(1.0f));
   float d0, d1;
   f2_unpack(d, d0, d1);
-  const uint64_t t = f2_pack(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
+  const uint64_t t = f2_pack(rcp_approx(d0), rcp_approx(d1));
   float a0, a1, e0, e1;
   f2_unpack(f2_mul(f2_mul(x, x), f2_dup(-0.72134752f)), a0, a1);
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(a0));
