@@ -246,6 +246,157 @@ dispatch_bwd_mma_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* 
   }
 }
 
+// The same product for the common case (top-1 / top-2, up to 64 experts, a gradient to gather):
+// every global read of the block is asynchronous.  The (expert, slot) pairs are read first; the Wg
+// tile and the gathered rows then travel to shared memory with cp.async (dropped pairs and tokens
+// past the end are zero-filled), dlogits through registers (it is split into bf16 hi + lo on the
+// way); the MMAs run as soon as the two small operand tiles are there, the gathered rows are only
+// waited for in front of the final sum.  No registers hold rows in flight, so three blocks fit an
+// SM (69 KB of shared memory each) and one block's stores overlap the next block's loads.
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+               ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+constexpr int kGmGatherBytes = 2 * kGmTok * kGmCols * 2;      // two rows per token, 128 columns
+
+__global__ void __launch_bounds__(256, 3)
+dispatch_bwd_mma_async_kernel(const __nv_bfloat16* __restrict__ ddisp, const int32_t* __restrict__ idx,
+                              const int32_t* __restrict__ slot, const float* __restrict__ dlogits,
+                              const __nv_bfloat16* __restrict__ wg, int64_t Ttok, int M, int E,
+                              int k, int C, int Cs, __nv_bfloat16* __restrict__ dx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int EP = E;
+  const int lda = EP + 8;
+  __nv_bfloat16* gt = reinterpret_cast<__nv_bfloat16*>(smem_raw);         // [2][64][128] gathered rows
+  unsigned char* ops = smem_raw + kGmGatherBytes;
+  __nv_bfloat16* a_hi = reinterpret_cast<__nv_bfloat16*>(ops);            // [64][lda]
+  __nv_bfloat16* a_lo = a_hi + kGmTok * lda;                              // [64][lda]
+  __nv_bfloat16* bs = a_lo + kGmTok * lda;                                // [EP][136]
+  float* cs = reinterpret_cast<float*>(ops);                              // [64][132], after the MMAs
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t tok0 = (int64_t)blockIdx.y * kGmTok;
+  const int col0 = blockIdx.x * kGmCols;
+  constexpr int kIt = kGmTok * (kGmCols / 8) / 256;                       // 4
+
+  int sl[kIt][2], ex[kIt][2];
+#pragma unroll
+  for (int it = 0; it < kIt; ++it) {
+    const int64_t t = min(tok0 + ((tid + 256 * it) >> 4), Ttok - 1);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int64_t pi = t * k + min(j, k - 1);
+      sl[it][j] = slot[pi];
+      ex[it][j] = idx[pi];
+    }
+  }
+  // group 0: the Wg tile
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = tid + 256 * u;
+    const int e = i >> 4, v = i & 15;
+    if (e < EP) cp_async_16(bs + e * kGmLdb + v * 8, wg + (int64_t)e * M + col0 + v * 8, 16);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  const int q4 = EP >> 2;
+  float4 dv[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = tid + 256 * u;
+    const int tl = i / q4, e = (i - tl * q4) * 4;
+    const int64_t t = tok0 + tl;
+    dv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < kGmTok * q4 && t < Ttok) dv[u] = *reinterpret_cast<const float4*>(dlogits + t * E + e);
+  }
+  // group 1: the gathered rows
+#pragma unroll
+  for (int it = 0; it < kIt; ++it) {
+    const int w = tid + 256 * it;
+    const int tl = w >> 4, c8 = (w & 15) * 8;
+    const int64_t t = tok0 + tl;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const bool ok = t < Ttok && j < k && sl[it][j] < C;
+      const int64_t r = ok ? (int64_t)ex[it][j] * Cs + sl[it][j] : 0;
+      cp_async_16(gt + (j * kGmTok + tl) * kGmCols + c8, ddisp + r * M + col0 + c8, ok ? 16 : 0);
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = tid + 256 * u;
+    const int tl = i / q4, e = (i - tl * q4) * 4;
+    if (i < kGmTok * q4) {
+      __align__(8) __nv_bfloat16 h[4];
+      __align__(8) __nv_bfloat16 l[4];
+      split_bf16(dv[u].x, h[0], l[0]);
+      split_bf16(dv[u].y, h[1], l[1]);
+      split_bf16(dv[u].z, h[2], l[2]);
+      split_bf16(dv[u].w, h[3], l[3]);
+      *reinterpret_cast<uint2*>(a_hi + tl * lda + e) = *reinterpret_cast<const uint2*>(h);
+      *reinterpret_cast<uint2*>(a_lo + tl * lda + e) = *reinterpret_cast<const uint2*>(l);
+    }
+  }
+  asm volatile("cp.async.wait_group 1;" ::: "memory");      // the Wg tile has landed
+  __syncthreads();
+
+  const int mt = warp & 3, nh = warp >> 2;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int ks = 0; ks < EP / 16; ++ks) {
+    uint32_t ah[4], al[4];
+    const int arow = mt * 16 + (lane & 15), acol = ks * 16 + (lane >> 4) * 8;
+    ldsm_x4(a_hi + arow * lda + acol, ah);
+    ldsm_x4(a_lo + arow * lda + acol, al);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int krow = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int ncol = nh * 64 + p * 16 + (lane >> 4) * 8;
+      uint32_t b[4];
+      ldsm_x4_trans(bs + krow * kGmLdb + ncol, b);
+      mma16816(acc[2 * p], ah, b[0], b[1]);
+      mma16816(acc[2 * p], al, b[0], b[1]);
+      mma16816(acc[2 * p + 1], ah, b[2], b[3]);
+      mma16816(acc[2 * p + 1], al, b[2], b[3]);
+    }
+  }
+  __syncthreads();                                  // operand tiles are dead: reuse as the C tile
+  constexpr int ldc = kGmCols + 4;
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      cs[(mt * 16 + g + (j >> 1) * 8) * ldc + nh * 64 + i * 8 + 2 * q + (j & 1)] = acc[i][j];
+  asm volatile("cp.async.wait_group 0;" ::: "memory");      // this thread's gathered vectors
+  __syncthreads();
+
+  // final sum: a thread owns 8 consecutive columns of one token (the vectors it fetched itself)
+#pragma unroll
+  for (int it = 0; it < kIt; ++it) {
+    const int w = tid + 256 * it;
+    const int tl = w >> 4, c8 = (w & 15) * 8;
+    const int64_t t = tok0 + tl;
+    if (t >= Ttok) continue;
+    float v[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) v[c] = cs[tl * ldc + c8 + c];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint4 pv = *reinterpret_cast<const uint4*>(gt + (j * kGmTok + tl) * kGmCols + c8);
+      const uint32_t wd[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        v[2 * c] += __uint_as_float(wd[c] << 16);
+        v[2 * c + 1] += __uint_as_float(wd[c] & 0xffff0000u);
+      }
+    }
+    Vec16<__nv_bfloat16>::store(dx + t * M + col0 + c8, v);
+  }
+}
+
 int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t* slot,
                             const float* dlogits, const void* wg, int64_t T, int M, int E, int k,
                             int C, int Cs, void* dx, cudaStream_t st) {
@@ -261,6 +412,21 @@ int launch_dispatch_bwd_mma(const void* ddisp, const int32_t* idx, const int32_t
     configured.set(dev_, (int64_t)smem);
   }
   dim3 grid(M / kGmCols, (unsigned)((T + kGmTok - 1) / kGmTok));
+  if (ddisp != nullptr && k <= 2 && E == EP && EP <= 64 && (E & 3) == 0 &&
+      (reinterpret_cast<uintptr_t>(ddisp) & 15) == 0 && (reinterpret_cast<uintptr_t>(wg) & 15) == 0) {
+    const size_t asmem = kGmGatherBytes + smem;
+    static PerDeviceInt aconfigured;
+    if ((int64_t)asmem > aconfigured.get(dev_)) {
+      MOLE_CUDA_OK(cudaFuncSetAttribute(dispatch_bwd_mma_async_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem));
+      aconfigured.set(dev_, (int64_t)asmem);
+    }
+    dispatch_bwd_mma_async_kernel<<<grid, 256, asmem, st>>>(
+        static_cast<const __nv_bfloat16*>(ddisp), idx, slot, dlogits,
+        static_cast<const __nv_bfloat16*>(wg), T, M, E, k, C, Cs, static_cast<__nv_bfloat16*>(dx));
+    MOLE_LAUNCH_OK();
+    return MOLE_OK;
+  }
   dispatch_bwd_mma_kernel<<<grid, 256, smem, st>>>(
       static_cast<const __nv_bfloat16*>(ddisp), idx, slot, dlogits,
       static_cast<const __nv_bfloat16*>(wg), T, M, E, EP, k, C, Cs, static_cast<__nv_bfloat16*>(dx));
