@@ -169,6 +169,14 @@ struct PeerMap {
   const int32_t* all_counts;
   int E;
 };
+// Order in which a pushing kernel walks the experts: rank r starts with the experts of rank r + 1
+// and ends with its own.  In natural order every rank would store to rank 0's memory first, then
+// to rank 1's ...: all senders on one receiver's links at a time.  Rotated, the ranks' targets
+// are a permutation at every moment.
+__device__ __forceinline__ int peer_rotate_expert(const PeerMap& pm, int e) {
+  const int shifted = e + ((pm.rank + 1) % pm.n) * pm.L;
+  return shifted >= pm.E ? shifted - pm.E : shifted;
+}
 __device__ __forceinline__ int64_t peer_row(const PeerMap& pm, int e, int s, int Cs, int* owner) {
   *owner = e / pm.L;
   const int l = e - *owner * pm.L;

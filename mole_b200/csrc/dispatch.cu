@@ -25,7 +25,8 @@ dispatch_fwd_kernel(const T* __restrict__ x, const int32_t* __restrict__ counts,
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (row >= (int64_t)E * Cs) return;
-  const int e = (int)(row / Cs), s = (int)(row - (int64_t)e * Cs);
+  const int e_walk = (int)(row / Cs), s = (int)(row - (int64_t)e_walk * Cs);
+  const int e = pm.n > 0 ? peer_rotate_expert(pm, e_walk) : e_walk;
   const int cnt = counts[e];
   uint4* dst;
   if (pm.n > 0) {
@@ -37,7 +38,7 @@ dispatch_fwd_kernel(const T* __restrict__ x, const int32_t* __restrict__ counts,
     if (s >= cnt) return;
     dst = reinterpret_cast<uint4*>(static_cast<T*>(pm.base[owner]) + prow * M);
   } else {
-    dst = reinterpret_cast<uint4*>(disp + row * M);
+    dst = reinterpret_cast<uint4*>(disp + row * M);       // e == e_walk here
   }
   const int padded = (cnt + kTileRows - 1) / kTileRows * kTileRows;
   if (s >= padded) return;
@@ -168,7 +169,8 @@ combine_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ rows,
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (row >= (int64_t)E * Cs) return;
-  const int e = (int)(row / Cs), s = (int)(row - (int64_t)e * Cs);
+  const int e_walk = (int)(row / Cs), s = (int)(row - (int64_t)e_walk * Cs);
+  const int e = pm.n > 0 ? peer_rotate_expert(pm, e_walk) : e_walk;
   const int cnt = counts[e];
   const int padded = (cnt + kTileRows - 1) / kTileRows * kTileRows;
   if (s >= padded) return;
@@ -191,7 +193,7 @@ combine_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ rows,
   const int64_t t = pair / k;
   const float g = gates[pair];
   const T* dyr = dy + t * M;
-  const T* orow = rows + row * M;
+  const T* orow = rows + ((int64_t)e * Cs + s) * M;      // the expert's row, not the walk position
   float dot = 0.f;
   for (int i = lane; i < nvec; i += 32) {
     float a[V], b[V], o[V];
