@@ -17,8 +17,11 @@
 // the next; where they do (c + c' > 512) the issuer first waits for the previous item's drain.
 //
 // The accumulator comes out transposed: a thread of the epilogue owns one feature and reads 16
-// rows of it per tcgen05.ld, and a warp's store instruction writes 32 neighbouring features of
-// one row (64 contiguous bytes).  Bias is one scalar per thread.
+// rows of it per tcgen05.ld; bias is one scalar per thread.  FC2 / dX store it as it comes (a
+// warp's store instruction writes 32 neighbouring features of one row, 64 contiguous bytes);
+// FC1 / dX2 turn each 16 x 32 block round in shared memory first and use 16-byte accesses (see
+// "FC1 / dX2 epilogue" below).  Experts of more than 320 rows are cut into panels of at most 256
+// rows for FC1 / dX2 (TcParams::panel_split), so that the next item's accumulator fits beside.
 //
 // Needs every expert's rows in one contiguous run (one source rank, or the compacted layout)
 // and outputs that stay in place (no row map).
