@@ -31,6 +31,7 @@ __global__ void __launch_bounds__(256)
 schedule_kernel(const int32_t* __restrict__ counts, int L, int n_src, int Cs, int e_begin,
                 int e_end, Schedule s) {
   __shared__ int part[256];
+  __shared__ int est[kMaxLocalExperts + 1];      // expert_tile_start, for the pair prefix below
   const int tid = threadIdx.x;
   const int npairs = (e_end - e_begin) * n_src;
   const int per = (npairs + 255) / 256;
@@ -47,12 +48,13 @@ schedule_kernel(const int32_t* __restrict__ counts, int L, int n_src, int Cs, in
     for (int i = 0; i < 256; ++i) { const int v = part[i]; part[i] = run; run += v; }
     *s.n_tiles = run;
     s.expert_tile_start[e_end - e_begin] = run;
+    est[e_end - e_begin] = run;
   }
   __syncthreads();
   int t = part[tid];
   for (int p = p0; p < p1; ++p) {
     const int l = e_begin + p / n_src, w = p % n_src;
-    if (w == 0) s.expert_tile_start[l - e_begin] = t;
+    if (w == 0) { s.expert_tile_start[l - e_begin] = t; est[l - e_begin] = t; }
     const int cnt = min(counts[w * L + l], Cs);
     const int nt = (cnt + kTileRows - 1) / kTileRows;
     const int row0 = (w * L + l) * Cs;
@@ -69,7 +71,7 @@ schedule_kernel(const int32_t* __restrict__ counts, int L, int n_src, int Cs, in
     int run = 0;
     for (int i = 0; i < ne; ++i) {
       s.expert_pair_start[i] = run;
-      run += (s.expert_tile_start[i + 1] - s.expert_tile_start[i] + 1) / 2;
+      run += (est[i + 1] - est[i] + 1) / 2;
     }
     s.expert_pair_start[ne] = run;
   }

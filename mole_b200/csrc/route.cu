@@ -360,27 +360,42 @@ __global__ void __launch_bounds__(kScanThreads)
 route_scan_kernel(int32_t* __restrict__ hist, const float* __restrict__ me_part, int64_t T,
                   int E, int k, int C, int nblk, int32_t* __restrict__ counts,
                   int32_t* __restrict__ offsets, int32_t* __restrict__ first_hist,
-                  float* __restrict__ l_aux) {
+                  float* __restrict__ l_aux, int32_t* __restrict__ perm) {
   __shared__ float prod[kMaxExperts];
   __shared__ int cnt[kMaxExperts];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n = k * nblk;
+  // perm starts as "no pair" everywhere (the slot kernel behind this one fills the kept pairs):
+  // done here instead of by a memset launch of its own
+  for (int64_t i = threadIdx.x; i < T * k; i += kScanThreads) perm[i] = -1;
   for (int e = warp; e < E; e += kScanThreads / 32) {
     int32_t* h = hist + (int64_t)e * n;
     int running = 0, first = 0;
-    for (int i0 = 0; i0 < n; i0 += 32) {
-      const int i = i0 + lane;
-      const int v = i < n ? h[i] : 0;
-      int incl = v;
+    // eight steps of 32 values are loaded at once: one memory round trip per 256 values
+    for (int i00 = 0; i00 < n; i00 += 256) {
+      int vv[8];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int u = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += u;
+      for (int j = 0; j < 8; ++j) {
+        const int i = i00 + 32 * j + lane;
+        vv[j] = i < n ? h[i] : 0;
       }
-      const int excl = running + incl - v;
-      if (i < n) h[i] = excl;
-      if (i == nblk) first = excl;              // everything of choice 0
-      running += __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i0 = i00 + 32 * j;
+        if (i0 >= n) break;                       // warp-uniform
+        const int i = i0 + lane;
+        const int v = vv[j];
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int u = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += u;
+        }
+        const int excl = running + incl - v;
+        if (i < n) h[i] = excl;
+        if (i == nblk) first = excl;              // everything of choice 0
+        running += __shfl_sync(0xffffffffu, incl, 31);
+      }
     }
     first = __reduce_max_sync(0xffffffffu, first);
     if (k == 1) first = running;
@@ -582,9 +597,8 @@ static int route_tail(RouteWs w, int64_t T, int E, int k, int C, int32_t* idx, i
                       float* gates, int32_t* counts, int32_t* offsets, int32_t* perm,
                       int32_t* first_hist, float* l_aux, cudaStream_t st) {
   const int nb = nblocks(T);
-  MOLE_CUDA_OK(cudaMemsetAsync(perm, 0xff, (size_t)T * k * 4, st));
   route_scan_kernel<<<1, kScanThreads, 0, st>>>(w.hist, w.me_part, T, E, k, C, nb, counts, offsets,
-                                               first_hist, l_aux);
+                                               first_hist, l_aux, perm);
   MOLE_LAUNCH_OK();
   route_slot_kernel<<<nb, kGateTok, 0, st>>>(idx, w.hist, offsets, T, E, k, C, nb, slot, gates,
                                              perm);
