@@ -66,6 +66,9 @@ def parse_args():
                     help="0 default, 1 CUDA cores, 2 one-CTA tcgen05, 3 CTA pairs (for comparisons)")
     ap.add_argument("--host-profile", action="store_true",
                     help="cProfile of the host side of a few steps on rank 0, printed to stderr")
+    ap.add_argument("--timeline", default="",
+                    help="write rank 0's kernel timeline of a few running steps (start, duration, gap "
+                         "to the previous kernel; CUPTI through torch.profiler) to this file and exit")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-report", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
@@ -297,6 +300,36 @@ def warm_up(step, hs: Harness, warmup: int):
             break
     hs.barrier()
     return extra
+
+
+def write_timeline(step, hs: Harness, rank, path, steps=6):
+    """Kernels of `steps` running layer steps in the order the GPU ran them, with the idle time
+    in front of each: what the per-kernel events of `gemm_roofline` cannot show (the small
+    kernels, the gaps, the waits of the expert-parallel barriers).  Per-step totals at the end."""
+    from torch.profiler import ProfilerActivity, profile
+    hs.barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+    hs.barrier()
+    if rank != 0:
+        return
+    evs = sorted((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                 if e.device_type == torch.autograd.DeviceType.CUDA)
+    first = [i for i, e in enumerate(evs) if "gate_topk" in e[2]]
+    with open(path, "w") as out:
+        prev_end = None
+        for s0, s1, name in evs:
+            gap = 0.0 if prev_end is None else s0 - prev_end
+            out.write("%12.1f us  dur %8.1f  gap %7.1f  %s\n" % (s0 - evs[0][0], s1 - s0, gap, name[:100]))
+            prev_end = s1 if prev_end is None else max(prev_end, s1)
+        for a, b in zip(first, first[1:]):
+            busy = sum(e[1] - e[0] for e in evs[a:b])
+            gemm = sum(e[1] - e[0] for e in evs[a:b] if "gemm" in e[2] or "wgrad_resident" in e[2])
+            out.write("step: %.1f us from its first kernel to the next step's; kernels %.1f us, of them "
+                      "grouped GEMMs %.1f us; %d launches\n" % (evs[b][0] - evs[a][0], busy, gemm, b - a))
+    print(json.dumps({"timeline": path, "kernels": len(evs), "steps": steps}))
 
 
 def check_fault(where):
@@ -882,6 +915,11 @@ def run_ours(args):
     extra = warm_up(step, hs, args.warmup)
     check_fault("after the warm-up")
 
+    if args.timeline:
+        write_timeline(step, hs, rank, args.timeline)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.host_profile and rank == 0:
         import cProfile
         import pstats
