@@ -85,8 +85,11 @@ struct Workspace {
   float* colsum;     // partial column sums of dX1 from the dX2 launch (panel kernel), or null
 };
 // Column sums of dX1 (the FC1 bias gradient) come out of the dX2 launch when the panel kernel
-// takes it: its epilogue threads each own one feature and walk down the rows anyway.
-static bool fused_colsum(const mole_ffn_desc* d) { return use_tc(d) && panel_ok(d) && d->F % 256 == 0; }
+// takes it (its epilogue threads each own one feature and walk down the rows anyway) or the
+// CTA-pair tile kernel (many rows per expert: the epilogue is hidden behind the main loop).
+static bool fused_colsum(const mole_ffn_desc* d) {
+  return use_tc(d) && d->F % 256 == 0 && (panel_ok(d) || !single_cta(d));
+}
 static int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 static int64_t workspace_bytes_of(const mole_ffn_desc* d) {
   int64_t b = align256(schedule_bytes(d->L, d->n_src, d->Cs));

@@ -534,13 +534,16 @@ panel_gemm_kernel(const __grid_constant__ PanelMaps maps, const __grid_constant_
   }
 }
 
-// Column sums that the dX2 panel kernel left as partial sums -- per (expert, panel, one of the four
-// row groups of the epilogue, feature) -- added in a fixed order: bit-reproducible.
+// Column sums that a dX2 launch left as partial sums -- the panel kernel per (expert, panel, one of
+// the four row groups of the epilogue, feature), the CTA-pair tile kernel per (row tile, one of
+// the tile's four 32-row quarters, feature) -- added in a fixed order: bit-reproducible.
 struct PanelColsumArgs {
   const float* ws;
   const int32_t* expert_tile_start;
   const int32_t* tile_rows;
   const int32_t* expert_pair_start;
+  const int32_t* tile_row0;    // tile layout (the CTA-pair tile kernel's partials, [row0 / 128][4][N])
+  int tiles;                   // 1: tile layout
   int N, panels, split, accumulate, e_begin;
   __nv_bfloat16* out;          // [n_slots, N]
   SlotMap gslot;
@@ -552,9 +555,16 @@ panel_colsum_reduce_kernel(const __grid_constant__ PanelColsumArgs a) {
   if (n >= a.N) return;
   const int ts = a.expert_tile_start[el], te = a.expert_tile_start[el + 1];
   const int rows = te > ts ? (te - ts - 1) * kTileRows + a.tile_rows[te - 1] : 0;
-  const int np = panel_count(rows, a.expert_pair_start[el + 1] - a.expert_pair_start[el], a.split);
   float v = 0.f;
-  for (int i = 0; i < np * 4; ++i) v += a.ws[((int64_t)el * a.panels * 4 + i) * a.N + n];
+  if (a.tiles) {
+    for (int t = ts; t < te; ++t) {
+      const float* part = a.ws + (int64_t)(a.tile_row0[t] / kTileRows) * 4 * a.N + n;
+      for (int q = 0; q < 4; ++q) v += part[(int64_t)q * a.N];
+    }
+  } else {
+    const int np = panel_count(rows, a.expert_pair_start[el + 1] - a.expert_pair_start[el], a.split);
+    for (int i = 0; i < np * 4; ++i) v += a.ws[((int64_t)el * a.panels * 4 + i) * a.N + n];
+  }
   __nv_bfloat16* out = a.out + (int64_t)a.gslot.s[a.e_begin + el] * a.N + n;
   if (a.accumulate) v += __bfloat162float(*out);
   *out = __float2bfloat16_rn(v);

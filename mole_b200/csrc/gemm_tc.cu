@@ -261,6 +261,7 @@ struct TcParams {
   int panel_split;          // panel kernel: experts of more than 320 rows are cut into panels of <= 256 rows
   float* colsum_ws;         // panel kernel, dX2: partial column sums [expert][panel][4][N], or null
   int colsum_panels;        // panels per expert the partial sums are laid out for
+  int colsum_tiles;         // 1: colsum_ws is laid out per row tile instead, [row0 / 128][4][N] (CTA-pair tile kernel)
   const __nv_bfloat16* bias;
   const __nv_bfloat16* aux;
   __nv_bfloat16* out0;
@@ -509,7 +510,8 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
                                               bool valid, __nv_bfloat16* sout, int64_t obase,
                                               const float* bias_s, int c_begin,
                                               uint32_t (&pre)[NSTEPS][8], uint8_t* strip,
-                                              __nv_bfloat16* yrow = nullptr, float gate = 0.f) {
+                                              __nv_bfloat16* yrow = nullptr, float gate = 0.f,
+                                              float* cs_part = nullptr, uint16_t* cs_strip = nullptr) {
   const bool remote = (EPI == EPI_BIAS || EPI == EPI_STORE) && p.peer_n > 0;
   uint32_t keep[NSTEPS][8];       // remote rows: the whole slice first, then whole-line stores
   {
@@ -577,6 +579,27 @@ __device__ __forceinline__ void epilogue_loop(const TcParams& p, uint32_t taddr,
         for (int i = 0; i < 8; ++i)
           o[i] = act_bwd_pair<ACT, GBWD>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), cur[i]);
         st_v8(p.out0 + obase + c, o);
+        if (cs_part != nullptr) {
+          // Column sums of the warp's 32 rows (of the stored, rounded values) for these 16 columns:
+          // through a [16 columns][32 rows] strip of bf16 (1 KB); lane l adds 16 rows of column l % 16, starting
+          // at a row that differs from lane to lane (no bank conflicts), and the two halves meet
+          // in one shuffle.  Lanes 0-15 store the sums: one partial per (row tile, warp, column).
+          const int lane = threadIdx.x & 31;
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            cs_strip[(2 * i) * 32 + lane] = (uint16_t)(o[i] & 0xffffu);
+            cs_strip[(2 * i + 1) * 32 + lane] = (uint16_t)(o[i] >> 16);
+          }
+          __syncwarp();
+          const int col = lane & 15, half = lane >> 4;
+          float sum = 0.f;
+#pragma unroll
+          for (int rr = 0; rr < 16; ++rr)
+            sum += __uint_as_float((uint32_t)cs_strip[col * 32 + half * 16 + ((rr + col) & 15)] << 16);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+          if (half == 0) cs_part[c + col] = sum;
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -1305,10 +1328,16 @@ tc2_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           epilogue_lines<NSTEPS>(p.out0, obase - (int64_t)lane * p.N, p.N,
                                  tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty,
                                  cq * (kBN2 / 4), store_strip[ew]);
-        else
+        else {
+          // dX2 with fused column sums: this warp's partial row for its (row tile, quarter)
+          float* cs_part = nullptr;
+          if (Ev::epi == EPI_DACT && MODE == TC_ROWS && p.colsum_ws != nullptr && p.colsum_tiles)
+            cs_part = p.colsum_ws + ((int64_t)(r0 / kTileRows) * 4 + quarter) * p.N + w.n0;
           epilogue_loop<Ev::epi, Ev::act, Ev::gbwd, Ev::bias, Ev::accum, NSTEPS>(
               p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN2, empty, valid, sout, obase,
-              bias_strip[ew], cq * (kBN2 / 4), pre, scatter_strip[ew]);
+              bias_strip[ew], cq * (kBN2 / 4), pre, scatter_strip[ew], nullptr, 0.f, cs_part,
+              reinterpret_cast<uint16_t*>(scatter_strip[ew]));
+        }
       }
       if (!empty) {
         tcgen05_fence_before();
@@ -1589,11 +1618,19 @@ static bool takes_panel(const RowGemmArgs& a) {
 static int panel_split_of(const RowGemmArgs& a) { return a.epi == EPI_FC1 || a.epi == EPI_DACT; }
 static int colsum_panels_of(int max_rows_per_expert) { return (max_rows_per_expert + 255) / 256; }
 
-bool tc_panel_colsum(const RowGemmArgs& a) {
-  return a.epi == EPI_DACT && a.colsum_ws != nullptr && takes_panel(a);
+// The CTA-pair tile kernel sums too (per row tile), where it runs the dX2 launch: that is the
+// many-rows-per-expert regime, in which its epilogue is hidden behind the main loop.
+static bool tile_colsum(const RowGemmArgs& a) {
+  return a.epi == EPI_DACT && a.colsum_ws != nullptr && !takes_panel(a) && a.N % 256 == 0 &&
+         !a.single_cta && a.rowmap == nullptr;
 }
+bool tc_panel_colsum(const RowGemmArgs& a) {
+  return a.epi == EPI_DACT && a.colsum_ws != nullptr && (takes_panel(a) || tile_colsum(a));
+}
+// room for either layout: [expert][panel][4][N] or [row tile][4][N]
 int64_t tc_panel_colsum_bytes(int n_experts, int max_rows_per_expert, int N) {
-  return (int64_t)n_experts * colsum_panels_of(max_rows_per_expert) * 4 * N * (int64_t)sizeof(float);
+  const int64_t per_expert = (max_rows_per_expert + kTileRows - 1) / kTileRows;     // >= its panels
+  return (int64_t)n_experts * per_expert * 4 * N * (int64_t)sizeof(float);
 }
 int tc_panel_colsum_reduce(const RowGemmArgs& a, const SlotMap& gslot, int accumulate, void* out,
                            cudaStream_t st) {
@@ -1604,6 +1641,8 @@ int tc_panel_colsum_reduce(const RowGemmArgs& a, const SlotMap& gslot, int accum
   r.expert_tile_start = a.sched.expert_tile_start;
   r.tile_rows = a.sched.tile_rows;
   r.expert_pair_start = a.sched.expert_pair_start;
+  r.tile_row0 = a.sched.tile_row0;
+  r.tiles = tile_colsum(a) ? 1 : 0;
   r.N = a.N;
   r.panels = colsum_panels_of(a.max_rows_per_expert);
   r.split = panel_split_of(a);
@@ -1661,6 +1700,7 @@ int tc_row_gemm(const RowGemmArgs& a, cudaStream_t st) {
   p.panel_split = panel_split_of(a);
   p.colsum_ws = tc_panel_colsum(a) ? a.colsum_ws : nullptr;
   p.colsum_panels = colsum_panels_of(a.max_rows_per_expert);
+  p.colsum_tiles = tile_colsum(a) ? 1 : 0;
   p.bias = static_cast<const __nv_bfloat16*>(a.bias);
   p.aux = static_cast<const __nv_bfloat16*>(a.aux);
   p.out0 = static_cast<__nv_bfloat16*>(a.out0);

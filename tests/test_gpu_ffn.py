@@ -204,8 +204,11 @@ def test_ffn_bf16_full_size_spot_check():
         assert rel_fro(a, b) < 4e-3
     # the CTA-pair kernel and the one-CTA kernel accumulate in the same order: identical bits
     assert torch.equal(out[valid], out3[valid]) and torch.equal(dx[valid], dx3[valid])
-    for a, b in zip(grads, grads3):
-        assert torch.equal(a, b)
+    for i, (a, b) in enumerate(zip(grads, grads3)):
+        if i == 1:      # FC1 bias gradient: summed in the CTA-pair kernel's dX2 epilogue, in another order
+            assert rel_fro(a, b) < 2e-3
+        else:
+            assert torch.equal(a, b)
     # the panel kernel (two or three row panels per expert here) sums over K in the same order
     out4, dx4, grads4 = run_gpu(case, backend=4)
     assert torch.equal(out[valid], out4[valid]) and torch.equal(dx[valid], dx4[valid])
