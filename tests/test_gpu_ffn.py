@@ -157,7 +157,7 @@ def test_ffn_bf16_four_sources_packed_per_expert(backend):
         assert torch.isnan(out_r[:, l].float()).all()
 
 
-@pytest.mark.parametrize("backend", [0, 4], ids=["default", "tcgen05_panel"])
+@pytest.mark.parametrize("backend", [0, 3, 4], ids=["default", "tcgen05_cta_pair", "tcgen05_panel"])
 def test_ffn_bf16_expert_range_slots_and_accumulate(backend):
     """A record of experts [2, 5) with weights living in permuted slots and gradients
     accumulated onto existing values (the offload pipeline's way of calling the FFN)."""
