@@ -66,6 +66,9 @@ def parse_args():
                     help="0 default, 1 CUDA cores, 2 one-CTA tcgen05, 3 CTA pairs (for comparisons)")
     ap.add_argument("--host-profile", action="store_true",
                     help="cProfile of the host side of a few steps on rank 0, printed to stderr")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="one GPU, GPU-resident experts: capture the step in a CUDA graph "
+                         "(mole_b200.utils.Ugraph.GraphedStep) and time its replays")
     ap.add_argument("--timeline", default="",
                     help="write rank 0's kernel timeline of a few running steps (start, duration, gap "
                          "to the previous kernel; CUPTI through torch.profiler) to this file and exit")
@@ -906,11 +909,27 @@ def run_ours(args):
     L = E // world
     MOLEDist(local_rank=local)
     hs = Harness(world, device)
-    m, x, gy = build_layer(cfg, world, rank, local, dtype, args.ffn_backend)
+    # --cuda-graph: the layer and its inputs are created on the stream the step is captured on
+    # (autograd ties the accumulation into a leaf's .grad to the stream of its creation)
+    use_graph = bool(args.cuda_graph) and world == 1 and not cfg.get("offload")
+    gstream = torch.cuda.Stream() if use_graph else None
+    if use_graph:
+        with torch.cuda.stream(gstream):
+            m, x, gy = build_layer(cfg, world, rank, local, dtype, args.ffn_backend)
+        torch.cuda.synchronize()
+    else:
+        m, x, gy = build_layer(cfg, world, rank, local, dtype, args.ffn_backend)
     want_parity = not args.no_parity and not cfg.get("offload")
     if want_parity:
         m.parity_tap = {}
     step = make_step(m, x, gy, cf)
+    if use_graph:
+        # eager runs of the step (warm-up, GEMM timing, parity) stay on the capture stream as well
+        raw_step = step
+
+        def step():
+            with torch.cuda.stream(gstream):
+                return raw_step()
 
     extra = warm_up(step, hs, args.warmup)
     check_fault("after the warm-up")
@@ -939,11 +958,24 @@ def run_ours(args):
     # A region in which the host needed nearly as long to enqueue a step as the GPU to run it
     # (another tenant's job on the host's cores) measures the host, not the kernels: it is taken
     # again, at most twice, and the count is reported.
+    timed_step, launches_per_step = step, None
+    if use_graph:
+        from mole_b200.utils.Ugraph import GraphedStep
+        m.l_aux = None                        # lets the eager steps' autograd graph go
+        if want_parity:
+            m.parity_tap = {}
+        torch.cuda.synchronize()
+        c0 = hs.launches()
+        timed_step = GraphedStep(raw_step, gstream, warmup=3)
+        launches_per_step = (hs.launches() - c0) // 4      # three warm-up runs and the captured one
+        for _ in range(3):
+            timed_step()
+        hs.barrier()
     host_bound_retries = 0
     while True:
         with ClockSampler(local) as clocks:
             n0 = hs.launches()
-            ms, host_ms = hs.timed(step, args.steps)
+            ms, host_ms = hs.timed(timed_step, args.steps)
             n1 = hs.launches()
         host_bound = hs.max_over_ranks(1.0 if host_ms >= 0.85 * ms / args.steps else 0.0) > 0
         if not host_bound or host_bound_retries >= 2:
@@ -999,7 +1031,8 @@ def run_ours(args):
                          "the 126 MB L2, so no flush is needed between iterations",
                    "timing": "CUDA events around the K steps on the launching stream; a ~25 ms GPU spin "
                              "queued before the first event lets the host enqueue ahead"},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": n1 - n0,
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": (n1 - n0) if launches_per_step is None else launches_per_step * args.steps,
+        "cuda_graph": use_graph,
         "host_enqueue_ms_per_step": host_ms, "host_bound_retries": host_bound_retries,
         "warmup_settling_steps": extra,
     }

@@ -60,7 +60,9 @@ int mole_device_fault(void* stream, int32_t* fault);
  * of the fault word (of the current device) into pinned host memory behind the work already on
  * `stream`; mole_device_fault_peek returns the value of the last such copy that has landed (0
  * before the first).  MOLECore polls at the end of every backward and peeks at the start of the
- * next forward.  The reference has no counterpart: its device code cannot time out. */
+ * next forward.  On a stream that is being captured into a CUDA graph the poll does nothing
+ * (its event would become part of the graph): poll behind a replay.  The reference has no
+ * counterpart: its device code cannot time out. */
 int mole_device_fault_poll(void* stream);
 int mole_device_fault_peek(int32_t* fault);
 

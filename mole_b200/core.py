@@ -627,6 +627,8 @@ class MOLECore:
         """Raises if a kernel of an earlier step recorded that one of its bounded waits ran out
         (that step's activations and gradients are not to be trusted).  Reads a host copy that
         ``_poll_fault`` requested behind the previous backward: no device synchronisation."""
+        if torch.cuda.is_current_stream_capturing():
+            return          # no event queries while a CUDA graph is being captured (Ugraph polls behind replays)
         code = ops.device_fault_peek()
         if code:
             raise RuntimeError(

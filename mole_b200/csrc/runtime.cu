@@ -137,6 +137,11 @@ extern "C" int mole_device_fault_poll(void* stream) {
   FaultSlot* f = fault_slot();
   if (!f || !f->host || !f->polled) return fail(MOLE_ERR_CUDA, "fault word not allocated");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // A stream that is being captured into a CUDA graph takes no poll: the event of the copy would
+  // become part of the graph and could no longer be queried.  Whoever replays the graph polls
+  // behind a replay instead.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) return MOLE_OK;
   if (f->poll_pending && cudaEventQuery(f->polled) != cudaSuccess) {
     cudaGetLastError();           // the previous poll's copy is still in flight: keep that one
     return MOLE_OK;

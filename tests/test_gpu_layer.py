@@ -193,3 +193,59 @@ def test_layer_bf16_combine_fused_into_second_gemm(k):
     assert torch.equal(m.FC1_W_GPU.grad_tensors, m0.FC1_W_GPU.grad_tensors)
     # the fused path really ran: a second forward without the fusion differs in rounding somewhere
     assert not torch.equal(y, y0) or k == 1
+
+
+def test_layer_step_replayed_from_a_cuda_graph():
+    """Forward + backward of a layer captured once in a CUDA graph and replayed: the replay gives
+    the eager step's bits -- on the inputs of the capture and on new ones copied into the same
+    tensors -- and leaves one graph launch per step on the host side."""
+    from mole_b200.utils.Ugraph import GraphedStep
+    T, M, E, F, k, cf = 2048, 256, 16, 512, 2, 1.25
+    inp = O.make_inputs(T, M, E, F, seed=31)
+    inp["wg"] = inp["wg"] * 5
+    g = torch.Generator().manual_seed(5)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):          # leaves are created on the stream the step will be captured on
+        m = build_module(inp, E, M, F, k, torch.bfloat16)
+        x = inp["x"].to(torch.bfloat16).cuda().requires_grad_(True)
+        gy = inp["gy"].to(torch.bfloat16).cuda()
+        x2 = torch.randn(T, M, generator=g).to(torch.bfloat16).cuda()
+    torch.cuda.synchronize()
+
+    def step():
+        x.grad = None
+        m.gate[0].linear.weight.grad = None
+        y = m(x, capacity_factor=cf)
+        y.backward(gy)
+        return y
+
+    def snapshot(y):
+        torch.cuda.synchronize()
+        return [t.detach().clone() for t in (y, x.grad, m.gate[0].linear.weight.grad,
+                                              m.FC1_W_GPU.grad_tensors, m.FC1_B_GPU.grad_tensors,
+                                              m.FC2_W_GPU.grad_tensors, m.FC2_B_GPU.grad_tensors)]
+
+    with torch.cuda.stream(s):
+        eager1 = snapshot(step())
+        with torch.no_grad():
+            x_saved = x.detach().clone()
+            x.copy_(x2)
+        eager2 = snapshot(step())
+        with torch.no_grad():
+            x.copy_(x_saved)
+    torch.cuda.synchronize()
+
+    # the layer keeps l_aux (and with it the autograd graph of the last eager forward, whose leaf
+    # nodes are tied to the stream of that forward): let it go before the capture
+    m.l_aux = None
+    graphed = GraphedStep(step, s)
+    got1 = snapshot(graphed())
+    with torch.no_grad():
+        x.copy_(x2)
+    got2 = snapshot(graphed())
+    torch.cuda.synchronize()
+    for name, a, b in zip(("y", "dx", "dWg", "gW1", "gb1", "gW2", "gb2"), eager1, got1):
+        assert torch.equal(a, b), f"{name}: replay differs from the eager step"
+    for name, a, b in zip(("y", "dx", "dWg", "gW1", "gb1", "gW2", "gb2"), eager2, got2):
+        assert torch.equal(a, b), f"{name}: replay on new inputs differs from the eager step"
+    assert not torch.equal(eager1[0], eager2[0])
